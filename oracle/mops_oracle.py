@@ -1,0 +1,304 @@
+"""Test infrastructure, not product code: Python access to the two CPU checkers.
+
+``Oracle``     this repository's plain-C restatement (``mops_oracle.c``), loaded from
+               ``oracle/_ref/libmops_oracle.so``.
+``Reference``  the unmodified reference CPU library built from the reference sources by
+               ``oracle/Makefile`` (``oracle/_ref/libmops_ref.so``), called through its own
+               C ABI (``mops/include/mops/*.h``): by-value ``{data, int64 shape[N]}`` structs,
+               status 0/1/2 and ``mops_get_last_error_message``.
+
+Both expose the same NumPy-level functions so tests can swap one for the other.
+Only ``tests/``, ``__graft_entry__.smoke()`` and the CPU legs of ``bench.py`` import this
+module; the library under test never does.
+"""
+import ctypes
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+ORACLE_SO = os.path.join(_HERE, "_ref", "libmops_oracle.so")
+REFERENCE_SO = os.path.join(_HERE, "_ref", "libmops_ref.so")
+
+_SUFFIX = {np.dtype("float32"): "f32", np.dtype("float64"): "f64"}
+_I64 = ctypes.c_int64
+
+
+def _c(a):
+    return np.ascontiguousarray(a)
+
+
+def _i32(a):
+    return np.ascontiguousarray(a, dtype=np.int32)
+
+
+def _ptr(a):
+    return None if a is None else ctypes.c_void_p(a.ctypes.data)
+
+
+class Oracle:
+    """ctypes front end of ``mops_oracle.c`` (pointer + sizes signatures)."""
+
+    def __init__(self, path=ORACLE_SO):
+        if not os.path.exists(path):
+            raise FileNotFoundError(f"{path} is missing: run `make -C oracle oracle`")
+        self.lib = ctypes.CDLL(path)
+
+    def _call(self, name, dtype, ptrs, sizes):
+        fn = getattr(self.lib, f"oracle_{name}_{_SUFFIX[np.dtype(dtype)]}")
+        fn.restype = None
+        fn.argtypes = [ctypes.c_void_p] * len(ptrs) + [_I64] * len(sizes)
+        fn(*[_ptr(p) for p in ptrs], *[int(s) for s in sizes])
+
+    # ---- HPE
+    def hpe(self, A, C, P):
+        A, C, P = _c(A), _c(C), _i32(P)
+        O = np.empty(A.shape[0], A.dtype)
+        self._call("hpe", A.dtype, [O, A, C, P], [A.shape[0], A.shape[1], P.shape[0], P.shape[1]])
+        return O
+
+    def hpe_vjp(self, gO, A, C, P):
+        gO, A, C, P = _c(gO), _c(A), _c(C), _i32(P)
+        gA = np.empty_like(A)
+        self._call("hpe_vjp", A.dtype, [gA, gO, A, C, P],
+                   [A.shape[0], A.shape[1], P.shape[0], P.shape[1]])
+        return gA
+
+    # ---- SAP
+    def sap(self, A, B, C, PA, PB, PO, n_out):
+        A, B, C = _c(A), _c(B), _c(C)
+        PA, PB, PO = _i32(PA), _i32(PB), _i32(PO)
+        O = np.empty((A.shape[0], n_out), A.dtype)
+        self._call("sap", A.dtype, [O, A, B, C, PA, PB, PO],
+                   [A.shape[0], A.shape[1], B.shape[1], n_out, C.shape[0]])
+        return O
+
+    def sap_vjp(self, gO, A, B, C, PA, PB, PO, need=(True, True)):
+        gO, A, B, C = _c(gO), _c(A), _c(B), _c(C)
+        PA, PB, PO = _i32(PA), _i32(PB), _i32(PO)
+        gA = np.empty_like(A) if need[0] else None
+        gB = np.empty_like(B) if need[1] else None
+        self._call("sap_vjp", A.dtype, [gA, gB, gO, A, B, C, PA, PB, PO],
+                   [A.shape[0], A.shape[1], B.shape[1], gO.shape[1], C.shape[0]])
+        return gA, gB
+
+    def sap_vjp_vjp(self, ggA, ggB, gO, A, B, C, PA, PB, PO, need=(True, True, True)):
+        gO, A, B, C = _c(gO), _c(A), _c(B), _c(C)
+        ggA = None if ggA is None else _c(ggA)
+        ggB = None if ggB is None else _c(ggB)
+        PA, PB, PO = _i32(PA), _i32(PB), _i32(PO)
+        ggO = np.empty_like(gO) if need[0] else None
+        gA2 = np.empty_like(A) if need[1] else None
+        gB2 = np.empty_like(B) if need[2] else None
+        self._call("sap_vjp_vjp", A.dtype, [ggO, gA2, gB2, ggA, ggB, gO, A, B, C, PA, PB, PO],
+                   [A.shape[0], A.shape[1], B.shape[1], gO.shape[1], C.shape[0]])
+        return ggO, gA2, gB2
+
+    # ---- OPSA
+    def opsa(self, A, B, P, n_out):
+        A, B, P = _c(A), _c(B), _i32(P)
+        O = np.empty((n_out, A.shape[1], B.shape[1]), A.dtype)
+        self._call("opsa", A.dtype, [O, A, B, P], [A.shape[0], A.shape[1], B.shape[1], n_out])
+        return O
+
+    def opsa_vjp(self, gO, A, B, P, need=(True, True)):
+        gO, A, B, P = _c(gO), _c(A), _c(B), _i32(P)
+        gA = np.empty_like(A) if need[0] else None
+        gB = np.empty_like(B) if need[1] else None
+        self._call("opsa_vjp", A.dtype, [gA, gB, gO, A, B, P],
+                   [A.shape[0], A.shape[1], B.shape[1], gO.shape[0]])
+        return gA, gB
+
+    # ---- OPSAW
+    def opsaw(self, A, B, W, PW, PO):
+        A, B, W, PW, PO = _c(A), _c(B), _c(W), _i32(PW), _i32(PO)
+        O = np.empty((W.shape[0], A.shape[1], B.shape[1]), A.dtype)
+        self._call("opsaw", A.dtype, [O, A, B, W, PW, PO],
+                   [A.shape[0], A.shape[1], B.shape[1], W.shape[0]])
+        return O
+
+    def opsaw_vjp(self, gO, A, B, W, PW, PO, need=(True, True, True)):
+        gO, A, B, W, PW, PO = _c(gO), _c(A), _c(B), _c(W), _i32(PW), _i32(PO)
+        gA = np.empty_like(A) if need[0] else None
+        gB = np.empty_like(B) if need[1] else None
+        gW = np.empty_like(W) if need[2] else None
+        self._call("opsaw_vjp", A.dtype, [gA, gB, gW, gO, A, B, W, PW, PO],
+                   [A.shape[0], A.shape[1], B.shape[1], W.shape[0]])
+        return gA, gB, gW
+
+    # ---- SASAW (M1 = indices_A, Jw = indices_W_1, M2 = indices_W_2, Io = indices_output_1,
+    #             M3 = indices_output_2)
+    def sasaw(self, A, B, C, W, M1, Jw, M2, Io, M3, n_out_2):
+        A, B, C, W = _c(A), _c(B), _c(C), _c(W)
+        M1, Jw, M2, Io, M3 = _i32(M1), _i32(Jw), _i32(M2), _i32(Io), _i32(M3)
+        O = np.empty((W.shape[0], n_out_2, B.shape[1]), A.dtype)
+        self._call("sasaw", A.dtype, [O, A, B, C, W, M1, Jw, M2, Io, M3],
+                   [A.shape[0], A.shape[1], B.shape[1], C.shape[0], W.shape[0], W.shape[1],
+                    n_out_2])
+        return O
+
+    def sasaw_vjp(self, gO, A, B, C, W, M1, Jw, M2, Io, M3, need=(True, True, True)):
+        gO, A, B, C, W = _c(gO), _c(A), _c(B), _c(C), _c(W)
+        M1, Jw, M2, Io, M3 = _i32(M1), _i32(Jw), _i32(M2), _i32(Io), _i32(M3)
+        gA = np.empty_like(A) if need[0] else None
+        gB = np.empty_like(B) if need[1] else None
+        gW = np.empty_like(W) if need[2] else None
+        self._call("sasaw_vjp", A.dtype, [gA, gB, gW, gO, A, B, C, W, M1, Jw, M2, Io, M3],
+                   [A.shape[0], A.shape[1], B.shape[1], C.shape[0], W.shape[0], W.shape[1],
+                    gO.shape[1]])
+        return gA, gB, gW
+
+
+# ------------------------------------------------------------------ reference C ABI
+def _struct(ndim, ctype):
+    class S(ctypes.Structure):
+        _fields_ = [("data", ctypes.c_void_p), ("shape", _I64 * ndim)]
+    return S
+
+
+_STRUCTS = {(n, k): _struct(n, None) for n in (1, 2, 3) for k in ("f32", "f64", "i32")}
+
+
+class Null:
+    """Stand-in for a gradient the caller does not want: ``{NULL, {0,…}}``."""
+
+    def __init__(self, ndim, dtype):
+        self.ndim, self.dtype = ndim, np.dtype(dtype)
+
+
+def _as_struct(a):
+    if isinstance(a, Null):
+        kind = "i32" if a.dtype == np.int32 else _SUFFIX[a.dtype]
+        s = _STRUCTS[(a.ndim, kind)]()
+        s.data = None
+        return s
+    kind = "i32" if a.dtype == np.int32 else _SUFFIX[a.dtype]
+    s = _STRUCTS[(a.ndim, kind)]()
+    s.data = a.ctypes.data
+    for d in range(a.ndim):
+        s.shape[d] = a.shape[d]
+    return s
+
+
+class ReferenceError_(RuntimeError):
+    pass
+
+
+class Reference:
+    """The unmodified reference CPU library through its C ABI (``mops_<op>_{f32,f64}``)."""
+
+    NAMES = {
+        "hpe": "homogeneous_polynomial_evaluation",
+        "sap": "sparse_accumulation_of_products",
+        "opsa": "outer_product_scatter_add",
+        "opsaw": "outer_product_scatter_add_with_weights",
+        "sasaw": "sparse_accumulation_scatter_add_with_weights",
+    }
+
+    def __init__(self, path=REFERENCE_SO, prefix="mops_"):
+        if not os.path.exists(path):
+            raise FileNotFoundError(f"{path} is missing: run `make -C oracle ref`")
+        # RTLD_LOCAL: the library under test exports the same symbol names.
+        self.lib = ctypes.CDLL(path, mode=os.RTLD_LOCAL | os.RTLD_NOW)
+        self.prefix = prefix
+        self.lib.mops_get_last_error_message.restype = ctypes.c_char_p
+
+    def raw(self, op, level, dtype, *args):
+        """Call ``<prefix><op><level>_<dtype>`` with arrays / ``Null`` placeholders."""
+        sym = f"{self.prefix}{self.NAMES[op]}{level}_{_SUFFIX[np.dtype(dtype)]}"
+        fn = getattr(self.lib, sym)
+        fn.restype = ctypes.c_int
+        structs = [_as_struct(a) for a in args]
+        fn.argtypes = [type(s) for s in structs]
+        status = fn(*structs)
+        if status != 0:
+            raise ReferenceError_(self.lib.mops_get_last_error_message().decode())
+
+    def hpe(self, A, C, P):
+        A, C, P = _c(A), _c(C), _i32(P)
+        O = np.empty(A.shape[0], A.dtype)
+        self.raw("hpe", "", A.dtype, O, A, C, P)
+        return O
+
+    def hpe_vjp(self, gO, A, C, P):
+        gO, A, C, P = _c(gO), _c(A), _c(C), _i32(P)
+        gA = np.empty_like(A)
+        self.raw("hpe", "_vjp", A.dtype, gA, gO, A, C, P)
+        return gA
+
+    def sap(self, A, B, C, PA, PB, PO, n_out):
+        A, B, C, PA, PB, PO = _c(A), _c(B), _c(C), _i32(PA), _i32(PB), _i32(PO)
+        O = np.empty((A.shape[0], n_out), A.dtype)
+        self.raw("sap", "", A.dtype, O, A, B, C, PA, PB, PO)
+        return O
+
+    def sap_vjp(self, gO, A, B, C, PA, PB, PO, need=(True, True)):
+        gO, A, B, C, PA, PB, PO = _c(gO), _c(A), _c(B), _c(C), _i32(PA), _i32(PB), _i32(PO)
+        gA = np.empty_like(A) if need[0] else None
+        gB = np.empty_like(B) if need[1] else None
+        self.raw("sap", "_vjp", A.dtype, gA if need[0] else Null(2, A.dtype),
+                 gB if need[1] else Null(2, A.dtype), gO, A, B, C, PA, PB, PO)
+        return gA, gB
+
+    def sap_vjp_vjp(self, ggA, ggB, gO, A, B, C, PA, PB, PO, need=(True, True, True)):
+        gO, A, B, C, PA, PB, PO = _c(gO), _c(A), _c(B), _c(C), _i32(PA), _i32(PB), _i32(PO)
+        ggO = np.empty_like(gO) if need[0] else None
+        gA2 = np.empty_like(A) if need[1] else None
+        gB2 = np.empty_like(B) if need[2] else None
+        n2 = Null(2, A.dtype)
+        self.raw("sap", "_vjp_vjp", A.dtype, ggO if need[0] else n2, gA2 if need[1] else n2,
+                 gB2 if need[2] else n2, n2 if ggA is None else _c(ggA),
+                 n2 if ggB is None else _c(ggB), gO, A, B, C, PA, PB, PO)
+        return ggO, gA2, gB2
+
+    def opsa(self, A, B, P, n_out):
+        A, B, P = _c(A), _c(B), _i32(P)
+        O = np.empty((n_out, A.shape[1], B.shape[1]), A.dtype)
+        self.raw("opsa", "", A.dtype, O, A, B, P)
+        return O
+
+    def opsa_vjp(self, gO, A, B, P, need=(True, True)):
+        gO, A, B, P = _c(gO), _c(A), _c(B), _i32(P)
+        gA = np.empty_like(A) if need[0] else None
+        gB = np.empty_like(B) if need[1] else None
+        n2 = Null(2, A.dtype)
+        self.raw("opsa", "_vjp", A.dtype, gA if need[0] else n2, gB if need[1] else n2, gO, A, B, P)
+        return gA, gB
+
+    def opsaw(self, A, B, W, PW, PO):
+        A, B, W, PW, PO = _c(A), _c(B), _c(W), _i32(PW), _i32(PO)
+        O = np.empty((W.shape[0], A.shape[1], B.shape[1]), A.dtype)
+        self.raw("opsaw", "", A.dtype, O, A, B, W, PW, PO)
+        return O
+
+    def opsaw_vjp(self, gO, A, B, W, PW, PO, need=(True, True, True)):
+        gO, A, B, W, PW, PO = _c(gO), _c(A), _c(B), _c(W), _i32(PW), _i32(PO)
+        gA = np.empty_like(A) if need[0] else None
+        gB = np.empty_like(B) if need[1] else None
+        gW = np.empty_like(W) if need[2] else None
+        n2 = Null(2, A.dtype)
+        self.raw("opsaw", "_vjp", A.dtype, gA if need[0] else n2, gB if need[1] else n2,
+                 gW if need[2] else n2, gO, A, B, W, PW, PO)
+        return gA, gB, gW
+
+    def sasaw(self, A, B, C, W, M1, Jw, M2, Io, M3, n_out_2):
+        A, B, C, W = _c(A), _c(B), _c(C), _c(W)
+        M1, Jw, M2, Io, M3 = _i32(M1), _i32(Jw), _i32(M2), _i32(Io), _i32(M3)
+        O = np.empty((W.shape[0], n_out_2, B.shape[1]), A.dtype)
+        self.raw("sasaw", "", A.dtype, O, A, B, C, W, M1, Jw, M2, Io, M3)
+        return O
+
+    def sasaw_vjp(self, gO, A, B, C, W, M1, Jw, M2, Io, M3, need=(True, True, True)):
+        gO, A, B, C, W = _c(gO), _c(A), _c(B), _c(C), _c(W)
+        M1, Jw, M2, Io, M3 = _i32(M1), _i32(Jw), _i32(M2), _i32(Io), _i32(M3)
+        gA = np.empty_like(A) if need[0] else None
+        gB = np.empty_like(B) if need[1] else None
+        gW = np.empty_like(W) if need[2] else None
+        self.raw("sasaw", "_vjp", A.dtype, gA if need[0] else Null(2, A.dtype),
+                 gB if need[1] else Null(2, A.dtype), gW if need[2] else Null(3, A.dtype),
+                 gO, A, B, C, W, M1, Jw, M2, Io, M3)
+        return gA, gB, gW
+
+
+def have_reference():
+    return os.path.exists(REFERENCE_SO)
