@@ -1,0 +1,194 @@
+/* C ABI of the B200 build of the mops sparse operations.
+ *
+ * Binary-compatible with the C ABI of lab-cosmo/mops: the same 60 entry points plus the
+ * error getter, the same by-value tensor structs, the same argument order and the same
+ * status convention. A program or binding written against the reference's `mops.h`
+ * (ctypes in python/mops/src/mops/_c_api.py:60-872, any C caller) can load this library
+ * instead of the reference's `libmops.so` without being rebuilt.
+ *
+ * Interfaces replaced, by file in the reference tree:
+ *   tensor structs                         mops/include/mops/tensor.h:11-49
+ *   mops_get_last_error_message            mops/include/mops.h:16, mops/src/capi.cpp:4-12
+ *   homogeneous_polynomial_evaluation      mops/include/mops/hpe.h:12-125
+ *   sparse_accumulation_of_products        mops/include/mops/sap.h:12-169
+ *   outer_product_scatter_add              mops/include/mops/opsa.h:12-133
+ *   outer_product_scatter_add_with_weights mops/include/mops/opsaw.h:12-170
+ *   sparse_accumulation_scatter_add_with_weights   mops/include/mops/sasaw.h:12-226
+ *
+ * Every operation <op> exists as
+ *     int mops_<op>_{f32,f64}(...)        host pointers  -- NOT implemented in this build:
+ *                                         returns 1 with an explanatory message
+ *     int mops_cuda_<op>_{f32,f64}(...)   device pointers -- the sm_100a kernels
+ * for <op> itself, <op>_vjp and <op>_vjp_vjp.
+ *
+ * Conventions (as in the reference):
+ *   - tensors are passed by value as {data, shape[N]}; data is contiguous, row-major;
+ *     index tensors are int32 and zero-based; mops_cuda_* take device pointers of the
+ *     current CUDA device;
+ *   - the caller allocates every output; outputs are fully overwritten;
+ *   - a gradient output with data == NULL is skipped;
+ *   - return 0 on success, 1 on error (message stored per thread), 2 on unknown error;
+ *   - mops_cuda_* return when the results are complete.
+ * Differences from the reference CUDA path, all on the safe side: index arrays are
+ * range-checked on the device and reported (status 1) instead of being trusted; scatter
+ * indices (indices_output, indices_output_1) need not be sorted, sorted input is merely the
+ * fast path; CUDA errors are reported through the status instead of terminating the process.
+ */
+#ifndef MOPS_H
+#define MOPS_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define MOPS_EXPORT __attribute__((visibility("default")))
+#else
+#define MOPS_EXPORT
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__cplusplus) || defined(__GNUC__)
+#define MOPS_RESTRICT __restrict__
+#else
+#define MOPS_RESTRICT restrict
+#endif
+
+#define MOPS_TENSOR_STRUCT(name, type, ndim)                                                       \
+    struct name {                                                                                  \
+        type* MOPS_RESTRICT data;                                                                  \
+        int64_t shape[ndim];                                                                       \
+    };                                                                                             \
+    typedef struct name name
+
+MOPS_TENSOR_STRUCT(mops_tensor_1d_f32_t, float, 1);
+MOPS_TENSOR_STRUCT(mops_tensor_2d_f32_t, float, 2);
+MOPS_TENSOR_STRUCT(mops_tensor_3d_f32_t, float, 3);
+MOPS_TENSOR_STRUCT(mops_tensor_1d_f64_t, double, 1);
+MOPS_TENSOR_STRUCT(mops_tensor_2d_f64_t, double, 2);
+MOPS_TENSOR_STRUCT(mops_tensor_3d_f64_t, double, 3);
+MOPS_TENSOR_STRUCT(mops_tensor_1d_i32_t, int32_t, 1);
+MOPS_TENSOR_STRUCT(mops_tensor_2d_i32_t, int32_t, 2);
+
+/* Parameter lists, S = f32 or f64. Outputs first, then grad_output, inputs, indices. */
+#define MOPS_V1(S) mops_tensor_1d_##S##_t
+#define MOPS_V2(S) mops_tensor_2d_##S##_t
+#define MOPS_V3(S) mops_tensor_3d_##S##_t
+#define MOPS_I1 mops_tensor_1d_i32_t
+#define MOPS_I2 mops_tensor_2d_i32_t
+
+/* O[i] = sum_j C[j] prod_k A[i, indices_A[j,k]] */
+#define MOPS_ARGS_HPE(S) MOPS_V1(S) output, MOPS_V2(S) A, MOPS_V1(S) C, MOPS_I2 indices_A
+#define MOPS_ARGS_HPE_VJP(S)                                                                       \
+    MOPS_V2(S) grad_A, MOPS_V1(S) grad_output, MOPS_V2(S) A, MOPS_V1(S) C, MOPS_I2 indices_A
+#define MOPS_ARGS_HPE_VJP_VJP(S)                                                                   \
+    MOPS_V1(S) grad_grad_output, MOPS_V2(S) grad_A_2, MOPS_V2(S) grad_grad_A,                      \
+        MOPS_V1(S) grad_output, MOPS_V2(S) A, MOPS_V1(S) C, MOPS_I2 indices_A
+
+/* O[i, indices_output[k]] += C[k] A[i, indices_A[k]] B[i, indices_B[k]] */
+#define MOPS_ARGS_SAP(S)                                                                           \
+    MOPS_V2(S) output, MOPS_V2(S) A, MOPS_V2(S) B, MOPS_V1(S) C, MOPS_I1 indices_A,                \
+        MOPS_I1 indices_B, MOPS_I1 indices_output
+#define MOPS_ARGS_SAP_VJP(S)                                                                       \
+    MOPS_V2(S) grad_A, MOPS_V2(S) grad_B, MOPS_V2(S) grad_output, MOPS_V2(S) A, MOPS_V2(S) B,      \
+        MOPS_V1(S) C, MOPS_I1 indices_A, MOPS_I1 indices_B, MOPS_I1 indices_output
+#define MOPS_ARGS_SAP_VJP_VJP(S)                                                                   \
+    MOPS_V2(S) grad_grad_output, MOPS_V2(S) grad_A_2, MOPS_V2(S) grad_B_2,                         \
+        MOPS_V2(S) grad_grad_A, MOPS_V2(S) grad_grad_B, MOPS_V2(S) grad_output, MOPS_V2(S) A,      \
+        MOPS_V2(S) B, MOPS_V1(S) C, MOPS_I1 indices_A, MOPS_I1 indices_B, MOPS_I1 indices_output
+
+/* O[indices_output[j], k, l] += A[j,k] B[j,l] */
+#define MOPS_ARGS_OPSA(S) MOPS_V3(S) output, MOPS_V2(S) A, MOPS_V2(S) B, MOPS_I1 indices_output
+#define MOPS_ARGS_OPSA_VJP(S)                                                                      \
+    MOPS_V2(S) grad_A, MOPS_V2(S) grad_B, MOPS_V3(S) grad_output, MOPS_V2(S) A, MOPS_V2(S) B,      \
+        MOPS_I1 indices_output
+#define MOPS_ARGS_OPSA_VJP_VJP(S)                                                                  \
+    MOPS_V3(S) grad_grad_output, MOPS_V2(S) grad_A_2, MOPS_V2(S) grad_B_2,                         \
+        MOPS_V2(S) grad_grad_A, MOPS_V2(S) grad_grad_B, MOPS_V3(S) grad_output, MOPS_V2(S) A,      \
+        MOPS_V2(S) B, MOPS_I1 indices_output
+
+/* O[indices_output[e], k, l] += A[e,k] B[e,l] W[indices_W[e], l] */
+#define MOPS_ARGS_OPSAW(S)                                                                         \
+    MOPS_V3(S) output, MOPS_V2(S) A, MOPS_V2(S) B, MOPS_V2(S) W, MOPS_I1 indices_W,                \
+        MOPS_I1 indices_output
+#define MOPS_ARGS_OPSAW_VJP(S)                                                                     \
+    MOPS_V2(S) grad_A, MOPS_V2(S) grad_B, MOPS_V2(S) grad_W, MOPS_V3(S) grad_output,               \
+        MOPS_V2(S) A, MOPS_V2(S) B, MOPS_V2(S) W, MOPS_I1 indices_W, MOPS_I1 indices_output
+#define MOPS_ARGS_OPSAW_VJP_VJP(S)                                                                 \
+    MOPS_V3(S) grad_grad_output, MOPS_V2(S) grad_A_2, MOPS_V2(S) grad_B_2, MOPS_V2(S) grad_W_2,    \
+        MOPS_V2(S) grad_grad_A, MOPS_V2(S) grad_grad_B, MOPS_V2(S) grad_grad_W,                    \
+        MOPS_V3(S) grad_output, MOPS_V2(S) A, MOPS_V2(S) B, MOPS_V2(S) W, MOPS_I1 indices_W,       \
+        MOPS_I1 indices_output
+
+/* O[indices_output_1[e], indices_output_2[n], :] +=
+ *     C[n] A[e, indices_A[n]] B[e, :] W[indices_W_1[e], indices_W_2[n], :] */
+#define MOPS_ARGS_SASAW(S)                                                                         \
+    MOPS_V3(S) output, MOPS_V2(S) A, MOPS_V2(S) B, MOPS_V1(S) C, MOPS_V3(S) W,                     \
+        MOPS_I1 indices_A, MOPS_I1 indices_W_1, MOPS_I1 indices_W_2, MOPS_I1 indices_output_1,     \
+        MOPS_I1 indices_output_2
+#define MOPS_ARGS_SASAW_VJP(S)                                                                     \
+    MOPS_V2(S) grad_A, MOPS_V2(S) grad_B, MOPS_V3(S) grad_W, MOPS_V3(S) grad_output,               \
+        MOPS_V2(S) A, MOPS_V2(S) B, MOPS_V1(S) C, MOPS_V3(S) W, MOPS_I1 indices_A,                 \
+        MOPS_I1 indices_W_1, MOPS_I1 indices_W_2, MOPS_I1 indices_output_1,                        \
+        MOPS_I1 indices_output_2
+/* grad_grad_W is declared 2-D in the reference's C header (sasaw.h:84); kept as is. */
+#define MOPS_ARGS_SASAW_VJP_VJP(S)                                                                 \
+    MOPS_V3(S) grad_grad_output, MOPS_V2(S) grad_A_2, MOPS_V2(S) grad_B_2, MOPS_V3(S) grad_W_2,    \
+        MOPS_V2(S) grad_grad_A, MOPS_V2(S) grad_grad_B, MOPS_V2(S) grad_grad_W,                    \
+        MOPS_V3(S) grad_output, MOPS_V2(S) A, MOPS_V2(S) B, MOPS_V1(S) C, MOPS_V3(S) W,            \
+        MOPS_I1 indices_A, MOPS_I1 indices_W_1, MOPS_I1 indices_W_2, MOPS_I1 indices_output_1,     \
+        MOPS_I1 indices_output_2
+
+/* Four entry points per (operation, level): host/device x f32/f64. */
+#define MOPS_DECLARE(name, ARGS)                                                                   \
+    MOPS_EXPORT int mops_##name##_f32(ARGS(f32));                                                  \
+    MOPS_EXPORT int mops_##name##_f64(ARGS(f64));                                                  \
+    MOPS_EXPORT int mops_cuda_##name##_f32(ARGS(f32));                                             \
+    MOPS_EXPORT int mops_cuda_##name##_f64(ARGS(f64));
+
+#define MOPS_FOR_EACH_ENTRY(X)                                                                     \
+    X(homogeneous_polynomial_evaluation, MOPS_ARGS_HPE)                                            \
+    X(homogeneous_polynomial_evaluation_vjp, MOPS_ARGS_HPE_VJP)                                    \
+    X(homogeneous_polynomial_evaluation_vjp_vjp, MOPS_ARGS_HPE_VJP_VJP)                            \
+    X(sparse_accumulation_of_products, MOPS_ARGS_SAP)                                              \
+    X(sparse_accumulation_of_products_vjp, MOPS_ARGS_SAP_VJP)                                      \
+    X(sparse_accumulation_of_products_vjp_vjp, MOPS_ARGS_SAP_VJP_VJP)                              \
+    X(outer_product_scatter_add, MOPS_ARGS_OPSA)                                                   \
+    X(outer_product_scatter_add_vjp, MOPS_ARGS_OPSA_VJP)                                           \
+    X(outer_product_scatter_add_vjp_vjp, MOPS_ARGS_OPSA_VJP_VJP)                                   \
+    X(outer_product_scatter_add_with_weights, MOPS_ARGS_OPSAW)                                     \
+    X(outer_product_scatter_add_with_weights_vjp, MOPS_ARGS_OPSAW_VJP)                             \
+    X(outer_product_scatter_add_with_weights_vjp_vjp, MOPS_ARGS_OPSAW_VJP_VJP)                     \
+    X(sparse_accumulation_scatter_add_with_weights, MOPS_ARGS_SASAW)                               \
+    X(sparse_accumulation_scatter_add_with_weights_vjp, MOPS_ARGS_SASAW_VJP)                       \
+    X(sparse_accumulation_scatter_add_with_weights_vjp_vjp, MOPS_ARGS_SASAW_VJP_VJP)
+
+MOPS_FOR_EACH_ENTRY(MOPS_DECLARE)
+
+/* Message of the last error on the calling thread; valid until that thread's next failing
+ * call. (mops/include/mops.h:16) */
+MOPS_EXPORT const char* mops_get_last_error_message(void);
+
+/* ---- Extensions of this build (no counterpart in the reference ABI) ------------------- */
+
+/* CUDA stream (a cudaStream_t) on which the calling thread's mops_cuda_* calls run.
+ * NULL selects the legacy default stream, which is what the reference uses. */
+MOPS_EXPORT void mops_b200_set_stream(void* stream);
+MOPS_EXPORT void* mops_b200_get_stream(void);
+
+/* wait != 0 (default): mops_cuda_* return when results are complete, as in the reference.
+ * wait == 0: they return after enqueueing on the stream; index errors found by the kernels
+ * are then not reported by that call. Per thread. */
+MOPS_EXPORT void mops_b200_set_wait(int wait);
+MOPS_EXPORT int mops_b200_get_wait(void);
+
+/* Version string of this build. */
+MOPS_EXPORT const char* mops_b200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif

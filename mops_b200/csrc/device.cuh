@@ -1,0 +1,127 @@
+// Device-side helpers shared by the kernels: status reporting, the segment search over a
+// sorted scatter index, the sortedness check, and reductions.
+//
+// Replaces mops/src/internal/cuda_utils.{cuh,cu} (atomic add with a pre-sm_60 fallback, the
+// shared-memory bump allocator) and mops/src/internal/cuda_first_occurences.cu (a separate
+// memset + kernel + device synchronisation that writes a first/last-occurrence table into a
+// cached global buffer before every scatter op). Here each warp finds the bounds of its own
+// output row with a 32-way search over the sorted index, so there is no table, no extra
+// launch and no synchronisation.
+#ifndef MOPS_B200_DEVICE_CUH
+#define MOPS_B200_DEVICE_CUH
+
+#include <cstdint>
+
+#include "runtime.hpp"
+
+namespace mops_b200 {
+
+constexpr unsigned kFullMask = 0xffffffffu;
+
+__device__ __forceinline__ void report_unsorted(const Status& st) {
+    st.dev[kUnsortedEpoch] = st.epoch;
+    st.host[kUnsortedEpoch] = st.epoch;
+    __threadfence_system();
+}
+
+__device__ __forceinline__ void report_bad_index(const Status& st, int which) {
+    st.dev[kBadIndex0 + which] = st.epoch;
+    st.host[kBadIndex0 + which] = st.epoch;
+    __threadfence_system();
+}
+
+__device__ __forceinline__ bool saw_unsorted(const Status& st) {
+    return *reinterpret_cast<volatile uint32_t*>(st.dev + kUnsortedEpoch) == st.epoch;
+}
+
+// Clamp an index read from a user array into [0, n) so that a bad value can never address
+// memory outside the operand; returns whether it had to.
+__device__ __forceinline__ bool clamp_index(int32_t& v, int32_t n) {
+    bool bad = static_cast<uint32_t>(v) >= static_cast<uint32_t>(n);
+    if (bad) v = 0;
+    return bad;
+}
+
+// First position in the ascending array P[lo, hi) whose value is >= r, found by the whole
+// warp: every round the 32 lanes probe 32 evenly spaced positions and one ballot narrows
+// the range 32-fold (five rounds for 2^24 entries, each a single coalescable load per lane).
+// All lanes must call it with the same arguments; all get the result. On an unsorted array
+// the result is some position in [lo, hi]; callers detect that case separately.
+__device__ __forceinline__ int64_t warp_lower_bound(const int32_t* __restrict__ P, int64_t lo,
+                                                    int64_t hi, int32_t r, int lane) {
+    while (hi > lo) {
+        int64_t n = hi - lo;
+        int64_t chunk = (n + 31) / 32; // >= 1
+        int64_t probe = lo + (lane + 1) * chunk - 1;
+        bool below = (probe < hi) && (__ldg(P + probe) < r);
+        int c = __popc(__ballot_sync(kFullMask, below));
+        int64_t new_lo = lo + c * chunk;
+        if (new_lo >= hi) {
+            lo = hi;
+            break;
+        }
+        // The answer is in [new_lo, new_lo + chunk - 1]: position new_lo + chunk - 1 was
+        // probed and is >= r (or lies at/after hi).
+        int64_t new_hi = new_lo + chunk - 1;
+        if (new_hi > hi) new_hi = hi;
+        lo = new_lo;
+        hi = new_hi;
+    }
+    return lo;
+}
+
+// Bounds [begin, end) of the entries whose (sorted) index equals r.
+__device__ __forceinline__ void warp_segment(const int32_t* __restrict__ P, int64_t J, int32_t r,
+                                             int lane, int64_t& begin, int64_t& end) {
+    begin = warp_lower_bound(P, 0, J, r, lane);
+    // Segments are short in practice: look in a window after `begin` first.
+    int64_t stop = begin + 1024 < J ? begin + 1024 : J;
+    end = warp_lower_bound(P, begin, stop, r + 1, lane);
+    if (end == stop && stop < J) end = warp_lower_bound(P, stop, J, r + 1, lane);
+}
+
+// Every warp of a grid checks one slice of the scatter index for ascending order and for
+// range; together the slices cover all adjacent pairs, so "no report" proves the index is
+// sorted and inside [0, n_rows). `part` in [0, n_parts).
+__device__ __forceinline__ void check_sorted_slice(const int32_t* __restrict__ P, int64_t J,
+                                                   int64_t n_rows, int64_t part, int64_t n_parts,
+                                                   int lane, const Status& st) {
+    if (J == 0) return;
+    int64_t per = (J + n_parts - 1) / n_parts;
+    int64_t a = part * per;
+    int64_t b = a + per < J ? a + per : J;
+    bool unsorted = false, bad = false;
+    for (int64_t j = a + lane; j < b; j += 32) {
+        int32_t v = __ldg(P + j);
+        int32_t next = (j + 1 < J) ? __ldg(P + j + 1) : v;
+        unsorted |= next < v;
+        bad |= (v < 0) || (static_cast<int64_t>(v) >= n_rows);
+    }
+    if (__any_sync(kFullMask, unsorted) && lane == 0) report_unsorted(st);
+    // Bit 0 is the scatter index of every scatter op.
+    if (__any_sync(kFullMask, bad) && lane == 0) report_bad_index(st, 0);
+}
+
+template <typename T> __device__ __forceinline__ T warp_sum(T v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(kFullMask, v, o);
+    return v;
+}
+
+// Fire-and-forget global accumulation (compiles to RED: no value comes back).
+template <typename T> __device__ __forceinline__ void red_add(T* addr, T v) { atomicAdd(addr, v); }
+
+// Unsorted index: runs only when the segmented kernel of the same call reported it.
+template <typename T>
+__global__ void zero_if_unsorted(T* __restrict__ out, int64_t n, Status st) {
+    if (!saw_unsorted(st)) return;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+        out[i] = T(0);
+}
+
+__host__ __device__ constexpr int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+} // namespace mops_b200
+
+#endif

@@ -1,0 +1,124 @@
+#include <mutex>
+#include <unordered_map>
+
+#include "runtime.hpp"
+
+namespace mops_b200 {
+
+[[noreturn]] void throw_cuda(cudaError_t err, const char* what, const char* file, int line) {
+    // Clear the (non-sticky) error so that the next call starts clean.
+    (void)cudaGetLastError();
+    throw std::runtime_error(
+        std::string("CUDA error: ") + cudaGetErrorString(err) + " in `" + what + "` at " + file +
+        ":" + std::to_string(line));
+}
+
+namespace {
+
+struct ThreadState {
+    cudaStream_t stream = nullptr;
+    bool wait = true;
+    uint32_t epoch = 0;
+    // One status block per device this thread has used. The blocks are a few bytes and live
+    // until the process exits.
+    std::unordered_map<int, Status> blocks;
+};
+
+thread_local ThreadState g_thread;
+
+struct DeviceInfo {
+    int sms = 0;
+    int smem = 0;
+};
+std::mutex g_info_mutex;
+std::unordered_map<int, DeviceInfo> g_info;
+
+const DeviceInfo& device_info(int device) {
+    std::lock_guard<std::mutex> lock(g_info_mutex);
+    auto it = g_info.find(device);
+    if (it == g_info.end()) {
+        DeviceInfo info;
+        MOPS_CUDA_OK(cudaDeviceGetAttribute(&info.sms, cudaDevAttrMultiProcessorCount, device));
+        MOPS_CUDA_OK(
+            cudaDeviceGetAttribute(&info.smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
+        it = g_info.emplace(device, info).first;
+    }
+    return it->second;
+}
+
+} // namespace
+
+int sm_count(int device) { return device_info(device).sms; }
+int max_optin_smem(int device) { return device_info(device).smem; }
+
+void set_stream(void* stream) { g_thread.stream = static_cast<cudaStream_t>(stream); }
+void* get_stream() { return g_thread.stream; }
+void set_wait(bool wait) { g_thread.wait = wait; }
+bool get_wait() { return g_thread.wait; }
+
+Call begin_call() {
+    Call call;
+    MOPS_CUDA_OK(cudaGetDevice(&call.device));
+    call.stream = g_thread.stream;
+    call.wait = g_thread.wait;
+
+    auto it = g_thread.blocks.find(call.device);
+    if (it == g_thread.blocks.end()) {
+        Status block{};
+        void* host = nullptr;
+        MOPS_CUDA_OK(cudaHostAlloc(&host, kStatusWords * sizeof(uint32_t),
+                                   cudaHostAllocMapped | cudaHostAllocPortable));
+        for (int i = 0; i < kStatusWords; i++) static_cast<volatile uint32_t*>(host)[i] = 0;
+        void* host_dev = nullptr;
+        MOPS_CUDA_OK(cudaHostGetDevicePointer(&host_dev, host, 0));
+        (void)host_dev; // with unified addressing the host pointer is the device-visible one
+        block.host = static_cast<uint32_t*>(host);
+        MOPS_CUDA_OK(cudaMalloc(reinterpret_cast<void**>(&block.dev),
+                                kStatusWords * sizeof(uint32_t)));
+        MOPS_CUDA_OK(cudaMemset(block.dev, 0, kStatusWords * sizeof(uint32_t)));
+        it = g_thread.blocks.emplace(call.device, block).first;
+    }
+    call.status = it->second;
+    g_thread.epoch += 1;
+    if (g_thread.epoch == 0) g_thread.epoch = 1;
+    call.status.epoch = g_thread.epoch;
+    return call;
+}
+
+void wait_stream(const Call& call) { MOPS_CUDA_OK(cudaStreamSynchronize(call.stream)); }
+
+bool host_saw_unsorted(const Call& call) {
+    return static_cast<volatile uint32_t*>(call.status.host)[kUnsortedEpoch] == call.status.epoch;
+}
+
+void end_call(const Call& call, const char* operation, const char* const* index_names,
+              int n_index_names) {
+    MOPS_CUDA_OK(cudaGetLastError());
+    if (!call.wait) return;
+    MOPS_CUDA_OK(cudaStreamSynchronize(call.stream));
+    volatile uint32_t* host = call.status.host;
+    std::string names;
+    for (int i = 0; i < n_index_names && i < kMaxIndexArrays; i++) {
+        if (host[kBadIndex0 + i] == call.status.epoch) {
+            if (!names.empty()) names += ", ";
+            names += index_names[i];
+        }
+    }
+    if (!names.empty()) {
+        throw std::runtime_error(
+            "Index array " + names + " in operation " + operation +
+            " contains negative or too large elements; this would cause out-of-bounds accesses");
+    }
+}
+
+void* scratch_alloc(const Call& call, size_t bytes) {
+    void* ptr = nullptr;
+    MOPS_CUDA_OK(cudaMallocAsync(&ptr, bytes, call.stream));
+    return ptr;
+}
+
+void scratch_free(const Call& call, void* ptr) {
+    if (ptr != nullptr) MOPS_CUDA_OK(cudaFreeAsync(ptr, call.stream));
+}
+
+} // namespace mops_b200

@@ -1,0 +1,87 @@
+// Host-side execution context shared by the five operations: which stream a call runs on,
+// whether it returns only when the results are complete, and the small status block through
+// which kernels report what they found in the index arrays.
+//
+// Replaces the reference's CUDA_CHECK_ERROR, which prints and calls exit()
+// (mops/src/internal/cuda_utils.cuh:11-24): here every CUDA failure becomes a
+// std::runtime_error, which the C API turns into status 1 and a stored message.
+#ifndef MOPS_B200_RUNTIME_HPP
+#define MOPS_B200_RUNTIME_HPP
+
+#include <cstdint>
+#include <stdexcept>
+#include <string>
+
+#include <cuda_runtime.h>
+
+#include "mops.hpp"
+
+namespace mops_b200 {
+
+// Words of the status block. Kernels write the device copy (read by later kernels of the
+// same call) and the host-mapped copy (read by the host after the stream has drained).
+// Every word holds the epoch (call number) of the last call that raised it; plain stores,
+// no atomics, so the host-mapped copy needs nothing special from the interconnect.
+enum StatusWord : int {
+    kUnsortedEpoch = 0, // a scatter index was not in ascending order
+    kBadIndex0 = 1,     // words 1..7: index array 0..6 of the op held an out-of-range value
+    kMaxIndexArrays = 7,
+    kStatusWords = 8
+};
+
+struct Status {
+    uint32_t* dev;  // device memory
+    uint32_t* host; // host-mapped pinned memory, same layout (device-visible address)
+    uint32_t epoch; // identifies this call; never 0
+};
+
+struct Call {
+    cudaStream_t stream;
+    bool wait; // true: results complete when the entry point returns
+    Status status;
+    int device;
+};
+
+[[noreturn]] void throw_cuda(cudaError_t err, const char* what, const char* file, int line);
+
+#define MOPS_CUDA_OK(expr)                                                                         \
+    do {                                                                                           \
+        cudaError_t mops_err__ = (expr);                                                           \
+        if (mops_err__ != cudaSuccess)                                                             \
+            ::mops_b200::throw_cuda(mops_err__, #expr, __FILE__, __LINE__);                        \
+    } while (0)
+
+// Starts a call on the calling thread's stream (default: the legacy default stream, like the
+// reference) for the current device; allocates that thread's status block on first use.
+Call begin_call();
+
+// True when the call found its scatter index unsorted (host view; only meaningful after the
+// stream has been synchronised).
+bool host_saw_unsorted(const Call& call);
+
+// Ends a call: checks the launch status, waits when `call.wait`, then turns index errors
+// reported by the kernels into exceptions. `index_names` lists the op's index arrays in the
+// bit order the kernels use.
+void end_call(const Call& call, const char* operation, const char* const* index_names,
+              int n_index_names);
+
+// Waits for the stream of `call` (used between the main and the fallback kernels when the
+// call is synchronous anyway).
+void wait_stream(const Call& call);
+
+// Per-thread settings (extensions to the reference API, which has no stream argument).
+void set_stream(void* stream); // cudaStream_t; nullptr = legacy default stream
+void* get_stream();
+void set_wait(bool wait); // false: entry points return after enqueueing (used by the torch ops)
+bool get_wait();
+
+// Scratch memory for one call, ordered on the call's stream.
+void* scratch_alloc(const Call& call, size_t bytes);
+void scratch_free(const Call& call, void* ptr);
+
+int sm_count(int device);
+int max_optin_smem(int device);
+
+} // namespace mops_b200
+
+#endif

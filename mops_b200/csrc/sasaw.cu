@@ -1,0 +1,646 @@
+// Sparse accumulation scatter-add with weights: forward and VJP, f32 and f64, for sm_100a.
+//
+//   O[I[e], M3[n], b] += C[n] A[e,M1[n]] B[e,b] W[J[e], M2[n], b]          (sasaw.hpp:10-52)
+//   gA[e,M1[n]]       += C[n] sum_b gO[I[e],M3[n],b] B[e,b] W[J[e],M2[n],b]
+//   gB[e,b]           += sum_n C[n] A[e,M1[n]] gO[I[e],M3[n],b] W[J[e],M2[n],b]
+//   gW[J[e],M2[n],b]  += C[n] A[e,M1[n]] B[e,b] gO[I[e],M3[n],b]
+// (I = indices_output_1, J = indices_W_1, M1 = indices_A, M2 = indices_W_2,
+//  M3 = indices_output_2.)
+//
+// The reference has no CUDA implementation of this operation: its entry points throw
+// (mops/src/sasaw/cuda.tpp:5-61). The CPU code (mops/src/sasaw/cpu.tpp:8-171) walks all N
+// coupling entries for every edge and every b.
+//
+// These kernels first contract the coupling table with the edge's A row:
+//     T_e[m3,m2] = sum_{n : M3[n]=m3, M2[n]=m2} C[n] A[e,M1[n]]
+// which does not depend on b, and then use the small dense T_e:
+//     O[I_e,m3,b]  += B[e,b] sum_m2 T_e[m3,m2] W[J_e,m2,b]
+//     gB[e,b]       = sum_m2 W[J_e,m2,b] sum_m3 T_e[m3,m2] gO[I_e,m3,b]
+//     gW[J_e,m2,b] += B[e,b] sum_m3 T_e[m3,m2] gO[I_e,m3,b]
+//     gA[e,M1[n]]  += C[n] U_e[M3[n],M2[n]],  U_e[m3,m2] = sum_b gO[I_e,m3,b] B[e,b] W[J_e,m2,b]
+// For 500 coupling entries on a 9x9 grid of cells this is about seven times fewer
+// multiply-adds than the direct form. A one-block kernel groups the coupling entries by cell
+// once per call (counting sort, entries of a cell kept in ascending n so the sums are
+// reproducible); the grouped table is call-scoped scratch memory.
+//
+// Forward: segmented reduction, one warp per output row (lane = b), accumulators for the row
+// in shared memory, one plain store per output row; atomic fallback when the scatter index
+// is not sorted. VJP: one warp per edge (lane = b), independent of the index order; gW is
+// accumulated with RED because indices_W_1 is not sorted.
+#include <algorithm>
+
+#include "checks.hpp"
+#include "device.cuh"
+
+namespace mops_b200 {
+namespace {
+
+// Index arrays in status-bit order.
+const char* const kIndexNames[] = {"indices_output_1", "indices_A", "indices_W_1", "indices_W_2",
+                                   "indices_output_2"};
+enum { kBitI = 0, kBitM1 = 1, kBitJ = 2, kBitM2 = 3, kBitM3 = 4 };
+
+// Coupling entries grouped by cell (m3 * nW1 + m2), in global scratch memory.
+template <typename T> struct Coupling {
+    T* C;           // [N]  coefficients in grouped order
+    int32_t* M1;    // [N]  A column of each grouped entry
+    int32_t* cell;  // [N]  cell of each grouped entry
+    int32_t* start; // [ncell + 1]  first grouped position of each cell
+    int32_t* order; // [N]  scratch for the sort
+    int N, ncell;
+};
+
+constexpr int kBuildThreads = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(kBuildThreads)
+sasaw_group_coupling(Coupling<T> cp, const T* __restrict__ C, const int32_t* __restrict__ M1,
+                     const int32_t* __restrict__ M2, const int32_t* __restrict__ M3, int nA,
+                     int nW1, int nO1, Status st) {
+    extern __shared__ int32_t cursor[]; // [ncell]
+    __shared__ int32_t chunk_sum[kBuildThreads];
+    const int tid = threadIdx.x, N = cp.N, ncell = cp.ncell;
+
+    for (int c = tid; c < ncell; c += kBuildThreads) cursor[c] = 0;
+    __syncthreads();
+    for (int n = tid; n < N; n += kBuildThreads) {
+        int32_t m1 = M1[n], m2 = M2[n], m3 = M3[n];
+        if (clamp_index(m1, nA)) report_bad_index(st, kBitM1);
+        if (clamp_index(m2, nW1)) report_bad_index(st, kBitM2);
+        if (clamp_index(m3, nO1)) report_bad_index(st, kBitM3);
+        atomicAdd(&cursor[m3 * nW1 + m2], 1);
+    }
+    __syncthreads();
+    // Exclusive scan of the per-cell counts: each thread scans a contiguous chunk.
+    const int per = (ncell + kBuildThreads - 1) / kBuildThreads;
+    const int c_lo = min(tid * per, ncell), c_hi = min(c_lo + per, ncell);
+    int local = 0;
+    for (int c = c_lo; c < c_hi; c++) local += cursor[c];
+    chunk_sum[tid] = local;
+    __syncthreads();
+    if (tid == 0) {
+        int run = 0;
+        for (int t = 0; t < kBuildThreads; t++) {
+            const int v = chunk_sum[t];
+            chunk_sum[t] = run;
+            run += v;
+        }
+    }
+    __syncthreads();
+    int run = chunk_sum[tid];
+    for (int c = c_lo; c < c_hi; c++) {
+        const int v = cursor[c];
+        cp.start[c] = run;
+        cursor[c] = run;
+        run += v;
+    }
+    if (tid == 0) cp.start[ncell] = N;
+    __syncthreads();
+    for (int n = tid; n < N; n += kBuildThreads) {
+        int32_t m2 = M2[n], m3 = M3[n];
+        clamp_index(m2, nW1);
+        clamp_index(m3, nO1);
+        cp.order[atomicAdd(&cursor[m3 * nW1 + m2], 1)] = n;
+    }
+    __syncthreads();
+    // Entries of one cell in ascending n (they were placed in arbitrary order).
+    for (int c = tid; c < ncell; c += kBuildThreads) {
+        const int lo = cp.start[c], hi = cursor[c];
+        for (int i = lo + 1; i < hi; i++) {
+            const int32_t v = cp.order[i];
+            int j = i - 1;
+            while (j >= lo && cp.order[j] > v) {
+                cp.order[j + 1] = cp.order[j];
+                j--;
+            }
+            cp.order[j + 1] = v;
+        }
+        for (int i = lo; i < hi; i++) cp.cell[i] = c;
+    }
+    __syncthreads();
+    for (int pos = tid; pos < N; pos += kBuildThreads) {
+        const int32_t n = cp.order[pos];
+        int32_t m1 = M1[n];
+        clamp_index(m1, nA);
+        cp.C[pos] = C[n];
+        cp.M1[pos] = m1;
+    }
+}
+
+// Shared-memory carve-up common to the forward and VJP kernels.
+template <typename T> struct Shared {
+    T* C;           // [N]
+    T* warp_base;   // per-warp scalars start here
+    int32_t* M1;    // [N]
+    int32_t* cell;  // [N] (VJP only)
+    int32_t* start; // [ncell + 1]
+};
+
+template <typename T>
+__device__ __forceinline__ Shared<T> carve(unsigned char* raw, const Coupling<T>& cp,
+                                           size_t per_warp_scalars, int warps, bool with_cell) {
+    Shared<T> s;
+    s.C = reinterpret_cast<T*>(raw);
+    s.warp_base = s.C + cp.N;
+    T* end = s.warp_base + per_warp_scalars * warps;
+    s.M1 = reinterpret_cast<int32_t*>(end);
+    s.cell = s.M1 + cp.N;
+    s.start = with_cell ? s.cell + cp.N : s.cell;
+    return s;
+}
+
+template <typename T>
+__device__ __forceinline__ void load_coupling(const Shared<T>& s, const Coupling<T>& cp,
+                                              bool with_cell) {
+    for (int i = threadIdx.x; i < cp.N; i += blockDim.x) {
+        s.C[i] = cp.C[i];
+        s.M1[i] = cp.M1[i];
+        if (with_cell) s.cell[i] = cp.cell[i];
+    }
+    for (int i = threadIdx.x; i <= cp.ncell; i += blockDim.x) s.start[i] = cp.start[i];
+}
+
+// T_e[cell] for one edge; a_s and T_s are this warp's buffers.
+template <typename T>
+__device__ __forceinline__ void contract_coupling(const Shared<T>& s, int ncell,
+                                                  const T* __restrict__ a_row, int nA, T* a_s,
+                                                  T* T_s, int lane) {
+    __syncwarp();
+    for (int m = lane; m < nA; m += 32) a_s[m] = a_row[m];
+    __syncwarp();
+    for (int c = lane; c < ncell; c += 32) {
+        T t = T(0);
+        for (int pos = s.start[c]; pos < s.start[c + 1]; pos++) t += s.C[pos] * a_s[s.M1[pos]];
+        T_s[c] = t;
+    }
+    __syncwarp();
+}
+
+template <typename T, bool SEGMENTED>
+__global__ void sasaw_fwd(T* __restrict__ O, const T* __restrict__ A, const T* __restrict__ B,
+                          const T* __restrict__ W, const int32_t* __restrict__ Jw,
+                          const int32_t* __restrict__ Io, Coupling<T> cp, int64_t E, int nA, int L,
+                          int64_t nW0, int nW1, int nO1, bool always, Status st) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int ncell = cp.ncell;
+    const size_t per_warp = static_cast<size_t>(nA) + ncell + (SEGMENTED ? static_cast<size_t>(nO1) * L : 0);
+    if (!SEGMENTED && !always && !saw_unsorted(st)) return;
+    Shared<T> s = carve<T>(smem_raw, cp, per_warp, warps, false);
+    load_coupling(s, cp, false);
+    __syncthreads();
+    T* a_s = s.warp_base + per_warp * warp;
+    T* T_s = a_s + nA;
+    T* Oacc = T_s + ncell;
+    const int64_t rowsize = static_cast<int64_t>(nO1) * L;
+
+    auto edge = [&](int64_t e, int64_t out_row) {
+        int32_t j = __ldg(Jw + e);
+        if (clamp_index(j, static_cast<int32_t>(nW0)) && lane == 0) report_bad_index(st, kBitJ);
+        contract_coupling(s, ncell, A + e * nA, nA, a_s, T_s, lane);
+        const T* w = W + static_cast<int64_t>(j) * nW1 * L;
+        for (int b = lane; b < L; b += 32) {
+            const T Bb = B[e * L + b];
+            for (int m3 = 0; m3 < nO1; m3++) {
+                T p = T(0);
+                for (int m2 = 0; m2 < nW1; m2++) {
+                    const int c = m3 * nW1 + m2;
+                    if (s.start[c + 1] > s.start[c]) p += T_s[c] * __ldg(w + m2 * L + b);
+                }
+                if (SEGMENTED)
+                    Oacc[m3 * L + b] += Bb * p;
+                else
+                    red_add(O + out_row * rowsize + m3 * L + b, Bb * p);
+            }
+        }
+    };
+
+    if (SEGMENTED) {
+        const int64_t r = static_cast<int64_t>(blockIdx.x) * warps + warp;
+        check_sorted_slice(Io, E, nW0, r, static_cast<int64_t>(gridDim.x) * warps, lane, st);
+        if (r >= nW0) return;
+        int64_t begin, end;
+        warp_segment(Io, E, static_cast<int32_t>(r), lane, begin, end);
+        for (int idx = lane; idx < rowsize; idx += 32) Oacc[idx] = T(0);
+        for (int64_t e = begin; e < end; e++) edge(e, r);
+        __syncwarp();
+        T* dst = O + r * rowsize;
+        for (int idx = lane; idx < rowsize; idx += 32) dst[idx] = Oacc[idx];
+    } else {
+        const int64_t nwarps = static_cast<int64_t>(gridDim.x) * warps;
+        for (int64_t e = static_cast<int64_t>(blockIdx.x) * warps + warp; e < E; e += nwarps) {
+            int32_t row = __ldg(Io + e);
+            if (clamp_index(row, static_cast<int32_t>(nW0))) {
+                if (lane == 0) report_bad_index(st, kBitI);
+                continue;
+            }
+            edge(e, row);
+        }
+    }
+}
+
+template <typename T>
+__global__ void sasaw_vjp(T* __restrict__ gA, T* __restrict__ gB, T* __restrict__ gW,
+                          const T* __restrict__ gO, const T* __restrict__ A,
+                          const T* __restrict__ B, const T* __restrict__ W,
+                          const int32_t* __restrict__ Jw, const int32_t* __restrict__ Io,
+                          Coupling<T> cp, int64_t E, int nA, int L, int64_t nW0, int nW1, int nO1,
+                          Status st) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int ncell = cp.ncell, N = cp.N;
+    const size_t per_warp = static_cast<size_t>(nA) + 2 * static_cast<size_t>(ncell) + static_cast<size_t>(nA) * 33;
+    Shared<T> s = carve<T>(smem_raw, cp, per_warp, warps, true);
+    load_coupling(s, cp, true);
+    __syncthreads();
+    T* a_s = s.warp_base + per_warp * warp;
+    T* T_s = a_s + nA;
+    T* U_s = T_s + ncell;
+    T* ga_priv = U_s + ncell; // [nA][33]: one private column per lane
+    const int64_t rowsize = static_cast<int64_t>(nO1) * L;
+    const bool want_a = gA != nullptr, want_b = gB != nullptr, want_w = gW != nullptr;
+
+    const int64_t nwarps = static_cast<int64_t>(gridDim.x) * warps;
+    for (int64_t e = static_cast<int64_t>(blockIdx.x) * warps + warp; e < E; e += nwarps) {
+        int32_t row = __ldg(Io + e), j = __ldg(Jw + e);
+        if (clamp_index(row, static_cast<int32_t>(nW0)) && lane == 0) report_bad_index(st, kBitI);
+        if (clamp_index(j, static_cast<int32_t>(nW0)) && lane == 0) report_bad_index(st, kBitJ);
+        contract_coupling(s, ncell, A + e * nA, nA, a_s, T_s, lane);
+        for (int c = lane; c < ncell; c += 32) U_s[c] = T(0);
+        __syncwarp();
+        const T* g = gO + static_cast<int64_t>(row) * rowsize;
+        const T* w = W + static_cast<int64_t>(j) * nW1 * L;
+        T* gw = want_w ? gW + static_cast<int64_t>(j) * nW1 * L : nullptr;
+        for (int b0 = 0; b0 < L; b0 += 32) {
+            const int b = b0 + lane;
+            const bool valid = b < L;
+            const T Bb = valid ? B[e * L + b] : T(0);
+            T gb = T(0);
+            for (int m2 = 0; m2 < nW1; m2++) {
+                const T wv = valid ? __ldg(w + m2 * L + b) : T(0);
+                T accw = T(0);
+                for (int m3 = 0; m3 < nO1; m3++) {
+                    const int c = m3 * nW1 + m2;
+                    if (s.start[c + 1] == s.start[c]) continue;
+                    const T gv = valid ? __ldg(g + m3 * L + b) : T(0);
+                    accw += T_s[c] * gv;
+                    if (want_a) {
+                        const T u = warp_sum(gv * wv * Bb);
+                        if (lane == 0) U_s[c] += u;
+                    }
+                }
+                gb += wv * accw;
+                if (want_w && valid) red_add(gw + m2 * L + b, Bb * accw);
+            }
+            if (want_b && valid) gB[e * L + b] = gb;
+        }
+        if (want_a) {
+            __syncwarp();
+            for (int idx = lane; idx < nA * 33; idx += 32) ga_priv[idx] = T(0);
+            __syncwarp();
+            for (int pos = lane; pos < N; pos += 32)
+                ga_priv[s.M1[pos] * 33 + lane] += s.C[pos] * U_s[s.cell[pos]];
+            __syncwarp();
+            for (int m = lane; m < nA; m += 32) {
+                T sum = T(0);
+                for (int l = 0; l < 32; l++) sum += ga_priv[m * 33 + l];
+                gA[e * nA + m] = sum;
+            }
+        }
+    }
+}
+
+// Any sizes, no shared memory: one thread per (edge, b) walking the whole coupling table.
+// Needs zero-filled O (forward) / gA, gW (VJP).
+template <typename T>
+__global__ void sasaw_fwd_wide(T* __restrict__ O, const T* __restrict__ A, const T* __restrict__ B,
+                               const T* __restrict__ C, const T* __restrict__ W,
+                               const int32_t* __restrict__ M1, const int32_t* __restrict__ Jw,
+                               const int32_t* __restrict__ M2, const int32_t* __restrict__ Io,
+                               const int32_t* __restrict__ M3, int64_t E, int nA, int L, int N,
+                               int64_t nW0, int nW1, int nO1, Status st) {
+    const int64_t total = E * L;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t e = i / L;
+        const int b = static_cast<int>(i - e * L);
+        int32_t row = __ldg(Io + e), j = __ldg(Jw + e);
+        if (clamp_index(row, static_cast<int32_t>(nW0))) { report_bad_index(st, kBitI); continue; }
+        if (clamp_index(j, static_cast<int32_t>(nW0))) { report_bad_index(st, kBitJ); continue; }
+        const T Bb = B[i];
+        for (int n = 0; n < N; n++) {
+            int32_t m1 = __ldg(M1 + n), m2 = __ldg(M2 + n), m3 = __ldg(M3 + n);
+            const bool b1 = clamp_index(m1, nA), b2 = clamp_index(m2, nW1), b3 = clamp_index(m3, nO1);
+            if (b1 || b2 || b3) {
+                if (b1) report_bad_index(st, kBitM1);
+                if (b2) report_bad_index(st, kBitM2);
+                if (b3) report_bad_index(st, kBitM3);
+                continue;
+            }
+            const T v = __ldg(C + n) * A[e * nA + m1] * Bb *
+                        __ldg(W + (static_cast<int64_t>(j) * nW1 + m2) * L + b);
+            red_add(O + (static_cast<int64_t>(row) * nO1 + m3) * L + b, v);
+        }
+    }
+}
+
+template <typename T>
+__global__ void sasaw_vjp_wide(T* __restrict__ gA, T* __restrict__ gB, T* __restrict__ gW,
+                               const T* __restrict__ gO, const T* __restrict__ A,
+                               const T* __restrict__ B, const T* __restrict__ C,
+                               const T* __restrict__ W, const int32_t* __restrict__ M1,
+                               const int32_t* __restrict__ Jw, const int32_t* __restrict__ M2,
+                               const int32_t* __restrict__ Io, const int32_t* __restrict__ M3,
+                               int64_t E, int nA, int L, int N, int64_t nW0, int nW1, int nO1,
+                               Status st) {
+    const int64_t total = E * L;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t e = i / L;
+        const int b = static_cast<int>(i - e * L);
+        int32_t row = __ldg(Io + e), j = __ldg(Jw + e);
+        if (clamp_index(row, static_cast<int32_t>(nW0))) report_bad_index(st, kBitI);
+        if (clamp_index(j, static_cast<int32_t>(nW0))) report_bad_index(st, kBitJ);
+        const T Bb = B[i];
+        T gb = T(0);
+        for (int n = 0; n < N; n++) {
+            int32_t m1 = __ldg(M1 + n), m2 = __ldg(M2 + n), m3 = __ldg(M3 + n);
+            const bool b1 = clamp_index(m1, nA), b2 = clamp_index(m2, nW1), b3 = clamp_index(m3, nO1);
+            if (b1 || b2 || b3) {
+                if (b1) report_bad_index(st, kBitM1);
+                if (b2) report_bad_index(st, kBitM2);
+                if (b3) report_bad_index(st, kBitM3);
+                continue;
+            }
+            const T c = __ldg(C + n), a = A[e * nA + m1];
+            const T gv = __ldg(gO + (static_cast<int64_t>(row) * nO1 + m3) * L + b);
+            const int64_t wi = (static_cast<int64_t>(j) * nW1 + m2) * L + b;
+            const T wv = __ldg(W + wi);
+            if (gA != nullptr) red_add(gA + e * nA + m1, gv * c * Bb * wv);
+            gb += gv * c * a * wv;
+            if (gW != nullptr) red_add(gW + wi, gv * c * a * Bb);
+        }
+        if (gB != nullptr) gB[i] = gb;
+    }
+}
+
+template <typename T> struct Problem {
+    const T *A, *B, *C, *W;
+    const int32_t *M1, *Jw, *M2, *Io, *M3;
+    int64_t E, nW0;
+    int nA, L, N, nW1, nO1;
+};
+
+// Allocates and fills the grouped coupling table; returns false when the grouped kernels
+// cannot be used (cell grid too large for one block's shared memory).
+template <typename T>
+bool build_coupling(const Call& call, const Problem<T>& p, Coupling<T>& cp, void** scratch) {
+    const int64_t ncell64 = static_cast<int64_t>(p.nO1) * p.nW1;
+    if (ncell64 > 8192 || ncell64 == 0) return false;
+    cp.N = p.N;
+    cp.ncell = static_cast<int>(ncell64);
+    const size_t nT = (static_cast<size_t>(p.N) * sizeof(T) + 15) / 16 * 16;
+    const size_t nI = static_cast<size_t>(p.N) * sizeof(int32_t);
+    const size_t bytes = nT + 3 * nI + (cp.ncell + 1) * sizeof(int32_t) + 16;
+    unsigned char* base = static_cast<unsigned char*>(scratch_alloc(call, bytes));
+    *scratch = base;
+    cp.C = reinterpret_cast<T*>(base);
+    cp.M1 = reinterpret_cast<int32_t*>(base + nT);
+    cp.cell = cp.M1 + p.N;
+    cp.order = cp.cell + p.N;
+    cp.start = cp.order + p.N;
+    sasaw_group_coupling<T><<<1, kBuildThreads, cp.ncell * sizeof(int32_t), call.stream>>>(
+        cp, p.C, p.M1, p.M2, p.M3, p.nA, p.nW1, p.nO1, call.status);
+    MOPS_CUDA_OK(cudaGetLastError());
+    return true;
+}
+
+template <typename T>
+size_t block_smem(const Coupling<T>& cp, size_t per_warp_scalars, int warps, bool with_cell) {
+    return (static_cast<size_t>(cp.N) + per_warp_scalars * warps) * sizeof(T) +
+           (static_cast<size_t>(cp.N) * (with_cell ? 2 : 1) + cp.ncell + 1) * sizeof(int32_t);
+}
+
+// Largest warp count (8, 4, 2, 1) whose shared memory fits; 0 if none does.
+template <typename T>
+int pick_warps(const Call& call, const Coupling<T>& cp, size_t per_warp_scalars, bool with_cell,
+               size_t* smem) {
+    for (int warps : {8, 4, 2, 1}) {
+        const size_t bytes = block_smem(cp, per_warp_scalars, warps, with_cell);
+        const size_t limit = warps == 1 ? static_cast<size_t>(max_optin_smem(call.device)) : 100 * 1024;
+        if (bytes <= limit) {
+            *smem = bytes;
+            return warps;
+        }
+    }
+    return 0;
+}
+
+template <typename Kernel> void allow_smem(Kernel kernel, size_t smem) {
+    if (smem > 48 * 1024)
+        MOPS_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          static_cast<int>(smem)));
+}
+
+template <typename T> void forward(const Call& call, T* O, const Problem<T>& p) {
+    const int64_t rowsize = static_cast<int64_t>(p.nO1) * p.L;
+    if (p.nW0 == 0 || rowsize == 0) return;
+    if (p.E == 0 || p.N == 0) {
+        MOPS_CUDA_OK(cudaMemsetAsync(O, 0, p.nW0 * rowsize * sizeof(T), call.stream));
+        return;
+    }
+    const int grid_generic = sm_count(call.device) * 8;
+    Coupling<T> cp{};
+    void* scratch = nullptr;
+    const bool grouped = build_coupling(call, p, cp, &scratch);
+    size_t smem_seg = 0, smem_edge = 0;
+    int warps_seg = 0, warps_edge = 0;
+    if (grouped) {
+        warps_seg = pick_warps(call, cp, static_cast<size_t>(p.nA) + cp.ncell + rowsize, false,
+                               &smem_seg);
+        warps_edge = pick_warps(call, cp, static_cast<size_t>(p.nA) + cp.ncell, false, &smem_edge);
+    }
+    if (grouped && warps_seg > 0 && warps_edge > 0) {
+        allow_smem(sasaw_fwd<T, true>, smem_seg);
+        sasaw_fwd<T, true><<<static_cast<unsigned>(ceil_div(p.nW0, warps_seg)), warps_seg * 32,
+                             smem_seg, call.stream>>>(O, p.A, p.B, p.W, p.Jw, p.Io, cp, p.E, p.nA,
+                                                      p.L, p.nW0, p.nW1, p.nO1, false, call.status);
+        MOPS_CUDA_OK(cudaGetLastError());
+        bool need_fallback = true; // asynchronous calls cannot look: always enqueue
+        if (call.wait) {
+            wait_stream(call);
+            need_fallback = host_saw_unsorted(call);
+        }
+        if (need_fallback) {
+            zero_if_unsorted<T><<<grid_generic, 256, 0, call.stream>>>(O, p.nW0 * rowsize,
+                                                                       call.status);
+            allow_smem(sasaw_fwd<T, false>, smem_edge);
+            const int64_t blocks = std::min<int64_t>(ceil_div(p.E, warps_edge), grid_generic);
+            sasaw_fwd<T, false><<<static_cast<unsigned>(blocks), warps_edge * 32, smem_edge,
+                                  call.stream>>>(O, p.A, p.B, p.W, p.Jw, p.Io, cp, p.E, p.nA, p.L,
+                                                 p.nW0, p.nW1, p.nO1, false, call.status);
+        }
+    } else {
+        MOPS_CUDA_OK(cudaMemsetAsync(O, 0, p.nW0 * rowsize * sizeof(T), call.stream));
+        sasaw_fwd_wide<T><<<grid_generic, 256, 0, call.stream>>>(
+            O, p.A, p.B, p.C, p.W, p.M1, p.Jw, p.M2, p.Io, p.M3, p.E, p.nA, p.L, p.N, p.nW0, p.nW1,
+            p.nO1, call.status);
+    }
+    MOPS_CUDA_OK(cudaGetLastError());
+    scratch_free(call, scratch);
+}
+
+template <typename T>
+void backward(const Call& call, T* gA, T* gB, T* gW, const T* gO, const Problem<T>& p) {
+    if (gA == nullptr && gB == nullptr && gW == nullptr) return;
+    const int64_t wsize = p.nW0 * static_cast<int64_t>(p.nW1) * p.L;
+    if (gW != nullptr && wsize > 0)
+        MOPS_CUDA_OK(cudaMemsetAsync(gW, 0, wsize * sizeof(T), call.stream));
+    if (p.E == 0) return;
+    const bool empty = p.N == 0 || p.L == 0 || p.nO1 == 0 || p.nW1 == 0 || p.nA == 0;
+    Coupling<T> cp{};
+    void* scratch = nullptr;
+    const bool grouped = !empty && build_coupling(call, p, cp, &scratch);
+    size_t smem = 0;
+    int warps = 0;
+    if (grouped)
+        warps = pick_warps(call, cp, static_cast<size_t>(p.nA) * 34 + 2 * static_cast<size_t>(cp.ncell),
+                           true, &smem);
+    if (empty) {
+        if (gA != nullptr && p.nA > 0)
+            MOPS_CUDA_OK(cudaMemsetAsync(gA, 0, p.E * p.nA * sizeof(T), call.stream));
+        if (gB != nullptr && p.L > 0)
+            MOPS_CUDA_OK(cudaMemsetAsync(gB, 0, p.E * p.L * sizeof(T), call.stream));
+    } else if (grouped && warps > 0) {
+        allow_smem(sasaw_vjp<T>, smem);
+        const int64_t blocks =
+            std::min<int64_t>(ceil_div(p.E, warps), static_cast<int64_t>(sm_count(call.device)) * 16);
+        sasaw_vjp<T><<<static_cast<unsigned>(blocks), warps * 32, smem, call.stream>>>(
+            gA, gB, gW, gO, p.A, p.B, p.W, p.Jw, p.Io, cp, p.E, p.nA, p.L, p.nW0, p.nW1, p.nO1,
+            call.status);
+    } else {
+        if (gA != nullptr)
+            MOPS_CUDA_OK(cudaMemsetAsync(gA, 0, p.E * p.nA * sizeof(T), call.stream));
+        sasaw_vjp_wide<T><<<sm_count(call.device) * 8, 256, 0, call.stream>>>(
+            gA, gB, gW, gO, p.A, p.B, p.C, p.W, p.M1, p.Jw, p.M2, p.Io, p.M3, p.E, p.nA, p.L, p.N,
+            p.nW0, p.nW1, p.nO1, call.status);
+    }
+    MOPS_CUDA_OK(cudaGetLastError());
+    scratch_free(call, scratch);
+}
+
+template <typename scalar_t>
+Problem<scalar_t> check_and_pack(const mops::Tensor<scalar_t, 3>& output,
+                                 const mops::Tensor<scalar_t, 2>& A,
+                                 const mops::Tensor<scalar_t, 2>& B,
+                                 const mops::Tensor<scalar_t, 1>& C,
+                                 const mops::Tensor<scalar_t, 3>& W,
+                                 const mops::Tensor<int32_t, 1>& indices_A,
+                                 const mops::Tensor<int32_t, 1>& indices_W_1,
+                                 const mops::Tensor<int32_t, 1>& indices_W_2,
+                                 const mops::Tensor<int32_t, 1>& indices_output_1,
+                                 const mops::Tensor<int32_t, 1>& indices_output_2,
+                                 const std::string& op) {
+    same_size(A, "A", 0, B, "B", 0, op);
+    same_size(W, "W", 0, output, "output", 0, op);
+    same_size(B, "B", 1, W, "W", 2, op);
+    same_size(C, "C", 0, indices_A, "indices_A", 0, op);
+    same_size(C, "C", 0, indices_W_2, "indices_W_2", 0, op);
+    same_size(C, "C", 0, indices_output_2, "indices_output_2", 0, op);
+    same_size(A, "A", 0, indices_output_1, "indices_output_1", 0, op);
+    same_size(A, "A", 0, indices_W_1, "indices_W_1", 0, op);
+    // Not checked by the reference (checks/sasaw.hpp:22-29), needed for memory safety here:
+    same_size(B, "B", 1, output, "output", 2, op);
+    fits_int32(W.shape[0], "W.shape[0]", op);
+    fits_int32(W.shape[1], "W.shape[1]", op);
+    fits_int32(A.shape[1], "A.shape[1]", op);
+    fits_int32(B.shape[1], "B.shape[1]", op);
+    fits_int32(C.shape[0], "C.shape[0]", op);
+    fits_int32(output.shape[1], "output.shape[1]", op);
+    Problem<scalar_t> p;
+    p.A = A.data;
+    p.B = B.data;
+    p.C = C.data;
+    p.W = W.data;
+    p.M1 = indices_A.data;
+    p.Jw = indices_W_1.data;
+    p.M2 = indices_W_2.data;
+    p.Io = indices_output_1.data;
+    p.M3 = indices_output_2.data;
+    p.E = static_cast<int64_t>(A.shape[0]);
+    p.nW0 = static_cast<int64_t>(W.shape[0]);
+    p.nA = static_cast<int>(A.shape[1]);
+    p.L = static_cast<int>(B.shape[1]);
+    p.N = static_cast<int>(C.shape[0]);
+    p.nW1 = static_cast<int>(W.shape[1]);
+    p.nO1 = static_cast<int>(output.shape[1]);
+    return p;
+}
+
+} // namespace
+} // namespace mops_b200
+
+using namespace mops_b200;
+
+template <typename scalar_t>
+void mops::cuda::sparse_accumulation_scatter_add_with_weights(
+    Tensor<scalar_t, 3> output, Tensor<scalar_t, 2> A, Tensor<scalar_t, 2> B,
+    Tensor<scalar_t, 1> C, Tensor<scalar_t, 3> W, Tensor<int32_t, 1> indices_A,
+    Tensor<int32_t, 1> indices_W_1, Tensor<int32_t, 1> indices_W_2,
+    Tensor<int32_t, 1> indices_output_1, Tensor<int32_t, 1> indices_output_2) {
+    const std::string op = "cuda_sparse_accumulation_scatter_add_with_weights";
+    Problem<scalar_t> p = check_and_pack(output, A, B, C, W, indices_A, indices_W_1, indices_W_2,
+                                         indices_output_1, indices_output_2, op);
+    Call call = begin_call();
+    forward<scalar_t>(call, output.data, p);
+    end_call(call, op.c_str(), kIndexNames, 5);
+}
+
+template <typename scalar_t>
+void mops::cuda::sparse_accumulation_scatter_add_with_weights_vjp(
+    Tensor<scalar_t, 2> grad_A, Tensor<scalar_t, 2> grad_B, Tensor<scalar_t, 3> grad_W,
+    Tensor<scalar_t, 3> grad_output, Tensor<scalar_t, 2> A, Tensor<scalar_t, 2> B,
+    Tensor<scalar_t, 1> C, Tensor<scalar_t, 3> W, Tensor<int32_t, 1> indices_A,
+    Tensor<int32_t, 1> indices_W_1, Tensor<int32_t, 1> indices_W_2,
+    Tensor<int32_t, 1> indices_output_1, Tensor<int32_t, 1> indices_output_2) {
+    const std::string op = "cuda_sparse_accumulation_scatter_add_with_weights_vjp";
+    grad_like(grad_A, "grad_A", A, "A", op);
+    grad_like(grad_B, "grad_B", B, "B", op);
+    grad_like(grad_W, "grad_W", W, "W", op);
+    Problem<scalar_t> p = check_and_pack(grad_output, A, B, C, W, indices_A, indices_W_1,
+                                         indices_W_2, indices_output_1, indices_output_2, op);
+    Call call = begin_call();
+    backward<scalar_t>(call, grad_A.data, grad_B.data, grad_W.data, grad_output.data, p);
+    end_call(call, op.c_str(), kIndexNames, 5);
+}
+
+template <typename scalar_t>
+void mops::cuda::sparse_accumulation_scatter_add_with_weights_vjp_vjp(
+    Tensor<scalar_t, 3>, Tensor<scalar_t, 2>, Tensor<scalar_t, 2>, Tensor<scalar_t, 3>,
+    Tensor<scalar_t, 2>, Tensor<scalar_t, 2>, Tensor<scalar_t, 3>, Tensor<scalar_t, 3>,
+    Tensor<scalar_t, 2>, Tensor<scalar_t, 2>, Tensor<scalar_t, 1>, Tensor<scalar_t, 3>,
+    Tensor<int32_t, 1>, Tensor<int32_t, 1>, Tensor<int32_t, 1>, Tensor<int32_t, 1>,
+    Tensor<int32_t, 1>) {
+    // The reference has no second-order SASAW on any device (mops/src/sasaw/cpu.tpp:193).
+    throw std::runtime_error("Not implemented");
+}
+
+#define INSTANTIATE(T)                                                                             \
+    template void mops::cuda::sparse_accumulation_scatter_add_with_weights<T>(                    \
+        mops::Tensor<T, 3>, mops::Tensor<T, 2>, mops::Tensor<T, 2>, mops::Tensor<T, 1>,           \
+        mops::Tensor<T, 3>, mops::Tensor<int32_t, 1>, mops::Tensor<int32_t, 1>,                   \
+        mops::Tensor<int32_t, 1>, mops::Tensor<int32_t, 1>, mops::Tensor<int32_t, 1>);            \
+    template void mops::cuda::sparse_accumulation_scatter_add_with_weights_vjp<T>(                \
+        mops::Tensor<T, 2>, mops::Tensor<T, 2>, mops::Tensor<T, 3>, mops::Tensor<T, 3>,           \
+        mops::Tensor<T, 2>, mops::Tensor<T, 2>, mops::Tensor<T, 1>, mops::Tensor<T, 3>,           \
+        mops::Tensor<int32_t, 1>, mops::Tensor<int32_t, 1>, mops::Tensor<int32_t, 1>,             \
+        mops::Tensor<int32_t, 1>, mops::Tensor<int32_t, 1>);                                      \
+    template void mops::cuda::sparse_accumulation_scatter_add_with_weights_vjp_vjp<T>(            \
+        mops::Tensor<T, 3>, mops::Tensor<T, 2>, mops::Tensor<T, 2>, mops::Tensor<T, 3>,           \
+        mops::Tensor<T, 2>, mops::Tensor<T, 2>, mops::Tensor<T, 3>, mops::Tensor<T, 3>,           \
+        mops::Tensor<T, 2>, mops::Tensor<T, 2>, mops::Tensor<T, 1>, mops::Tensor<T, 3>,           \
+        mops::Tensor<int32_t, 1>, mops::Tensor<int32_t, 1>, mops::Tensor<int32_t, 1>,             \
+        mops::Tensor<int32_t, 1>, mops::Tensor<int32_t, 1>);
+
+INSTANTIATE(float)
+INSTANTIATE(double)

@@ -1,0 +1,282 @@
+"""Parity of the sm_100a kernels, called through the C ABI, against the CPU oracle, the
+committed golden vectors and (where built) the unmodified reference CPU library.
+
+Tolerances (conftest.assert_parity): 1e-12 of the tensor's largest magnitude for f64,
+1e-5 for f32."""
+import os
+
+import numpy as np
+import pytest
+
+import fixtures
+from conftest import assert_parity
+from helpers import run_checker, run_library, to_dev
+from mops_b200 import workloads
+
+pytestmark = pytest.mark.gpu
+
+GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "golden.npz"))
+DTYPES = [np.float64, np.float32]
+
+
+def compare(op, d, dtype, checker, second_order=False, what=""):
+    got = run_library(op, to_dev(d, dtype), second_order)
+    want = run_checker(checker, op, d, dtype, second_order)
+    assert set(got) == set(want)
+    for k in want:
+        assert_parity(got[k], want[k], f"{what or op}/{k}/{np.dtype(dtype).name}")
+
+
+# ---------------------------------------------------------------- the reference's fixtures
+@pytest.mark.parametrize("name", sorted(fixtures.CASES))
+def test_golden_vectors(name):
+    """f64 results equal the vectors produced by the reference's NumPy implementations.
+    Scatter indices of these fixtures are unsorted: exercises the unsorted-index path."""
+    d = fixtures.CASES[name]()
+    op = name.split("_")[0]
+    got = run_library(op, to_dev(d, np.float64), second_order=(op == "sap"))
+    keys = [k for k in GOLD.files if k.startswith(name + "/")]
+    assert len(keys) == len(got)
+    for k in keys:
+        assert_parity(got[k.split("/")[1]], GOLD[k], k)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", sorted(fixtures.CASES))
+def test_fixtures_against_oracle(oracle, name, dtype):
+    op = name.split("_")[0]
+    compare(op, fixtures.CASES[name](), dtype, oracle, second_order=(op == "sap"), what=name)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["opsa", "opsa_empty_row", "opsaw", "opsaw_empty_row", "sasaw"])
+def test_fixtures_sorted_indices(oracle, name, dtype):
+    """The same fixtures with the entries sorted by output row: the segmented fast path
+    (this is how the reference's own CUDA tests call OPSA, python/mops/tests/opsa.py:96)."""
+    d = fixtures.CASES[name]()
+    key = "indices_output_1" if name == "sasaw" else "indices_output"
+    order = np.argsort(d[key], kind="stable")
+    per_entry = {"A", "B", key, "indices_W", "indices_W_1"}
+    d = {k: (v[order] if k in per_entry and isinstance(v, np.ndarray) else v) for k, v in d.items()}
+    compare(name.split("_")[0], d, dtype, oracle, what=name + "/sorted")
+
+
+# ---------------------------------------------------------------- benchmark shapes
+SMALL = {"hpe": {}, "sap": {}, "opsa": {}, "opsaw": {}, "sasaw": dict(E=6000, n=100)}
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("op", sorted(SMALL))
+def test_benchmark_shapes_against_oracle(oracle, op, dtype):
+    compare(op, workloads.GENERATORS[op](dtype=dtype, **SMALL[op]), dtype, oracle)
+
+
+@pytest.mark.parametrize("op", sorted(SMALL))
+def test_benchmark_shapes_against_reference_library(reference, op):
+    compare(op, workloads.GENERATORS[op](**SMALL[op]), np.float64, reference)
+
+
+def test_sasaw_full_small_config(oracle):
+    """SASAW at the full E=60000 / 1000-node shape (about two seconds of oracle time)."""
+    compare("sasaw", workloads.sasaw(), np.float64, oracle)
+
+
+# ---------------------------------------------------------------- edge cases
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("K", list(range(0, 11)))
+def test_hpe_every_order(oracle, K, dtype):
+    r = np.random.default_rng(100 + K)
+    d = dict(A=r.uniform(-1, 1, (77, 13)), C=r.standard_normal(41),
+             indices_A=r.integers(0, 13, (41, K), dtype=np.int32), grad_output=r.standard_normal(77))
+    compare("hpe", d, dtype, oracle, what=f"hpe K={K}")
+
+
+def test_hpe_order_above_10_is_an_error():
+    import torch
+    import mops_b200 as M
+    A = torch.zeros(4, 3, device="cuda", dtype=torch.float64)
+    C = torch.zeros(2, device="cuda", dtype=torch.float64)
+    P = torch.zeros(2, 11, device="cuda", dtype=torch.int32)
+    with pytest.raises(M.MopsError, match="Only up to polynomial order 10 is supported"):
+        M.homogeneous_polynomial_evaluation(A, C, P)
+
+
+@pytest.mark.parametrize("I", [1, 31, 32, 33, 257])
+def test_ragged_batch_sizes(oracle, I):
+    compare("hpe", workloads.hpe(I=I, N=17, J=50, K=3), np.float64, oracle, what=f"hpe I={I}")
+    compare("sap", workloads.sap(I=I, K=120), np.float64, oracle, second_order=False,
+            what=f"sap I={I}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_wide_operands_take_the_global_memory_kernels(oracle, dtype):
+    """Operand widths whose tiles do not fit in shared memory."""
+    compare("hpe", workloads.hpe(I=70, N=1500, J=64, K=3), dtype, oracle, what="hpe wide")
+    compare("sap", workloads.sap(I=70, nA=900, nB=700, nO=800, K=500), dtype, oracle,
+            what="sap wide")
+    compare("opsa", workloads.opsa(J=300, K=40, L=900, nO=7), dtype, oracle, what="opsa wide")
+    compare("opsaw", workloads.opsaw(E=300, K=40, L=900, n=7), dtype, oracle, what="opsaw wide")
+    compare("sasaw", workloads.sasaw(E=200, nA=5, L=700, n=6, N=40, nW2=30, nO2=40), dtype,
+            oracle, what="sasaw wide")
+
+
+@pytest.mark.parametrize("K,L", [(1, 1), (3, 7), (13, 20), (17, 33), (40, 5), (2, 64), (25, 25)])
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_outer_product_shapes(oracle, K, L, dtype):
+    compare("opsa", workloads.opsa(J=700, K=K, L=L, nO=23), dtype, oracle, what=f"opsa {K}x{L}")
+    compare("opsaw", workloads.opsaw(E=700, K=K, L=L, n=23), dtype, oracle, what=f"opsaw {K}x{L}")
+
+
+def test_single_giant_segment_and_many_empty_rows(oracle):
+    d = workloads.opsa(J=5000, K=5, L=6, nO=40)
+    d["indices_output"][:] = 17
+    compare("opsa", d, np.float64, oracle, what="opsa one segment")
+    d = workloads.opsa(J=50, K=5, L=6, nO=4000)
+    compare("opsa", d, np.float64, oracle, what="opsa mostly empty")
+    d = workloads.sasaw(E=40, n=300, N=60)
+    compare("sasaw", d, np.float64, oracle, what="sasaw mostly empty")
+
+
+def test_sasaw_shapes(oracle):
+    for kw in (dict(E=500, nA=1, L=1, n=9, N=1, nW2=1, nO2=1),
+               dict(E=500, nA=4, L=33, n=9, N=37, nW2=3, nO2=5),
+               dict(E=500, nA=16, L=64, n=9, N=300, nW2=7, nO2=3)):
+        d = workloads.sasaw(**kw)
+        d["indices_output_2"] = np.random.default_rng(3).permutation(d["indices_output_2"])
+        compare("sasaw", d, np.float64, oracle, what=f"sasaw {kw}")
+
+
+def test_empty_inputs():
+    import torch
+    import mops_b200 as M
+    f = dict(device="cuda", dtype=torch.float64)
+    i = dict(device="cuda", dtype=torch.int32)
+    out = M.outer_product_scatter_add(torch.zeros(0, 3, **f), torch.zeros(0, 4, **f),
+                                      torch.zeros(0, **i), 5)
+    assert out.shape == (5, 3, 4) and float(out.abs().sum()) == 0.0
+    out = M.sparse_accumulation_of_products(torch.zeros(6, 3, **f), torch.zeros(6, 2, **f),
+                                            torch.zeros(0, **f), torch.zeros(0, **i),
+                                            torch.zeros(0, **i), torch.zeros(0, **i), 4)
+    assert out.shape == (6, 4) and float(out.abs().sum()) == 0.0
+    out = M.homogeneous_polynomial_evaluation(torch.zeros(0, 3, **f), torch.zeros(2, **f),
+                                              torch.zeros(2, 2, **i))
+    assert out.shape == (0,)
+    out = M.homogeneous_polynomial_evaluation(torch.ones(5, 3, **f), torch.zeros(0, **f),
+                                              torch.zeros(0, 2, **i))
+    assert out.shape == (5,) and float(out.abs().sum()) == 0.0
+
+
+def test_skipped_gradients(oracle):
+    import mops_b200 as M
+    d = workloads.opsaw(E=400, n=11)
+    t = to_dev(d, np.float64)
+    want = run_checker(oracle, "opsaw", d, np.float64)
+    for need in [(True, False, False), (False, True, False), (False, False, True)]:
+        gA, gB, gW = M.outer_product_scatter_add_with_weights_vjp(
+            t["grad_output"], t["A"], t["B"], t["W"], t["indices_W"], t["indices_output"], *need)
+        for g, name, n in zip((gA, gB, gW), ("grad_A", "grad_B", "grad_W"), need):
+            assert (g is not None) == n
+            if n:
+                assert_parity(g.cpu().numpy(), want[name], name)
+    d = workloads.sap(I=100)
+    t = to_dev(d, np.float64)
+    want = run_checker(oracle, "sap", d, np.float64)
+    gA, gB = M.sparse_accumulation_of_products_vjp(
+        t["grad_output"], t["A"], t["B"], t["C"], t["indices_A"], t["indices_B"],
+        t["indices_output"], compute_grad_A=False)
+    assert gA is None
+    assert_parity(gB.cpu().numpy(), want["grad_B"], "grad_B only")
+
+
+def test_out_of_range_indices_are_reported():
+    """The reference trusts device index arrays; here they are checked on the device."""
+    import mops_b200 as M
+    d = workloads.opsa(J=500, nO=10)
+    d["indices_output"][-1] = 10
+    t = to_dev(d, np.float64)
+    with pytest.raises(M.MopsError, match="Index array indices_output in operation "
+                                          "cuda_outer_product_scatter_add contains"):
+        M.outer_product_scatter_add(t["A"], t["B"], t["indices_output"], 10)
+    d = workloads.hpe(I=64, N=10, J=20)
+    d["indices_A"][7, 2] = -1
+    t = to_dev(d, np.float64)
+    with pytest.raises(M.MopsError, match="Index array indices_A"):
+        M.homogeneous_polynomial_evaluation(t["A"], t["C"], t["indices_A"])
+    d = workloads.sap(I=64)
+    d["indices_B"][3] = 6
+    t = to_dev(d, np.float64)
+    with pytest.raises(M.MopsError, match="Index array indices_B"):
+        M.sparse_accumulation_of_products(t["A"], t["B"], t["C"], t["indices_A"], t["indices_B"],
+                                          t["indices_output"], 50)
+    # the library keeps working afterwards
+    d = workloads.sap(I=64)
+    t = to_dev(d, np.float64)
+    M.sparse_accumulation_of_products(t["A"], t["B"], t["C"], t["indices_A"], t["indices_B"],
+                                      t["indices_output"], 50)
+
+
+def test_runs_are_bitwise_reproducible():
+    """Kernels that use no atomics give identical bits on every run."""
+    for op in ("hpe", "sap", "opsa"):
+        d = to_dev(workloads.GENERATORS[op](), np.float64)
+        a, b = run_library(op, d), run_library(op, d)
+        for k in a:
+            assert np.array_equal(a[k], b[k]), f"{op}/{k}"
+    d = to_dev(workloads.opsaw(), np.float64)
+    a, b = run_library("opsaw", d), run_library("opsaw", d)
+    for k in ("output", "grad_A", "grad_B"):
+        assert np.array_equal(a[k], b[k]), f"opsaw/{k}"
+
+
+def test_host_arrays_round_trip(oracle):
+    """NumPy in, NumPy out: staged through the GPU (there is no CPU implementation)."""
+    import mops_b200 as M
+    d = workloads.opsa(J=3000, nO=50)
+    out = M.outer_product_scatter_add(d["A"], d["B"], d["indices_output"], 50)
+    assert isinstance(out, np.ndarray)
+    assert_parity(out, oracle.opsa(d["A"], d["B"], d["indices_output"], 50), "numpy opsa")
+
+
+# ---------------------------------------------------------------- full-size properties
+def test_full_size_properties():
+    """At the scaled sizes the oracle is too slow; check size-independent properties:
+    linearity in A, agreement of the forward with a sum of two halves of the entries, and
+    <gO, O(A,B)> == <gA, A> (the VJP is the adjoint of a map that is linear in A)."""
+    import torch
+    import mops_b200 as M
+    torch.manual_seed(5)
+    J, K, L, nO = 1 << 21, 13, 20, 1 << 15
+    f = dict(device="cuda", dtype=torch.float64)
+    A, B = torch.randn(J, K, **f), torch.randn(J, L, **f)
+    P = torch.sort(torch.randint(0, nO, (J,), device="cuda", dtype=torch.int32)).values
+    O = M.outer_product_scatter_add(A, B, P, nO)
+    O2 = M.outer_product_scatter_add(2.5 * A, B, P, nO)
+    assert torch.allclose(O2, 2.5 * O, rtol=1e-13, atol=1e-12)
+    h = J // 2
+    while P[h] == P[h - 1]:
+        h += 1
+    Oa = M.outer_product_scatter_add(A[:h], B[:h], P[:h], nO)
+    Ob = M.outer_product_scatter_add(A[h:].contiguous(), B[h:].contiguous(), P[h:].contiguous(), nO)
+    assert torch.equal(Oa + Ob, O)
+    gO = torch.randn(nO, K, L, **f)
+    gA, gB = M.outer_product_scatter_add_vjp(gO, A, B, P)
+    lhs, rhs = float((gO * O).sum()), float((gA * A).sum())
+    assert abs(lhs - rhs) <= 1e-10 * max(abs(lhs), 1.0)
+    rhs_b = float((gB * B).sum())
+    assert abs(lhs - rhs_b) <= 1e-10 * max(abs(lhs), 1.0)
+
+    I = 1 << 18
+    d = workloads.sap(I=8)
+    C = torch.from_numpy(d["C"]).cuda()
+    idx = [torch.from_numpy(d[k]).cuda() for k in ("indices_A", "indices_B", "indices_output")]
+    A, B = torch.rand(I, 20, **f), torch.rand(I, 6, **f)
+    O = M.sparse_accumulation_of_products(A, B, C, *idx, 50)
+    gO = torch.randn(I, 50, **f)
+    gA, gB = M.sparse_accumulation_of_products_vjp(gO, A, B, C, *idx)
+    lhs = float((gO * O).sum())
+    assert abs(lhs - float((gA * A).sum())) <= 1e-10 * max(abs(lhs), 1.0)
+    assert abs(lhs - float((gB * B).sum())) <= 1e-10 * max(abs(lhs), 1.0)
+    # rows are independent: any block of rows equals the same rows computed alone
+    sub = M.sparse_accumulation_of_products(A[1000:1100].contiguous(), B[1000:1100].contiguous(),
+                                            C, *idx, 50)
+    assert torch.equal(sub, O[1000:1100])
