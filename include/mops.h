@@ -184,6 +184,22 @@ MOPS_EXPORT void* mops_b200_get_stream(void);
 MOPS_EXPORT void mops_b200_set_wait(int wait);
 MOPS_EXPORT int mops_b200_get_wait(void);
 
+/* SASAW forward for callers that cannot allocate device memory at the time they call: a
+ * host program whose own pool has reserved the whole device, where a cudaMalloc made by a
+ * library fails or fragments that pool, and latency-critical loops, where a driver
+ * allocation may block or synchronise the device.
+ * No counterpart in the reference. Same arguments, result and status convention as
+ * mops_cuda_sparse_accumulation_scatter_add_with_weights_f64, but its internal scratch (the
+ * grouped coupling table and the status words) is a fixed array inside the library instead
+ * of call-scoped allocations: it calls no cudaMalloc/cudaFree or other allocating routine.
+ * Limits: C.shape[0] <= 4096 coupling entries and output.shape[1] * W.shape[1] <= 1024;
+ * beyond that it returns 1 with a message. All calls share the one array per GPU (held until
+ * the process exits, about 100 KB), so calls whose GPU work overlaps race: serialise them.
+ * The first call on each device looks up the array's address and must be made outside any
+ * stream capture. Runs on the thread's stream (mops_b200_set_stream) and returns when done. */
+MOPS_EXPORT int mops_b200_cuda_sparse_accumulation_scatter_add_with_weights_noalloc_f64(
+    MOPS_ARGS_SASAW(f64));
+
 /* Version string of this build. */
 MOPS_EXPORT const char* mops_b200_version(void);
 

@@ -29,7 +29,8 @@ def abi_symbols():
 
 
 EXTENSION_SYMBOLS = ("mops_b200_set_stream", "mops_b200_get_stream", "mops_b200_set_wait",
-                     "mops_b200_get_wait", "mops_b200_version")
+                     "mops_b200_get_wait", "mops_b200_version",
+                     "mops_b200_cuda_sparse_accumulation_scatter_add_with_weights_noalloc_f64")
 
 
 class MopsError(Exception):

@@ -135,6 +135,21 @@ DEFINE_ENTRY(sparse_accumulation_scatter_add_with_weights_vjp, MOPS_ARGS_SASAW_V
 DEFINE_ENTRY(sparse_accumulation_scatter_add_with_weights_vjp_vjp, MOPS_ARGS_SASAW_VJP_VJP,
              NAMES_SASAW_VJP_VJP)
 
+namespace mops_b200 {
+void sasaw_forward_noalloc_f64(mops::Tensor<double, 3>, mops::Tensor<double, 2>,
+                               mops::Tensor<double, 2>, mops::Tensor<double, 1>,
+                               mops::Tensor<double, 3>, mops::Tensor<int32_t, 1>,
+                               mops::Tensor<int32_t, 1>, mops::Tensor<int32_t, 1>,
+                               mops::Tensor<int32_t, 1>, mops::Tensor<int32_t, 1>);
+}
+
+// Allocation-free SASAW forward (see sasaw.cu); same arguments and status convention as
+// mops_cuda_sparse_accumulation_scatter_add_with_weights_f64.
+extern "C" int mops_b200_cuda_sparse_accumulation_scatter_add_with_weights_noalloc_f64(
+    MOPS_ARGS_SASAW(f64)) {
+    return guarded([&] { mops_b200::sasaw_forward_noalloc_f64(NAMES_SASAW(AS_CPP)); });
+}
+
 extern "C" const char* mops_get_last_error_message(void) { return g_last_error.c_str(); }
 
 extern "C" void mops_b200_set_stream(void* stream) { mops_b200::set_stream(stream); }

@@ -28,6 +28,7 @@
 // is not sorted. VJP: one warp per edge (lane = b), independent of the index order; gW is
 // accumulated with RED because indices_W_1 is not sorted.
 #include <algorithm>
+#include <mutex>
 
 #include "checks.hpp"
 #include "device.cuh"
@@ -644,3 +645,173 @@ void mops::cuda::sparse_accumulation_scatter_add_with_weights_vjp_vjp(
 
 INSTANTIATE(float)
 INSTANTIATE(double)
+
+// ------------------------------------------------------------ allocation-free SASAW forward
+//
+// mops_b200_cuda_sparse_accumulation_scatter_add_with_weights_noalloc_f64: the forward above
+// for callers that cannot allocate device memory at the time they call: a host program
+// whose own memory pool has reserved the whole device (a simulation code or a serving
+// process that takes all of HBM at start-up, where a cudaMalloc from a library fails or
+// fragments the pool), and latency-critical loops, where a driver allocation may block or
+// synchronise the device. It computes exactly what
+// mops_cuda_sparse_accumulation_scatter_add_with_weights_f64 computes, but everything the
+// normal path allocates (the grouped coupling table and the status words the kernels report
+// through) lives in the fixed device array below, so the entry point calls no cudaMalloc,
+// cudaFree, cudaMallocAsync or any other allocating routine. The caller still passes all
+// inputs and the output.
+//
+// Limits and rules:
+//   * at most kNoAllocMaxEntries coupling entries (C.shape[0]) and kNoAllocMaxCells cells
+//     (output.shape[1] * W.shape[1]); larger problems are rejected with status 1;
+//   * every GPU that loads this library holds the array (about 100 KB) until the process ends;
+//   * all calls share the array and it keeps the previous call's contents: the status words
+//     are cleared at the start of each call, the table is rewritten in full; two calls whose
+//     GPU work overlaps (different streams or threads) race on it, so serialise them;
+//   * the first call on each device looks up the array's device address
+//     (cudaGetSymbolAddress); make that first call outside any stream capture;
+//   * runs on the calling thread's stream (mops_b200_set_stream) and returns when the result
+//     is complete.
+namespace mops_b200 {
+namespace {
+
+constexpr int kNoAllocMaxEntries = 4096;
+constexpr int kNoAllocMaxCells = 1024;
+constexpr size_t kNoAllocStatusBytes = 256; // status words, padded so the table stays aligned
+constexpr size_t kNoAllocBytes = kNoAllocStatusBytes + kNoAllocMaxEntries * sizeof(double) +
+                                 3 * kNoAllocMaxEntries * sizeof(int32_t) +
+                                 (kNoAllocMaxCells + 1) * sizeof(int32_t) + 252;
+
+// In host code this name is only a handle for cudaGetSymbolAddress, never a device address.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+
+constexpr int kNoAllocMaxDevices = 64;
+std::mutex g_noalloc_mutex;
+unsigned char* g_noalloc_address[kNoAllocMaxDevices] = {};
+uint32_t g_noalloc_epoch = 0;
+
+// Device address of the scratch array on the current device (looked up once per device).
+unsigned char* noalloc_scratch_for_current_device(int* device_out) {
+    int device = 0;
+    MOPS_CUDA_OK(cudaGetDevice(&device));
+    if (device < 0 || device >= kNoAllocMaxDevices)
+        throw std::runtime_error("device ordinal out of range for the allocation-free entry point");
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (g_noalloc_address[device] == nullptr) {
+        void* ptr = nullptr;
+        MOPS_CUDA_OK(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+        g_noalloc_address[device] = static_cast<unsigned char*>(ptr);
+    }
+    *device_out = device;
+    return g_noalloc_address[device];
+}
+
+void forward_noalloc(double* O, const Problem<double>& p) {
+    using T = double;
+    const int64_t rowsize = static_cast<int64_t>(p.nO1) * p.L;
+    const int64_t ncell = static_cast<int64_t>(p.nO1) * p.nW1;
+    if (p.N > kNoAllocMaxEntries || ncell > kNoAllocMaxCells) {
+        throw std::runtime_error(
+            "the allocation-free SASAW entry point supports at most " +
+            std::to_string(kNoAllocMaxEntries) + " coupling entries and " +
+            std::to_string(kNoAllocMaxCells) + " (output_size x W.shape[1]) cells; got " +
+            std::to_string(p.N) + " and " + std::to_string(ncell) +
+            ". Use mops_cuda_sparse_accumulation_scatter_add_with_weights_f64 instead");
+    }
+    Call call;
+    unsigned char* base = noalloc_scratch_for_current_device(&call.device);
+    call.stream = static_cast<cudaStream_t>(get_stream());
+    call.wait = true;
+    {
+        std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+        g_noalloc_epoch += 1;
+        if (g_noalloc_epoch == 0) g_noalloc_epoch = 1;
+        call.status.epoch = g_noalloc_epoch;
+    }
+    // Both views of the status block are the device array: nothing here is host-mapped.
+    call.status.dev = reinterpret_cast<uint32_t*>(base);
+    call.status.host = call.status.dev;
+    MOPS_CUDA_OK(cudaMemsetAsync(base, 0, kNoAllocStatusBytes, call.stream));
+
+    if (p.nW0 == 0 || rowsize == 0) return;
+    if (p.E == 0 || p.N == 0) {
+        MOPS_CUDA_OK(cudaMemsetAsync(O, 0, p.nW0 * rowsize * sizeof(T), call.stream));
+        MOPS_CUDA_OK(cudaStreamSynchronize(call.stream));
+        return;
+    }
+
+    Coupling<T> cp{};
+    cp.N = p.N;
+    cp.ncell = static_cast<int>(ncell);
+    unsigned char* table = base + kNoAllocStatusBytes;
+    cp.C = reinterpret_cast<T*>(table);
+    cp.M1 = reinterpret_cast<int32_t*>(table + kNoAllocMaxEntries * sizeof(T));
+    cp.cell = cp.M1 + kNoAllocMaxEntries;
+    cp.order = cp.cell + kNoAllocMaxEntries;
+    cp.start = cp.order + kNoAllocMaxEntries;
+    sasaw_group_coupling<T><<<1, kBuildThreads, cp.ncell * sizeof(int32_t), call.stream>>>(
+        cp, p.C, p.M1, p.M2, p.M3, p.nA, p.nW1, p.nO1, call.status);
+    MOPS_CUDA_OK(cudaGetLastError());
+
+    size_t smem_seg = 0, smem_edge = 0;
+    const int warps_seg =
+        pick_warps(call, cp, static_cast<size_t>(p.nA) + cp.ncell + rowsize, false, &smem_seg);
+    const int warps_edge =
+        pick_warps(call, cp, static_cast<size_t>(p.nA) + cp.ncell, false, &smem_edge);
+    if (warps_seg == 0 || warps_edge == 0) {
+        throw std::runtime_error("rows of this size do not fit the allocation-free SASAW entry "
+                                 "point's shared-memory kernels; use "
+                                 "mops_cuda_sparse_accumulation_scatter_add_with_weights_f64");
+    }
+    allow_smem(sasaw_fwd<T, true>, smem_seg);
+    sasaw_fwd<T, true><<<static_cast<unsigned>(ceil_div(p.nW0, warps_seg)), warps_seg * 32,
+                         smem_seg, call.stream>>>(O, p.A, p.B, p.W, p.Jw, p.Io, cp, p.E, p.nA, p.L,
+                                                  p.nW0, p.nW1, p.nO1, false, call.status);
+    MOPS_CUDA_OK(cudaGetLastError());
+    MOPS_CUDA_OK(cudaStreamSynchronize(call.stream));
+
+    uint32_t words[kStatusWords];
+    MOPS_CUDA_OK(cudaMemcpy(words, base, sizeof(words), cudaMemcpyDeviceToHost));
+    if (words[kUnsortedEpoch] == call.status.epoch) {
+        const int grid_generic = sm_count(call.device) * 8;
+        zero_if_unsorted<T><<<grid_generic, 256, 0, call.stream>>>(O, p.nW0 * rowsize, call.status);
+        allow_smem(sasaw_fwd<T, false>, smem_edge);
+        const int64_t blocks = std::min<int64_t>(ceil_div(p.E, warps_edge), grid_generic);
+        sasaw_fwd<T, false><<<static_cast<unsigned>(blocks), warps_edge * 32, smem_edge,
+                              call.stream>>>(O, p.A, p.B, p.W, p.Jw, p.Io, cp, p.E, p.nA, p.L,
+                                             p.nW0, p.nW1, p.nO1, false, call.status);
+        MOPS_CUDA_OK(cudaGetLastError());
+        MOPS_CUDA_OK(cudaStreamSynchronize(call.stream));
+        MOPS_CUDA_OK(cudaMemcpy(words, base, sizeof(words), cudaMemcpyDeviceToHost));
+    }
+    std::string names;
+    for (int i = 0; i < 5; i++) {
+        if (words[kBadIndex0 + i] == call.status.epoch) {
+            if (!names.empty()) names += ", ";
+            names += kIndexNames[i];
+        }
+    }
+    if (!names.empty()) {
+        throw std::runtime_error(
+            "Index array " + names + " in operation "
+            "cuda_sparse_accumulation_scatter_add_with_weights (allocation-free) contains "
+            "negative or too large elements; this would cause out-of-bounds accesses");
+    }
+}
+
+} // namespace
+
+// Called by the C entry point in capi.cu.
+void sasaw_forward_noalloc_f64(mops::Tensor<double, 3> output, mops::Tensor<double, 2> A,
+                               mops::Tensor<double, 2> B, mops::Tensor<double, 1> C,
+                               mops::Tensor<double, 3> W, mops::Tensor<int32_t, 1> indices_A,
+                               mops::Tensor<int32_t, 1> indices_W_1,
+                               mops::Tensor<int32_t, 1> indices_W_2,
+                               mops::Tensor<int32_t, 1> indices_output_1,
+                               mops::Tensor<int32_t, 1> indices_output_2) {
+    const std::string op = "cuda_sparse_accumulation_scatter_add_with_weights";
+    Problem<double> p = check_and_pack(output, A, B, C, W, indices_A, indices_W_1, indices_W_2,
+                                       indices_output_1, indices_output_2, op);
+    forward_noalloc(output.data, p);
+}
+
+} // namespace mops_b200
