@@ -65,8 +65,12 @@ def selected_cases(which):
     return list(CASES) if which == "all" else [which]
 
 
+SCALE = 1  # --scale N divides every batch dimension by N (small cases for ncu captures)
+
+
 def generate(name, rank, divisor=1):
     op, dtype, kw, _ = CASES[name]
+    divisor *= SCALE
     kw = {k: (v // divisor if k in BATCH_KEYS[op] else v) for k, v in kw.items()}
     seed = workloads.SEEDS[op] + 1000 * rank
     if name == "opsa_f32":
@@ -247,14 +251,20 @@ def main():
     ap.add_argument("--workload", default="all", choices=["all"] + list(CASES))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--scale", type=int, default=1,
+                    help="divide every batch dimension by this (small cases for profiling)")
     args = ap.parse_args()
+    global SCALE
+    SCALE = max(1, args.scale)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     names = selected_cases(args.workload)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
-    config = {"workload": "fwd+vjp of " + ",".join(names) + " at the scaled per-GPU sizes",
-              "cases": {n: {**{k: int(v) for k, v in CASES[n][2].items()},
+    config = {"workload": "fwd+vjp of " + ",".join(names) + " at the scaled per-GPU sizes" +
+              (f" divided by {SCALE}" if SCALE > 1 else ""),
+              "cases": {n: {**{k: int(v) // (SCALE if k in BATCH_KEYS[CASES[n][0]] else 1)
+                               for k, v in CASES[n][2].items()},
                             "dtype": np.dtype(CASES[n][1]).name} for n in names},
               "sharding": "independent shard per rank (batch rows / output-segment ranges)",
               "cache": "inputs larger than L2 (126 MB) for every case"}

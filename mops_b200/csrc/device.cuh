@@ -120,6 +120,61 @@ __global__ void zero_if_unsorted(T* __restrict__ out, int64_t n, Status st) {
         out[i] = T(0);
 }
 
+
+// ---------------------------------------------------------------- asynchronous staging
+// Element-wise global -> shared copies that do not pass through registers (LDGSTS): a lane
+// can put a whole chunk in flight and go on; completion is tracked per committed group.
+template <int BYTES>
+__device__ __forceinline__ void cp_async(void* smem_dst, const void* global_src) {
+    const unsigned dst = static_cast<unsigned>(__cvta_generic_to_shared(smem_dst));
+    asm volatile("cp.async.ca.shared.global [%0], [%1], %2;\n" ::"r"(dst), "l"(global_src),
+                 "n"(BYTES)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
+// ---------------------------------------------------------------- segment offsets
+// offsets[r] = first position of the ascending index P whose value is >= r, for r in
+// [0, n_rows]; offsets[n_rows] = J. One thread per boundary between neighbouring entries:
+// entry j starts every row in (P[j-1], P[j]]. The same pass checks order and range, so the
+// kernels that consume the table can trust it, or skip their work when the index was not
+// sorted (saw_unsorted). Long runs of empty rows are filled by the whole warp.
+// Replaces the reference's first-occurrence pass (memset + kernel + device synchronisation
+// into a cached global buffer, mops/src/internal/cuda_first_occurences.cu:82-117).
+static __global__ void segment_offsets(const int32_t* __restrict__ P, int64_t J, int64_t n_rows,
+                                       int64_t* __restrict__ offsets, Status st) {
+    const int lane = threadIdx.x & 31;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    // Whole warps iterate together so that the cooperative fill below sees all 32 lanes.
+    const int64_t rounds = (J + 1 + stride - 1) / stride;
+    int64_t j = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    for (int64_t it = 0; it < rounds; it++, j += stride) {
+        int64_t prev = 0, cur = -1; // empty range by default
+        if (j <= J) {
+            const int64_t p_raw = j == 0 ? -1 : static_cast<int64_t>(__ldg(P + j - 1));
+            const int64_t c_raw = j == J ? n_rows : static_cast<int64_t>(__ldg(P + j));
+            if (j < J && (c_raw < 0 || c_raw >= n_rows)) report_bad_index(st, 0);
+            if (c_raw < p_raw) report_unsorted(st);
+            prev = p_raw < -1 ? -1 : (p_raw > n_rows ? n_rows : p_raw);
+            cur = c_raw < -1 ? -1 : (c_raw > n_rows ? n_rows : c_raw);
+        }
+        // rows prev+1 .. cur start at entry j
+        if (cur > prev) offsets[prev + 1] = j;
+        unsigned wide = __ballot_sync(kFullMask, cur > prev + 1);
+        while (wide) {
+            const int src = __ffs(wide) - 1;
+            wide &= wide - 1;
+            const int64_t lo = __shfl_sync(kFullMask, prev, src) + 2;
+            const int64_t hi = __shfl_sync(kFullMask, cur, src);
+            const int64_t at = __shfl_sync(kFullMask, j, src);
+            for (int64_t r = lo + lane; r <= hi; r += 32) offsets[r] = at;
+        }
+    }
+}
+
 __host__ __device__ constexpr int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
 } // namespace mops_b200

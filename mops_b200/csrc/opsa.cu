@@ -69,88 +69,144 @@ template <typename T, int N> __device__ __forceinline__ void store_vec(T* p, con
 struct FwdPlan {
     int TK, TL; // register tile per lane
     int LL, LK; // lane grid: LL lanes along l, LK along k (LL*LK <= 32)
-    int CH;     // entries staged per chunk
+    int CH;     // entries per staged chunk (<= 32)
+    int stage_scalars; // scalars of one stage: CH*L (B) [+ CH*L (W rows)] + CH*K (A) + padding
     size_t smem_per_warp;
 };
 
+// One warp per output row. The row's entries [offsets[r], offsets[r+1]) are contiguous in A
+// and B; they stream through two shared-memory stages with cp.async, the next chunk in
+// flight while the current one is consumed. Lane (lk, ll) keeps the TK x TL tile
+// k in [lk*TK, lk*TK+TK), l in [ll*TL, ll*TL+TL) of the K x L result in registers.
 template <typename T, int TK, int TL, bool WEIGHTED>
 __global__ void __launch_bounds__(kFwdWarps * 32)
-opsa_fwd_segmented(T* __restrict__ O, const T* __restrict__ A, const T* __restrict__ B,
-                   const T* __restrict__ W, const int32_t* __restrict__ PW,
-                   const int32_t* __restrict__ P, int64_t J, int K, int L, int64_t nO,
-                   FwdPlan plan, Status st) {
+opsa_fwd_rows(T* __restrict__ O, const T* __restrict__ A, const T* __restrict__ B,
+              const T* __restrict__ W, const int32_t* __restrict__ PW,
+              const int64_t* __restrict__ offsets, int K, int L, int64_t nO, FwdPlan plan,
+              Status st) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
+    if (saw_unsorted(st)) return; // the atomic kernel of the same call does the work
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t r = static_cast<int64_t>(blockIdx.x) * kFwdWarps + warp;
-
-    check_sorted_slice(P, J, nO, r, static_cast<int64_t>(gridDim.x) * kFwdWarps, lane, st);
     if (r >= nO) return;
 
     const int CH = plan.CH;
-    T* Bs = reinterpret_cast<T*>(smem_raw + warp * plan.smem_per_warp); // [CH][L], 16-byte aligned
-    T* As = Bs + static_cast<size_t>(CH) * L;                            // [CH][K]
-
-    int64_t begin, end;
-    warp_segment(P, J, static_cast<int32_t>(r), lane, begin, end);
+    T* stage0 = reinterpret_cast<T*>(smem_raw + warp * plan.smem_per_warp);
+    // stage layout: Bs [CH][L] | Ws [CH][L] (weighted only) | As [CH][K] | padding
+    const int a_off = (WEIGHTED ? 2 : 1) * CH * L;
+    const int64_t begin = offsets[r], end = offsets[r + 1];
 
     const int ll = lane % plan.LL, lk = lane / plan.LL;
-    const bool active = lk < plan.LK;
     T* Orow = O + r * K * L;
+
+    // Issues the copies of chunk [c0, c0+n) into stage `buf`. pw_lane: lane jj holds PW[c0+jj].
+    auto issue = [&](int buf, int64_t c0, int n, int32_t pw_lane) {
+        T* Bs = stage0 + buf * plan.stage_scalars;
+        const T* b = B + c0 * L;
+        for (int idx = lane; idx < n * L; idx += 32) cp_async<sizeof(T)>(Bs + idx, b + idx);
+        T* As = Bs + a_off;
+        const T* a = A + c0 * K;
+        for (int idx = lane; idx < n * K; idx += 32) cp_async<sizeof(T)>(As + idx, a + idx);
+        if (WEIGHTED) {
+            T* Ws = Bs + CH * L;
+            for (int jj = 0; jj < n; jj++) {
+                const int32_t pw = __shfl_sync(kFullMask, pw_lane, jj);
+                const T* w = W + static_cast<int64_t>(pw) * L;
+                for (int l = lane; l < L; l += 32) cp_async<sizeof(T)>(Ws + jj * L + l, w + l);
+            }
+        }
+        cp_async_commit();
+    };
+    auto load_pw = [&](int64_t c0, int n) -> int32_t {
+        int32_t pw = 0;
+        if (WEIGHTED && lane < n) {
+            pw = __ldg(PW + c0 + lane);
+            if (clamp_index(pw, static_cast<int32_t>(nO))) report_bad_index(st, 1);
+        }
+        return pw;
+    };
 
     for (int kb = 0; kb < K; kb += plan.LK * TK) {
         for (int lb = 0; lb < L; lb += plan.LL * TL) {
             const int k0 = kb + lk * TK, l0 = lb + ll * TL;
+            const bool active = lk < plan.LK && l0 < L && k0 < K;
             T acc[TK][TL];
 #pragma unroll
             for (int t = 0; t < TK; t++)
 #pragma unroll
                 for (int u = 0; u < TL; u++) acc[t][u] = T(0);
 
-            for (int64_t c0 = begin; c0 < end; c0 += CH) {
+            const int64_t total = end - begin;
+            const int nchunks = static_cast<int>((total + CH - 1) / CH);
+            __syncwarp();
+            if (nchunks > 0) {
+                const int n0 = static_cast<int>(total < CH ? total : CH);
+                issue(0, begin, n0, load_pw(begin, n0));
+            }
+            int32_t pw_next = 0;
+            if (nchunks > 1) {
+                const int64_t c1 = begin + CH;
+                pw_next = load_pw(c1, static_cast<int>(end - c1 < CH ? end - c1 : CH));
+            }
+            for (int c = 0; c < nchunks; c++) {
+                const int64_t c0 = begin + static_cast<int64_t>(c) * CH;
                 const int n = static_cast<int>(end - c0 < CH ? end - c0 : CH);
-                __syncwarp();
-                if (WEIGHTED) {
-                    for (int jj = 0; jj < n; jj++) {
-                        int32_t pw = __ldg(PW + c0 + jj);
-                        if (clamp_index(pw, static_cast<int32_t>(nO)) && lane == 0)
-                            report_bad_index(st, 1);
-                        const T* b = B + (c0 + jj) * L;
-                        const T* w = W + static_cast<int64_t>(pw) * L;
-                        for (int l = lane; l < L; l += 32) Bs[jj * L + l] = b[l] * __ldg(w + l);
+                if (c + 1 < nchunks) {
+                    const int64_t c1 = c0 + CH;
+                    issue((c + 1) & 1, c1, static_cast<int>(end - c1 < CH ? end - c1 : CH), pw_next);
+                    if (c + 2 < nchunks) {
+                        const int64_t c2 = c1 + CH;
+                        pw_next = load_pw(c2, static_cast<int>(end - c2 < CH ? end - c2 : CH));
                     }
+                    cp_async_wait<1>();
                 } else {
-                    const T* b = B + c0 * L;
-                    for (int idx = lane; idx < n * L; idx += 32) Bs[idx] = b[idx];
-                }
-                {
-                    const T* a = A + c0 * K;
-                    for (int idx = lane; idx < n * K; idx += 32) As[idx] = a[idx];
+                    cp_async_wait<0>();
                 }
                 __syncwarp();
-                if (active && l0 < L) {
+                if (active) {
+                    const T* pb = stage0 + (c & 1) * plan.stage_scalars + l0;
+                    const T* pa = pb - l0 + a_off + k0;
+#pragma unroll 2
                     for (int jj = 0; jj < n; jj++) {
                         T a[TK], b[TL];
+                        // k0+t beyond K reads the next row or the padding: those
+                        // accumulators are never stored.
 #pragma unroll
-                        for (int t = 0; t < TK; t++)
-                            a[t] = (k0 + t < K) ? As[jj * K + k0 + t] : T(0);
+                        for (int t = 0; t < TK; t++) a[t] = pa[t];
                         if (TL > 1) {
-                            load_vec<T, TL>(Bs + jj * L + l0, b);
+                            load_vec<T, TL>(pb, b);
                         } else {
-                            b[0] = Bs[jj * L + l0];
+                            b[0] = pb[0];
+                        }
+                        if (WEIGHTED) {
+                            T w[TL];
+                            if (TL > 1) {
+                                load_vec<T, TL>(pb + CH * L, w);
+                            } else {
+                                w[0] = pb[CH * L];
+                            }
+#pragma unroll
+                            for (int u = 0; u < TL; u++) b[u] *= w[u];
                         }
 #pragma unroll
                         for (int t = 0; t < TK; t++)
 #pragma unroll
                             for (int u = 0; u < TL; u++) acc[t][u] += a[t] * b[u];
+                        pa += K;
+                        pb += L;
                     }
                 }
+                __syncwarp(); // stage (c & 1) may be overwritten by the copy issued next round
             }
-            if (active && l0 < L) {
+            if (active) {
 #pragma unroll
                 for (int t = 0; t < TK; t++) {
                     if (k0 + t < K) {
-#pragma unroll
-                        for (int u = 0; u < TL; u++) Orow[(k0 + t) * L + l0 + u] = acc[t][u];
+                        if (TL > 1) {
+                            store_vec<T, TL>(Orow + (k0 + t) * L + l0, acc[t]);
+                        } else {
+                            Orow[(k0 + t) * L + l0] = acc[t][0];
+                        }
                     }
                 }
             }
@@ -189,7 +245,7 @@ __global__ void opsa_fwd_atomic(T* __restrict__ O, const T* __restrict__ A,
     }
 }
 
-template <typename T> FwdPlan plan_forward(int K, int L, bool l_aligned) {
+template <typename T, bool WEIGHTED> FwdPlan plan_forward(int K, int L, bool l_aligned) {
     FwdPlan p;
     const int widest = 16 / static_cast<int>(sizeof(T));
     p.TL = 1;
@@ -205,18 +261,25 @@ template <typename T> FwdPlan plan_forward(int K, int L, bool l_aligned) {
     p.LK = 32 / p.LL;
     if (p.LK > K) p.LK = K;
     p.TK = static_cast<int>(std::min<int64_t>(kMaxTK, ceil_div(K, p.LK)));
+    // Two stages per warp, about 9 KB together, so that three 8-warp blocks share an SM.
+    const size_t row_bytes = (static_cast<size_t>(K) + (WEIGHTED ? 2 : 1) * L) * sizeof(T);
     p.CH = 32;
-    const size_t row_bytes = static_cast<size_t>(K + L) * sizeof(T);
-    while (p.CH > 1 && p.CH * row_bytes > 12 * 1024) p.CH /= 2;
-    p.smem_per_warp = (p.CH * row_bytes + 15) / 16 * 16;
+    while (p.CH > 1 && 2 * p.CH * row_bytes > 9 * 1024) p.CH /= 2;
+    // padding: TK scalars so the unguarded A reads of the last row stay inside the stage;
+    // rounded so that every stage starts 16-byte aligned
+    const int per16 = 16 / static_cast<int>(sizeof(T));
+    int scalars = p.CH * (K + (WEIGHTED ? 2 : 1) * L) + kMaxTK;
+    scalars = (scalars + per16 - 1) / per16 * per16;
+    p.stage_scalars = scalars;
+    p.smem_per_warp = 2 * static_cast<size_t>(scalars) * sizeof(T);
     return p;
 }
 
 template <typename T, int TK, int TL, bool WEIGHTED>
 void launch_fwd_tile(const Call& call, const FwdPlan& plan, T* O, const T* A, const T* B,
-                     const T* W, const int32_t* PW, const int32_t* P, int64_t J, int K, int L,
+                     const T* W, const int32_t* PW, const int64_t* offsets, int K, int L,
                      int64_t nO) {
-    auto kernel = opsa_fwd_segmented<T, TK, TL, WEIGHTED>;
+    auto kernel = opsa_fwd_rows<T, TK, TL, WEIGHTED>;
     const size_t smem = plan.smem_per_warp * kFwdWarps;
     if (smem > 48 * 1024) {
         MOPS_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -224,7 +287,7 @@ void launch_fwd_tile(const Call& call, const FwdPlan& plan, T* O, const T* A, co
     }
     const int64_t blocks = ceil_div(nO, kFwdWarps);
     kernel<<<static_cast<unsigned>(blocks), kFwdWarps * 32, smem, call.stream>>>(
-        O, A, B, W, PW, P, J, K, L, nO, plan, call.status);
+        O, A, B, W, PW, offsets, K, L, nO, plan, call.status);
 }
 
 template <typename T, int TL, bool WEIGHTED, typename... Args>
@@ -251,26 +314,34 @@ void forward(const Call& call, T* O, const T* A, const T* B, const T* W, const i
         return;
     }
     const bool aligned = reinterpret_cast<uintptr_t>(O) % 16 == 0;
-    FwdPlan plan = plan_forward<T>(K, L, aligned);
+    FwdPlan plan = plan_forward<T, WEIGHTED>(K, L, aligned);
     const size_t smem = plan.smem_per_warp * kFwdWarps;
     const bool segmented = smem <= static_cast<size_t>(max_optin_smem(call.device));
     const int grid_generic = sm_count(call.device) * 8;
 
     if (segmented) {
+        // Segment table: call-scoped scratch, (nO + 1) offsets.
+        int64_t* offsets =
+            static_cast<int64_t*>(scratch_alloc(call, (nO + 1) * sizeof(int64_t)));
+        const int64_t pre_blocks = std::min<int64_t>(ceil_div(J + 1, 256), grid_generic * 4);
+        segment_offsets<<<static_cast<unsigned>(pre_blocks), 256, 0, call.stream>>>(
+            P, J, nO, offsets, call.status);
+        MOPS_CUDA_OK(cudaGetLastError());
         if constexpr (sizeof(T) == 8) {
             if (plan.TL == 2)
-                dispatch_tk<T, 2, WEIGHTED>(plan.TK, call, plan, O, A, B, W, PW, P, J, K, L, nO);
+                dispatch_tk<T, 2, WEIGHTED>(plan.TK, call, plan, O, A, B, W, PW, offsets, K, L, nO);
             else
-                dispatch_tk<T, 1, WEIGHTED>(plan.TK, call, plan, O, A, B, W, PW, P, J, K, L, nO);
+                dispatch_tk<T, 1, WEIGHTED>(plan.TK, call, plan, O, A, B, W, PW, offsets, K, L, nO);
         } else {
             if (plan.TL == 4)
-                dispatch_tk<T, 4, WEIGHTED>(plan.TK, call, plan, O, A, B, W, PW, P, J, K, L, nO);
+                dispatch_tk<T, 4, WEIGHTED>(plan.TK, call, plan, O, A, B, W, PW, offsets, K, L, nO);
             else if (plan.TL == 2)
-                dispatch_tk<T, 2, WEIGHTED>(plan.TK, call, plan, O, A, B, W, PW, P, J, K, L, nO);
+                dispatch_tk<T, 2, WEIGHTED>(plan.TK, call, plan, O, A, B, W, PW, offsets, K, L, nO);
             else
-                dispatch_tk<T, 1, WEIGHTED>(plan.TK, call, plan, O, A, B, W, PW, P, J, K, L, nO);
+                dispatch_tk<T, 1, WEIGHTED>(plan.TK, call, plan, O, A, B, W, PW, offsets, K, L, nO);
         }
         MOPS_CUDA_OK(cudaGetLastError());
+        scratch_free(call, offsets);
         bool need_fallback = true; // asynchronous calls cannot look: always enqueue
         if (call.wait) {
             wait_stream(call);
@@ -299,7 +370,7 @@ struct VjpPlan {
 };
 
 template <typename T, int KP, int VL, bool WEIGHTED>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 4)
 opsa_vjp_entries(T* __restrict__ gA, T* __restrict__ gB, T* __restrict__ gW,
                  const T* __restrict__ gO, const T* __restrict__ A, const T* __restrict__ B,
                  const T* __restrict__ W, const int32_t* __restrict__ PW,
@@ -315,20 +386,60 @@ opsa_vjp_entries(T* __restrict__ gA, T* __restrict__ gB, T* __restrict__ gW,
 
     const int64_t base = static_cast<int64_t>(blockIdx.x) * EPB;
     const int n = static_cast<int>(J - base < EPB ? J - base : EPB);
+    int32_t* pws = reinterpret_cast<int32_t*>(Ss + (nkc > 1 ? static_cast<size_t>(EPB) * Lp : 0));
 
-    for (int idx = tid; idx < n * K; idx += EPB) {
-        const int jj = idx / K, k = idx - jj * K;
-        As[jj * Kp + k] = A[base * K + idx];
-    }
-    for (int idx = tid; idx < n * L; idx += EPB) {
-        const int jj = idx / L, l = idx - jj * L;
-        Bs[jj * Lp + l] = B[base * L + idx];
-        if (WEIGHTED) {
-            int32_t pw = __ldg(PW + base + jj);
-            if (clamp_index(pw, static_cast<int32_t>(nO))) report_bad_index(st, 1);
-            Ws[jj * Lp + l] = __ldg(W + static_cast<int64_t>(pw) * L + l);
+    // Stage the entries' rows: element idx of the contiguous slice -> (entry, column), tracked
+    // incrementally (no division per element), copied asynchronously so that all of a
+    // thread's loads are in flight together.
+    {
+        const int dj = EPB / K, dk = EPB - dj * K;
+        int jj = tid / K, k = tid - jj * K;
+        const T* src = A + base * K;
+        for (int idx = tid; idx < n * K; idx += EPB) {
+            cp_async<sizeof(T)>(As + jj * Kp + k, src + idx);
+            jj += dj;
+            k += dk;
+            if (k >= K) {
+                k -= K;
+                jj++;
+            }
         }
     }
+    {
+        const int dj = EPB / L, dl = EPB - dj * L;
+        int jj = tid / L, l = tid - jj * L;
+        const T* src = B + base * L;
+        for (int idx = tid; idx < n * L; idx += EPB) {
+            cp_async<sizeof(T)>(Bs + jj * Lp + l, src + idx);
+            jj += dj;
+            l += dl;
+            if (l >= L) {
+                l -= L;
+                jj++;
+            }
+        }
+    }
+    if (WEIGHTED) {
+        if (tid < n) {
+            int32_t pw = __ldg(PW + base + tid);
+            if (clamp_index(pw, static_cast<int32_t>(nO))) report_bad_index(st, 1);
+            pws[tid] = pw;
+        }
+        __syncthreads();
+        const int dj = EPB / L, dl = EPB - dj * L;
+        int jj = tid / L, l = tid - jj * L;
+        for (int idx = tid; idx < n * L; idx += EPB) {
+            cp_async<sizeof(T)>(Ws + jj * Lp + l, W + static_cast<int64_t>(pws[jj]) * L + l);
+            jj += dj;
+            l += dl;
+            if (l >= L) {
+                l -= L;
+                jj++;
+            }
+        }
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
     __syncthreads();
 
     if (tid < n) {
@@ -340,6 +451,12 @@ opsa_vjp_entries(T* __restrict__ gA, T* __restrict__ gB, T* __restrict__ gW,
         T* w_row = Ws + tid * Lp;
         T* s_row = Ss + tid * Lp;
 
+        // Byte offset of gO row t of a chunk, kept in registers so that every gO load is
+        // "running pointer + 32-bit offset" instead of a 64-bit multiply-add per load.
+        unsigned t_off[KP];
+#pragma unroll
+        for (int t = 0; t < KP; t++) t_off[t] = static_cast<unsigned>(t) * L * sizeof(T);
+
         for (int kc = 0; kc < nkc; kc++) {
             const int kbase = kc * KP;
             T a[KP], ga[KP];
@@ -348,7 +465,8 @@ opsa_vjp_entries(T* __restrict__ gA, T* __restrict__ gB, T* __restrict__ gW,
                 a[t] = (kbase + t < K) ? a_row[kbase + t] : T(0);
                 ga[t] = T(0);
             }
-            for (int l0 = 0; l0 < L; l0 += VL) {
+            const char* g_l = reinterpret_cast<const char*>(g + static_cast<int64_t>(kbase) * L);
+            for (int l0 = 0; l0 < L; l0 += VL, g_l += VL * sizeof(T)) {
                 T b[VL], w[VL], bw[VL], s[VL];
 #pragma unroll
                 for (int u = 0; u < VL; u++) {
@@ -361,10 +479,11 @@ opsa_vjp_entries(T* __restrict__ gA, T* __restrict__ gB, T* __restrict__ gW,
                 for (int t = 0; t < KP; t++) {
                     if (kbase + t < K) {
                         T gv[VL];
+                        const T* src = reinterpret_cast<const T*>(g_l + t_off[t]);
                         if (VL > 1) {
-                            load_vec<T, VL>(g + static_cast<int64_t>(kbase + t) * L + l0, gv);
+                            load_vec<T, VL>(src, gv);
                         } else {
-                            gv[0] = __ldg(g + static_cast<int64_t>(kbase + t) * L + l0);
+                            gv[0] = __ldg(src);
                         }
 #pragma unroll
                         for (int u = 0; u < VL; u++) {
@@ -409,19 +528,31 @@ opsa_vjp_entries(T* __restrict__ gA, T* __restrict__ gB, T* __restrict__ gW,
     __syncthreads();
 
     if (gA != nullptr) {
+        const int dj = EPB / K, dk = EPB - dj * K;
+        int jj = tid / K, k = tid - jj * K;
+        T* dst = gA + base * K;
         for (int idx = tid; idx < n * K; idx += EPB) {
-            const int jj = idx / K, k = idx - jj * K;
-            gA[base * K + idx] = As[jj * Kp + k];
+            dst[idx] = As[jj * Kp + k];
+            jj += dj;
+            k += dk;
+            if (k >= K) {
+                k -= K;
+                jj++;
+            }
         }
     }
     if (gB != nullptr || (WEIGHTED && gW != nullptr)) {
+        const int dj = EPB / L, dl = EPB - dj * L;
+        int jj = tid / L, l = tid - jj * L;
         for (int idx = tid; idx < n * L; idx += EPB) {
-            const int jj = idx / L, l = idx - jj * L;
             if (gB != nullptr) gB[base * L + idx] = Bs[jj * Lp + l];
-            if (WEIGHTED && gW != nullptr) {
-                int32_t pw = __ldg(PW + base + jj);
-                if (!clamp_index(pw, static_cast<int32_t>(nO)))
-                    red_add(gW + static_cast<int64_t>(pw) * L + l, Ws[jj * Lp + l]);
+            if (WEIGHTED && gW != nullptr)
+                red_add(gW + static_cast<int64_t>(pws[jj]) * L + l, Ws[jj * Lp + l]);
+            jj += dj;
+            l += dl;
+            if (l >= L) {
+                l -= L;
+                jj++;
             }
         }
     }
@@ -481,14 +612,25 @@ void launch_vjp_tile(const Call& call, const VjpPlan& plan, int64_t J, Args... a
                                                                                    call.status);
 }
 
+// Register-tile width along K: exact for K <= 8, next even value up to 16, chunks of 16 above.
+inline int vjp_tile_k(int K) { return K <= 8 ? K : (K <= 16 ? (K + 1) / 2 * 2 : 16); }
+
 template <typename T, int VL, bool WEIGHTED, typename... Args>
 void dispatch_kp(int K, Args... args) {
-    if (K <= 4)
-        launch_vjp_tile<T, 4, VL, WEIGHTED>(args...);
-    else if (K <= 8)
-        launch_vjp_tile<T, 8, VL, WEIGHTED>(args...);
-    else
-        launch_vjp_tile<T, 16, VL, WEIGHTED>(args...);
+    switch (vjp_tile_k(K)) {
+    case 1: launch_vjp_tile<T, 1, VL, WEIGHTED>(args...); break;
+    case 2: launch_vjp_tile<T, 2, VL, WEIGHTED>(args...); break;
+    case 3: launch_vjp_tile<T, 3, VL, WEIGHTED>(args...); break;
+    case 4: launch_vjp_tile<T, 4, VL, WEIGHTED>(args...); break;
+    case 5: launch_vjp_tile<T, 5, VL, WEIGHTED>(args...); break;
+    case 6: launch_vjp_tile<T, 6, VL, WEIGHTED>(args...); break;
+    case 7: launch_vjp_tile<T, 7, VL, WEIGHTED>(args...); break;
+    case 8: launch_vjp_tile<T, 8, VL, WEIGHTED>(args...); break;
+    case 10: launch_vjp_tile<T, 10, VL, WEIGHTED>(args...); break;
+    case 12: launch_vjp_tile<T, 12, VL, WEIGHTED>(args...); break;
+    case 14: launch_vjp_tile<T, 14, VL, WEIGHTED>(args...); break;
+    default: launch_vjp_tile<T, 16, VL, WEIGHTED>(args...); break;
+    }
 }
 
 template <typename T, bool WEIGHTED>
@@ -509,7 +651,7 @@ void backward(const Call& call, T* gA, T* gB, T* gW, const T* gO, const T* A, co
     }
 
     VjpPlan plan;
-    const int KP = K <= 4 ? 4 : (K <= 8 ? 8 : 16);
+    const int KP = vjp_tile_k(K);
     plan.nkc = static_cast<int>(ceil_div(K, KP));
     plan.Kp = K | 1;
     plan.Lp = L | 1;
@@ -517,7 +659,7 @@ void backward(const Call& call, T* gA, T* gB, T* gW, const T* gO, const T* A, co
     const size_t per_entry = (plan.Kp + static_cast<size_t>(tiles_l) * plan.Lp) * sizeof(T);
     plan.threads = 128;
     while (plan.threads > 32 && plan.threads * per_entry > 96 * 1024) plan.threads /= 2;
-    plan.smem = plan.threads * per_entry;
+    plan.smem = plan.threads * (per_entry + sizeof(int32_t));
 
     const int widest = 16 / static_cast<int>(sizeof(T));
     int VL = 1;

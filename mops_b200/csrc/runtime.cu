@@ -111,9 +111,35 @@ void end_call(const Call& call, const char* operation, const char* const* index_
     }
 }
 
+namespace {
+// One stream-ordered pool per device that keeps freed blocks instead of returning them to the
+// driver at the next synchronisation (the default pool's behaviour, which would make every
+// call pay for mapping its scratch memory again).
+std::mutex g_pool_mutex;
+std::unordered_map<int, cudaMemPool_t> g_pools;
+
+cudaMemPool_t scratch_pool(int device) {
+    std::lock_guard<std::mutex> lock(g_pool_mutex);
+    auto it = g_pools.find(device);
+    if (it == g_pools.end()) {
+        cudaMemPoolProps props = {};
+        props.allocType = cudaMemAllocationTypePinned;
+        props.handleTypes = cudaMemHandleTypeNone;
+        props.location.type = cudaMemLocationTypeDevice;
+        props.location.id = device;
+        cudaMemPool_t pool = nullptr;
+        MOPS_CUDA_OK(cudaMemPoolCreate(&pool, &props));
+        uint64_t keep = UINT64_MAX;
+        MOPS_CUDA_OK(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
+        it = g_pools.emplace(device, pool).first;
+    }
+    return it->second;
+}
+} // namespace
+
 void* scratch_alloc(const Call& call, size_t bytes) {
     void* ptr = nullptr;
-    MOPS_CUDA_OK(cudaMallocAsync(&ptr, bytes, call.stream));
+    MOPS_CUDA_OK(cudaMallocFromPoolAsync(&ptr, bytes, scratch_pool(call.device), call.stream));
     return ptr;
 }
 

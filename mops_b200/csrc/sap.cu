@@ -9,195 +9,400 @@
 // shared-memory atomic per (row, triplet), and the three indices of a triplet packed into 8
 // bits each, which silently breaks for any dimension above 255.
 //
-// Here the batch dimension is the parallel one: lane = row. A block loads its rows of every
-// operand with coalesced reads and keeps them transposed in shared memory ([column][row],
-// padded), so that each triplet's operands are conflict-free reads at warp-uniform offsets,
-// and each lane owns its row of every output tile: the scatter needs no atomics at all.
-// Consecutive triplets with the same output column (indices_output is usually sorted) are
-// summed in a register and flushed once. Outputs go back with coalesced stores. Indices are
-// plain int32, any size.
+// Design. The batch dimension is the parallel one: lane = row. A block loads its rows of
+// every input with coalesced asynchronous copies and keeps them transposed in shared memory
+// ([column][row], padded), so that each triplet's operands are conflict-free reads at
+// warp-uniform offsets. The triplet list is the same for every row, so it is compiled once
+// per call by a one-block "plan" kernel into tables the row kernels stream through L1 as
+// 16-byte broadcasts: coefficients with ready-made shared-memory offsets, in three orders:
+//   * by k, cut into runs of equal output column, for O and ggO;
+//   * grouped by indices_A (stable), for gA and gA2;
+//   * grouped by indices_B (stable), for gB and gB2.
+// Every output element is then a plain sum over one group, accumulated in a register in
+// ascending k (the order of the reference CPU loops) and stored once: no atomics, no
+// read-modify-write chains in shared memory, no output tiles. Indices are range-checked by
+// the plan kernel; they are plain int32, any size.
+#include <algorithm>
+#include <cstring>
+
 #include "checks.hpp"
 #include "device.cuh"
 
 namespace mops_b200 {
 namespace {
 
-// A transposed operand tile in shared memory: element (row, col) at data[col * stride + row].
-template <typename T> struct Tile {
-    T* data;
-    int cols;
+constexpr int kPlanThreads = 256;
+constexpr uint32_t kFirstRun = 0x80000000u; // flag in run_col: first run of this output column
+
+// One triplet with its operand offsets already multiplied by the tile stride.
+template <typename T> struct alignas(16) Entry {
+    T c;
+    int32_t o1, o2;
 };
 
-template <typename T>
-__device__ __forceinline__ void tile_load(Tile<T> t, const T* __restrict__ M, int64_t i0, int64_t I,
-                                          int R, int stride) {
-    const int64_t rows = I - i0 < R ? I - i0 : R;
-    const int64_t valid = rows * t.cols;
-    const int total = R * t.cols;
-    const T* src = M == nullptr ? nullptr : M + i0 * t.cols;
-    for (int idx = threadIdx.x; idx < total; idx += blockDim.x) {
-        const int row = idx / t.cols, c = idx - row * t.cols;
-        t.data[c * stride + row] = (src != nullptr && idx < valid) ? src[idx] : T(0);
+template <typename T> struct Plan {
+    // by k: (c, A offset, B offset); runs of equal output column
+    Entry<T>* by_k;
+    int32_t* run_end; // [n_runs] one past the last k of the run
+    uint32_t* run_col; // [n_runs] output column | kFirstRun
+    int32_t* zero_cols; // [n_zero] output columns no triplet writes
+    // grouped by indices_A: (c, gO offset, B offset); grouped by indices_B: (c, gO offset, A offset)
+    Entry<T>* by_a;
+    Entry<T>* by_b;
+    int32_t* a_start; // [nA + 1]
+    int32_t* b_start; // [nB + 1]
+    int32_t* first_k; // [nO] scratch: smallest k writing each output column
+    int32_t* counts;  // [0] n_runs, [1] n_zero
+    int32_t* cursor;  // [max(nA, nB) + 1] scratch for the sorts
+};
+
+// Stable counting sort of k = 0..K-1 by key[k] in [0, nbins), done by one warp so that equal
+// keys keep ascending k. `emit(pos, k)` stores element k at sorted position pos.
+template <typename Emit>
+__device__ __forceinline__ void warp_stable_group(const int32_t* __restrict__ key, int nkeys,
+                                                  int K, int nbins, int32_t* start,
+                                                  int32_t* cursor, int lane, Emit emit) {
+    for (int b = lane; b <= nbins; b += 32) cursor[b] = 0;
+    __syncwarp();
+    for (int k = lane; k < K; k += 32) {
+        int32_t v = key[k];
+        clamp_index(v, nkeys);
+        atomicAdd(&cursor[v], 1);
+    }
+    __syncwarp();
+    int run = 0;
+    for (int b0 = 0; b0 <= nbins; b0 += 32) {
+        const int b = b0 + lane;
+        const int v = b < nbins ? cursor[b] : 0;
+        int incl = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(kFullMask, incl, o);
+            if (lane >= o) incl += t;
+        }
+        if (b <= nbins) {
+            start[b] = run + incl - v;
+            cursor[b] = run + incl - v;
+        }
+        run += __shfl_sync(kFullMask, incl, 31);
+    }
+    __syncwarp();
+    for (int k0 = 0; k0 < K; k0 += 32) {
+        const int k = k0 + lane;
+        const bool live = k < K;
+        int32_t v = live ? key[k] : -1 - lane; // distinct dummies for idle lanes
+        if (live) clamp_index(v, nkeys);
+        const unsigned same = __match_any_sync(kFullMask, v);
+        const int rank = __popc(same & ((1u << lane) - 1));
+        const int leader = __ffs(same) - 1;
+        int base = 0;
+        if (live && lane == leader) {
+            base = cursor[v];
+            cursor[v] = base + __popc(same);
+        }
+        base = __shfl_sync(kFullMask, base, leader);
+        if (live) emit(base + rank, k);
+        __syncwarp();
     }
 }
 
 template <typename T>
-__device__ __forceinline__ void tile_store(Tile<T> t, T* __restrict__ M, int64_t i0, int64_t I,
-                                           int R, int stride) {
-    if (M == nullptr) return;
-    const int64_t rows = I - i0 < R ? I - i0 : R;
-    const int64_t valid = rows * t.cols;
-    T* dst = M + i0 * t.cols;
-    for (int idx = threadIdx.x; idx < valid; idx += blockDim.x) {
-        const int row = idx / t.cols, c = idx - row * t.cols;
-        dst[idx] = t.data[c * stride + row];
+__global__ void __launch_bounds__(kPlanThreads)
+sap_plan(Plan<T> plan, const T* __restrict__ C, const int32_t* __restrict__ PA,
+         const int32_t* __restrict__ PB, const int32_t* __restrict__ PO, int K, int nA, int nB,
+         int nO, int stride, bool want_runs, bool want_groups, Status st) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    __shared__ int n_runs_shared;
+
+    // Range checks once for the whole call.
+    for (int k = tid; k < K; k += kPlanThreads) {
+        int32_t pa = PA[k], pb = PB[k], po = PO[k];
+        if (clamp_index(pa, nA)) report_bad_index(st, 0);
+        if (clamp_index(pb, nB)) report_bad_index(st, 1);
+        if (clamp_index(po, nO)) report_bad_index(st, 2);
     }
+    if (want_runs) {
+        for (int o = tid; o < nO; o += kPlanThreads) plan.first_k[o] = INT32_MAX;
+        __syncthreads();
+        for (int k = tid; k < K; k += kPlanThreads) {
+            int32_t pa = PA[k], pb = PB[k], po = PO[k];
+            clamp_index(pa, nA);
+            clamp_index(pb, nB);
+            clamp_index(po, nO);
+            plan.by_k[k] = Entry<T>{C[k], pa * stride, pb * stride};
+            // a run starts where the output column changes
+            int32_t prev = k == 0 ? -1 : PO[k - 1];
+            if (k > 0) clamp_index(prev, nO);
+            if (po != prev) atomicMin(&plan.first_k[po], k);
+        }
+        __syncthreads();
+        if (warp == 0) {
+            // compact the run starts, in order
+            int n_runs = 0;
+            for (int k0 = 0; k0 < K; k0 += 32) {
+                const int k = k0 + lane;
+                int32_t po = -1, prev = -1;
+                if (k < K) {
+                    po = PO[k];
+                    clamp_index(po, nO);
+                    if (k > 0) {
+                        prev = PO[k - 1];
+                        clamp_index(prev, nO);
+                    }
+                }
+                const bool starts = k < K && po != prev;
+                const unsigned m = __ballot_sync(kFullMask, starts);
+                if (starts) {
+                    const int r = n_runs + __popc(m & ((1u << lane) - 1));
+                    plan.run_col[r] = static_cast<uint32_t>(po) |
+                                      (plan.first_k[po] == k ? kFirstRun : 0u);
+                    if (r > 0) plan.run_end[r - 1] = k;
+                }
+                n_runs += __popc(m);
+            }
+            if (lane == 0) {
+                if (n_runs > 0) plan.run_end[n_runs - 1] = K;
+                plan.counts[0] = n_runs;
+                n_runs_shared = n_runs;
+            }
+        } else if (warp == 1) {
+            // output columns nobody writes
+            int n_zero = 0;
+            for (int o0 = 0; o0 < nO; o0 += 32) {
+                const int o = o0 + lane;
+                const bool empty = o < nO && plan.first_k[o] == INT32_MAX;
+                const unsigned m = __ballot_sync(kFullMask, empty);
+                if (empty) plan.zero_cols[n_zero + __popc(m & ((1u << lane) - 1))] = o;
+                n_zero += __popc(m);
+            }
+            if (lane == 0) plan.counts[1] = n_zero;
+        }
+    }
+    __syncthreads();
+    if (want_groups && warp == 0) {
+        warp_stable_group(PA, nA, K, nA, plan.a_start, plan.cursor, lane, [&](int pos, int k) {
+            int32_t pb = PB[k], po = PO[k];
+            clamp_index(pb, nB);
+            clamp_index(po, nO);
+            plan.by_a[pos] = Entry<T>{C[k], po * stride, pb * stride};
+        });
+        warp_stable_group(PB, nB, K, nB, plan.b_start, plan.cursor, lane, [&](int pos, int k) {
+            int32_t pa = PA[k], po = PO[k];
+            clamp_index(pa, nA);
+            clamp_index(po, nO);
+            plan.by_b[pos] = Entry<T>{C[k], po * stride, pa * stride};
+        });
+    }
+    (void)n_runs_shared;
+}
+
+// A transposed operand tile in shared memory: element (row, col) at data[col * stride + row].
+template <typename T>
+__device__ __forceinline__ void tile_load(T* tile, int cols, const T* __restrict__ M, int64_t i0,
+                                          int64_t I, int R, int stride) {
+    const int tid = threadIdx.x;
+    const int64_t rows = I - i0 < R ? I - i0 : R;
+    const int valid = static_cast<int>(rows) * cols, total = R * cols;
+    const T* src = M == nullptr ? nullptr : M + i0 * cols;
+    const int dr = R / cols, dc = R - dr * cols;
+    int row = tid / cols, c = tid - row * cols;
+    for (int idx = tid; idx < total; idx += R) {
+        if (src != nullptr && idx < valid)
+            cp_async<sizeof(T)>(tile + c * stride + row, src + idx);
+        else
+            tile[c * stride + row] = T(0);
+        row += dr;
+        c += dc;
+        if (c >= cols) {
+            c -= cols;
+            row++;
+        }
+    }
+}
+
+template <typename T> __device__ __forceinline__ Entry<T> fetch(const Entry<T>* p) {
+    static_assert(sizeof(Entry<T>) == 16, "table entries are read as one 16-byte broadcast");
+    const int4 raw = __ldg(reinterpret_cast<const int4*>(p));
+    Entry<T> e;
+    memcpy(&e, &raw, 16);
+    return e;
+}
+
+// Shared-memory entry read: one 16-byte broadcast.
+template <typename T> __device__ __forceinline__ Entry<T> fetch_shared(const Entry<T>* p) {
+    const int4 raw = *reinterpret_cast<const int4*>(p);
+    Entry<T> e;
+    memcpy(&e, &raw, 16);
+    return e;
+}
+
+template <bool IN_SMEM, typename T>
+__device__ __forceinline__ Entry<T> get(const Entry<T>* p) {
+    return IN_SMEM ? fetch_shared(p) : fetch(p);
+}
+
+// Copies a plan table into shared memory (the row tiles stream through L1 and would evict
+// it there); returns the pointer the row loop should read. `slot` is 16-byte aligned.
+template <bool IN_SMEM, typename T>
+__device__ __forceinline__ const Entry<T>* stage_table(const Entry<T>* table, int K,
+                                                       unsigned char* slot) {
+    if (!IN_SMEM) return table;
+    Entry<T>* dst = reinterpret_cast<Entry<T>*>(slot);
+    for (int k = threadIdx.x; k < K; k += blockDim.x) cp_async<16>(dst + k, table + k);
+    return dst;
+}
+
+__host__ __device__ inline size_t up16(size_t n) { return (n + 15) / 16 * 16; }
+
+template <typename T, bool IN_SMEM>
+__global__ void sap_fwd_rows(T* __restrict__ O, const T* __restrict__ A, const T* __restrict__ B,
+                             Plan<T> plan, int64_t I, int nA, int nB, int nO, int K) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int R = blockDim.x, S = R + 1, tid = threadIdx.x;
+    T* At = reinterpret_cast<T*>(smem_raw);
+    T* Bt = At + static_cast<size_t>(nA) * S;
+    unsigned char* tables = smem_raw + up16(static_cast<size_t>(nA + nB) * S * sizeof(T));
+    const int64_t i0 = static_cast<int64_t>(blockIdx.x) * R;
+    tile_load(At, nA, A, i0, I, R, S);
+    tile_load(Bt, nB, B, i0, I, R, S);
+    const Entry<T>* by_k = stage_table<IN_SMEM>(plan.by_k, K, tables);
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+    if (i0 + tid >= I) return;
+
+    const T* a = At + tid;
+    const T* b = Bt + tid;
+    T* o = O + (i0 + tid) * nO;
+    const int n_runs = plan.counts[0], n_zero = plan.counts[1];
+    int k = 0;
+    for (int r = 0; r < n_runs; r++) {
+        const int end = __ldg(plan.run_end + r);
+        const uint32_t col = __ldg(plan.run_col + r);
+        T acc = T(0);
+#pragma unroll 4
+        for (; k < end; k++) {
+            const Entry<T> e = get<IN_SMEM>(by_k + k);
+            acc += e.c * a[e.o1] * b[e.o2];
+        }
+        T* dst = o + (col & ~kFirstRun);
+        if (col & kFirstRun)
+            *dst = acc;
+        else
+            *dst += acc; // unsorted indices_output: a later run of an earlier column
+    }
+    for (int z = 0; z < n_zero; z++) o[__ldg(plan.zero_cols + z)] = T(0);
+}
+
+// gX[i, x] = sum over the group of x of (G[i, o1] * c) * Y[i, o2], for both groupings.
+template <bool IN_SMEM, typename T>
+__device__ __forceinline__ void grouped_sums(T* __restrict__ out_row, int n_groups,
+                                             const int32_t* __restrict__ start,
+                                             const Entry<T>* __restrict__ table, const T* g,
+                                             const T* y) {
+    int x = __ldg(start);
+    for (int grp = 0; grp < n_groups; grp++) {
+        const int end = __ldg(start + grp + 1);
+        T acc = T(0);
+#pragma unroll 4
+        for (; x < end; x++) {
+            const Entry<T> e = get<IN_SMEM>(table + x);
+            acc += g[e.o1] * e.c * y[e.o2];
+        }
+        out_row[grp] = acc;
+    }
+}
+
+template <typename T, bool IN_SMEM>
+__global__ void sap_vjp_rows(T* __restrict__ gA, T* __restrict__ gB, const T* __restrict__ gO,
+                             const T* __restrict__ A, const T* __restrict__ B, Plan<T> plan,
+                             int64_t I, int nA, int nB, int nO, int K) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int R = blockDim.x, S = R + 1, tid = threadIdx.x;
+    T* At = reinterpret_cast<T*>(smem_raw);
+    T* Bt = At + static_cast<size_t>(nA) * S;
+    T* Gt = Bt + static_cast<size_t>(nB) * S;
+    unsigned char* tables = smem_raw + up16(static_cast<size_t>(nA + nB + nO) * S * sizeof(T));
+    const int64_t i0 = static_cast<int64_t>(blockIdx.x) * R;
+    if (gB != nullptr) tile_load(At, nA, A, i0, I, R, S);
+    if (gA != nullptr) tile_load(Bt, nB, B, i0, I, R, S);
+    tile_load(Gt, nO, gO, i0, I, R, S);
+    const Entry<T>* by_a = stage_table<IN_SMEM>(plan.by_a, gA != nullptr ? K : 0, tables);
+    const Entry<T>* by_b = stage_table<IN_SMEM>(plan.by_b, gB != nullptr ? K : 0,
+                                                tables + static_cast<size_t>(K) * sizeof(Entry<T>));
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+    if (i0 + tid >= I) return;
+    const int64_t i = i0 + tid;
+    if (gA != nullptr)
+        grouped_sums<IN_SMEM>(gA + i * nA, nA, plan.a_start, by_a, Gt + tid, Bt + tid);
+    if (gB != nullptr)
+        grouped_sums<IN_SMEM>(gB + i * nB, nB, plan.b_start, by_b, Gt + tid, At + tid);
+}
+
+template <typename T, bool IN_SMEM>
+__global__ void sap_vjp_vjp_rows(T* __restrict__ ggO, T* __restrict__ gA2, T* __restrict__ gB2,
+                                 const T* __restrict__ ggA, const T* __restrict__ ggB,
+                                 const T* __restrict__ gO, const T* __restrict__ A,
+                                 const T* __restrict__ B, Plan<T> plan, int64_t I, int nA, int nB,
+                                 int nO, int K) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int R = blockDim.x, S = R + 1, tid = threadIdx.x;
+    T* At = reinterpret_cast<T*>(smem_raw);
+    T* Bt = At + static_cast<size_t>(nA) * S;
+    T* Gt = Bt + static_cast<size_t>(nB) * S;
+    T* hAt = Gt + static_cast<size_t>(nO) * S;
+    T* hBt = hAt + static_cast<size_t>(nA) * S;
+    const int64_t i0 = static_cast<int64_t>(blockIdx.x) * R;
+    tile_load(At, nA, A, i0, I, R, S);
+    tile_load(Bt, nB, B, i0, I, R, S);
+    tile_load(Gt, nO, gO, i0, I, R, S);
+    tile_load(hAt, nA, ggA, i0, I, R, S); // a missing second-order input reads as zeros
+    tile_load(hBt, nB, ggB, i0, I, R, S);
+    unsigned char* tables =
+        smem_raw + up16(static_cast<size_t>(2 * nA + 2 * nB + nO) * S * sizeof(T));
+    const size_t table_bytes = static_cast<size_t>(K) * sizeof(Entry<T>);
+    const Entry<T>* by_k = stage_table<IN_SMEM>(plan.by_k, ggO != nullptr ? K : 0, tables);
+    const Entry<T>* by_a = stage_table<IN_SMEM>(plan.by_a, gA2 != nullptr ? K : 0, tables + table_bytes);
+    const Entry<T>* by_b = stage_table<IN_SMEM>(plan.by_b, gB2 != nullptr ? K : 0, tables + 2 * table_bytes);
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+    if (i0 + tid >= I) return;
+    const int64_t i = i0 + tid;
+    if (ggO != nullptr) {
+        const T *a = At + tid, *b = Bt + tid, *ha = hAt + tid, *hb = hBt + tid;
+        T* o = ggO + i * nO;
+        const int n_runs = plan.counts[0], n_zero = plan.counts[1];
+        int k = 0;
+        for (int r = 0; r < n_runs; r++) {
+            const int end = __ldg(plan.run_end + r);
+            const uint32_t col = __ldg(plan.run_col + r);
+            T acc = T(0);
+            for (; k < end; k++) {
+                const Entry<T> e = get<IN_SMEM>(by_k + k);
+                acc += ha[e.o1] * b[e.o2] * e.c;
+                acc += hb[e.o2] * a[e.o1] * e.c;
+            }
+            T* dst = o + (col & ~kFirstRun);
+            if (col & kFirstRun)
+                *dst = acc;
+            else
+                *dst += acc;
+        }
+        for (int z = 0; z < n_zero; z++) o[__ldg(plan.zero_cols + z)] = T(0);
+    }
+    // gA2[i,pa] = sum c ggB[i,pb] gO[i,po];  gB2[i,pb] = sum c ggA[i,pa] gO[i,po]
+    if (gA2 != nullptr)
+        grouped_sums<IN_SMEM>(gA2 + i * nA, nA, plan.a_start, by_a, Gt + tid, hBt + tid);
+    if (gB2 != nullptr)
+        grouped_sums<IN_SMEM>(gB2 + i * nB, nB, plan.b_start, by_b, Gt + tid, hAt + tid);
 }
 
 struct Triplet {
     int32_t pa, pb, po;
 };
-
-// Reads triplet k (warp-uniform), clamping bad indices; block 0 reports them.
-__device__ __forceinline__ Triplet read_triplet(const int32_t* __restrict__ PA,
-                                                const int32_t* __restrict__ PB,
-                                                const int32_t* __restrict__ PO, int64_t k, int nA,
-                                                int nB, int nO, const Status& st) {
-    Triplet t{__ldg(PA + k), __ldg(PB + k), __ldg(PO + k)};
-    const bool ba = clamp_index(t.pa, nA), bb = clamp_index(t.pb, nB), bo = clamp_index(t.po, nO);
-    if ((ba || bb || bo) && blockIdx.x == 0 && threadIdx.x == 0) {
-        if (ba) report_bad_index(st, 0);
-        if (bb) report_bad_index(st, 1);
-        if (bo) report_bad_index(st, 2);
-    }
-    return t;
-}
-
-template <typename T>
-__global__ void sap_fwd_tile(T* __restrict__ O, const T* __restrict__ A, const T* __restrict__ B,
-                             const T* __restrict__ C, const int32_t* __restrict__ PA,
-                             const int32_t* __restrict__ PB, const int32_t* __restrict__ PO,
-                             int64_t I, int nA, int nB, int nO, int64_t K, Status st) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    const int R = blockDim.x, S = R + 1, tid = threadIdx.x;
-    Tile<T> At{reinterpret_cast<T*>(smem_raw), nA};
-    Tile<T> Bt{At.data + static_cast<size_t>(nA) * S, nB};
-    Tile<T> Ot{Bt.data + static_cast<size_t>(nB) * S, nO};
-    const int64_t i0 = static_cast<int64_t>(blockIdx.x) * R;
-
-    tile_load(At, A, i0, I, R, S);
-    tile_load(Bt, B, i0, I, R, S);
-    for (int idx = tid; idx < nO * S; idx += R) Ot.data[idx] = T(0);
-    __syncthreads();
-
-    const T* a = At.data + tid;
-    const T* b = Bt.data + tid;
-    T* o = Ot.data + tid;
-    int cur = -1;
-    T acc = T(0);
-    for (int64_t k = 0; k < K; k++) {
-        const Triplet t = read_triplet(PA, PB, PO, k, nA, nB, nO, st);
-        const T v = __ldg(C + k) * a[t.pa * S] * b[t.pb * S];
-        if (t.po == cur) {
-            acc += v;
-        } else {
-            if (cur >= 0) o[cur * S] += acc;
-            cur = t.po;
-            acc = v;
-        }
-    }
-    if (cur >= 0) o[cur * S] += acc;
-    __syncthreads();
-    tile_store(Ot, O, i0, I, R, S);
-}
-
-template <typename T>
-__global__ void sap_vjp_tile(T* __restrict__ gA, T* __restrict__ gB, const T* __restrict__ gO,
-                             const T* __restrict__ A, const T* __restrict__ B,
-                             const T* __restrict__ C, const int32_t* __restrict__ PA,
-                             const int32_t* __restrict__ PB, const int32_t* __restrict__ PO,
-                             int64_t I, int nA, int nB, int nO, int64_t K, Status st) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    const int R = blockDim.x, S = R + 1, tid = threadIdx.x;
-    Tile<T> At{reinterpret_cast<T*>(smem_raw), nA};
-    Tile<T> Bt{At.data + static_cast<size_t>(nA) * S, nB};
-    Tile<T> Gt{Bt.data + static_cast<size_t>(nB) * S, nO};
-    Tile<T> gAt{Gt.data + static_cast<size_t>(nO) * S, nA};
-    Tile<T> gBt{gAt.data + static_cast<size_t>(nA) * S, nB};
-    const int64_t i0 = static_cast<int64_t>(blockIdx.x) * R;
-
-    tile_load(At, A, i0, I, R, S);
-    tile_load(Bt, B, i0, I, R, S);
-    tile_load(Gt, gO, i0, I, R, S);
-    for (int idx = tid; idx < (nA + nB) * S; idx += R) gAt.data[idx] = T(0); // gAt and gBt are adjacent
-    __syncthreads();
-
-    const T *a = At.data + tid, *b = Bt.data + tid, *g = Gt.data + tid;
-    T *ga = gAt.data + tid, *gb = gBt.data + tid;
-    const bool want_a = gA != nullptr, want_b = gB != nullptr;
-    for (int64_t k = 0; k < K; k++) {
-        const Triplet t = read_triplet(PA, PB, PO, k, nA, nB, nO, st);
-        const T gc = g[t.po * S] * __ldg(C + k);
-        if (want_a) ga[t.pa * S] += gc * b[t.pb * S];
-        if (want_b) gb[t.pb * S] += gc * a[t.pa * S];
-    }
-    __syncthreads();
-    tile_store(gAt, gA, i0, I, R, S);
-    tile_store(gBt, gB, i0, I, R, S);
-}
-
-template <typename T>
-__global__ void sap_vjp_vjp_tile(T* __restrict__ ggO, T* __restrict__ gA2, T* __restrict__ gB2,
-                                 const T* __restrict__ ggA, const T* __restrict__ ggB,
-                                 const T* __restrict__ gO, const T* __restrict__ A,
-                                 const T* __restrict__ B, const T* __restrict__ C,
-                                 const int32_t* __restrict__ PA, const int32_t* __restrict__ PB,
-                                 const int32_t* __restrict__ PO, int64_t I, int nA, int nB, int nO,
-                                 int64_t K, Status st) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    const int R = blockDim.x, S = R + 1, tid = threadIdx.x;
-    T* p = reinterpret_cast<T*>(smem_raw);
-    auto take = [&](int cols) {
-        Tile<T> t{p, cols};
-        p += static_cast<size_t>(cols) * S;
-        return t;
-    };
-    Tile<T> At = take(nA), Bt = take(nB), Gt = take(nO), hAt = take(nA), hBt = take(nB);
-    Tile<T> ggOt = take(nO), gA2t = take(nA), gB2t = take(nB); // outputs, adjacent
-    const int64_t i0 = static_cast<int64_t>(blockIdx.x) * R;
-
-    tile_load(At, A, i0, I, R, S);
-    tile_load(Bt, B, i0, I, R, S);
-    tile_load(Gt, gO, i0, I, R, S);
-    tile_load(hAt, ggA, i0, I, R, S); // a missing second-order input reads as zeros
-    tile_load(hBt, ggB, i0, I, R, S);
-    for (int idx = tid; idx < (nO + nA + nB) * S; idx += R) ggOt.data[idx] = T(0);
-    __syncthreads();
-
-    const T *a = At.data + tid, *b = Bt.data + tid, *g = Gt.data + tid;
-    const T *ha = hAt.data + tid, *hb = hBt.data + tid;
-    T *o = ggOt.data + tid, *oa = gA2t.data + tid, *ob = gB2t.data + tid;
-    const bool have_a = ggA != nullptr, have_b = ggB != nullptr;
-    for (int64_t k = 0; k < K; k++) {
-        const Triplet t = read_triplet(PA, PB, PO, k, nA, nB, nO, st);
-        const T c = __ldg(C + k);
-        const T go = g[t.po * S];
-        if (have_a) {
-            const T h = ha[t.pa * S];
-            o[t.po * S] += h * b[t.pb * S] * c;
-            ob[t.pb * S] += h * go * c;
-        }
-        if (have_b) {
-            const T h = hb[t.pb * S];
-            o[t.po * S] += h * a[t.pa * S] * c;
-            oa[t.pa * S] += h * go * c;
-        }
-    }
-    __syncthreads();
-    tile_store(ggOt, ggO, i0, I, R, S);
-    tile_store(gA2t, gA2, i0, I, R, S);
-    tile_store(gB2t, gB2, i0, I, R, S);
-}
 
 // Any width: one thread per row working directly on its rows in global memory. Used when the
 // tiles of 32 rows do not fit in shared memory.
@@ -249,15 +454,24 @@ __global__ void sap_wide(int level, T* __restrict__ out0, T* __restrict__ out1,
     }
 }
 
-// Rows per block: the largest of 128/64/32 whose tiles stay under ~100 KB (so that at least
-// two blocks share an SM); 0 if not even 32 rows fit in the opt-in limit.
-template <typename T> int rows_per_block(const Call& call, int cols, size_t* smem) {
-    for (int R : {128, 64, 32}) {
-        const size_t bytes = static_cast<size_t>(cols) * (R + 1) * sizeof(T);
-        const size_t limit = R == 32 ? static_cast<size_t>(max_optin_smem(call.device)) : 100 * 1024;
-        if (bytes <= limit) {
-            *smem = bytes;
-            return R;
+// Rows per block and whether the plan tables go to shared memory. Prefers the tables in
+// shared memory and a footprint that lets two blocks share an SM; returns 0 rows if not even
+// 32 rows of tiles fit in the opt-in limit (then the global-memory kernel is used).
+template <typename T>
+int rows_per_block(const Call& call, int cols, int n_tables, int64_t K, size_t* smem,
+                   bool* tables_in_smem) {
+    const size_t limit = static_cast<size_t>(max_optin_smem(call.device));
+    const size_t tables = static_cast<size_t>(n_tables) * K * sizeof(Entry<T>);
+    for (int pass = 0; pass < 3; pass++) {
+        for (int R : {128, 64, 32}) {
+            const size_t tiles = up16(static_cast<size_t>(cols) * (R + 1) * sizeof(T));
+            const size_t total = tiles + (pass < 2 ? tables : 0);
+            const size_t cap = pass == 0 ? 112 * 1024 : limit;
+            if (total <= cap) {
+                *smem = total;
+                *tables_in_smem = pass < 2;
+                return R;
+            }
         }
     }
     return 0;
@@ -267,6 +481,44 @@ template <typename Kernel> void allow_smem(Kernel kernel, size_t smem) {
     if (smem > 48 * 1024)
         MOPS_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           static_cast<int>(smem)));
+}
+
+// Allocates the call-scoped plan tables and runs the plan kernel.
+template <typename T>
+Plan<T> make_plan(const Call& call, void** scratch, const T* C, const int32_t* PA,
+                  const int32_t* PB, const int32_t* PO, int64_t K, int nA, int nB, int nO,
+                  int stride, bool want_runs, bool want_groups) {
+    const size_t table = up16(static_cast<size_t>(K) * sizeof(Entry<T>));
+    const size_t ints_k = up16(static_cast<size_t>(K) * sizeof(int32_t));
+    const size_t ints_o = up16(static_cast<size_t>(nO) * sizeof(int32_t));
+    const size_t ints_a = up16((static_cast<size_t>(nA) + 1) * sizeof(int32_t));
+    const size_t ints_b = up16((static_cast<size_t>(nB) + 1) * sizeof(int32_t));
+    const size_t total = 3 * table + 2 * ints_k + 2 * ints_o + 2 * ints_a + 2 * ints_b + 16 +
+                         std::max(ints_a, ints_b);
+    unsigned char* p = static_cast<unsigned char*>(scratch_alloc(call, total));
+    *scratch = p;
+    Plan<T> plan;
+    auto take = [&](size_t bytes) {
+        unsigned char* q = p;
+        p += bytes;
+        return q;
+    };
+    plan.by_k = reinterpret_cast<Entry<T>*>(take(table));
+    plan.by_a = reinterpret_cast<Entry<T>*>(take(table));
+    plan.by_b = reinterpret_cast<Entry<T>*>(take(table));
+    plan.run_end = reinterpret_cast<int32_t*>(take(ints_k));
+    plan.run_col = reinterpret_cast<uint32_t*>(take(ints_k));
+    plan.zero_cols = reinterpret_cast<int32_t*>(take(ints_o));
+    plan.first_k = reinterpret_cast<int32_t*>(take(ints_o));
+    plan.a_start = reinterpret_cast<int32_t*>(take(ints_a));
+    plan.b_start = reinterpret_cast<int32_t*>(take(ints_b));
+    plan.counts = reinterpret_cast<int32_t*>(take(16));
+    plan.cursor = reinterpret_cast<int32_t*>(take(std::max(ints_a, ints_b)));
+    sap_plan<T><<<1, kPlanThreads, 0, call.stream>>>(plan, C, PA, PB, PO, static_cast<int>(K), nA,
+                                                     nB, nO, stride, want_runs, want_groups,
+                                                     call.status);
+    MOPS_CUDA_OK(cudaGetLastError());
+    return plan;
 }
 
 const char* const kIndexNames[] = {"indices_A", "indices_B", "indices_output"};
@@ -285,6 +537,7 @@ void check_sap_shapes(const mops::Tensor<scalar_t, 2>& output, const mops::Tenso
     fits_int32(A.shape[1], "A.shape[1]", op);
     fits_int32(B.shape[1], "B.shape[1]", op);
     fits_int32(output.shape[1], "output.shape[1]", op);
+    fits_int32(C.shape[0], "C.shape[0]", op);
 }
 
 } // namespace
@@ -314,12 +567,19 @@ void mops::cuda::sparse_accumulation_of_products(Tensor<scalar_t, 2> output, Ten
         return;
     }
     size_t smem = 0;
-    const int R = rows_per_block<scalar_t>(call, nA + nB + nO, &smem);
+    bool in_smem = false;
+    const int R = rows_per_block<scalar_t>(call, nA + nB, 1, K, &smem, &in_smem);
     if (R > 0) {
-        allow_smem(sap_fwd_tile<scalar_t>, smem);
-        sap_fwd_tile<scalar_t><<<static_cast<unsigned>(ceil_div(I, R)), R, smem, call.stream>>>(
-            output.data, A.data, B.data, C.data, indices_A.data, indices_B.data,
-            indices_output.data, I, nA, nB, nO, K, call.status);
+        void* scratch = nullptr;
+        Plan<scalar_t> plan = make_plan<scalar_t>(call, &scratch, C.data, indices_A.data,
+                                                  indices_B.data, indices_output.data, K, nA, nB,
+                                                  nO, R + 1, true, false);
+        auto kernel = in_smem ? sap_fwd_rows<scalar_t, true> : sap_fwd_rows<scalar_t, false>;
+        allow_smem(kernel, smem);
+        kernel<<<static_cast<unsigned>(ceil_div(I, R)), R, smem, call.stream>>>(
+            output.data, A.data, B.data, plan, I, nA, nB, nO, static_cast<int>(K));
+        MOPS_CUDA_OK(cudaGetLastError());
+        scratch_free(call, scratch);
     } else {
         sap_wide<scalar_t><<<static_cast<unsigned>(ceil_div(I, 128)), 128, 0, call.stream>>>(
             0, output.data, nullptr, nullptr, nullptr, nullptr, nullptr, A.data, B.data, C.data,
@@ -356,12 +616,20 @@ void mops::cuda::sparse_accumulation_of_products_vjp(
         return;
     }
     size_t smem = 0;
-    const int R = rows_per_block<scalar_t>(call, 2 * nA + 2 * nB + nO, &smem);
+    bool in_smem = false;
+    const int R = rows_per_block<scalar_t>(call, nA + nB + nO, 2, K, &smem, &in_smem);
     if (R > 0) {
-        allow_smem(sap_vjp_tile<scalar_t>, smem);
-        sap_vjp_tile<scalar_t><<<static_cast<unsigned>(ceil_div(I, R)), R, smem, call.stream>>>(
-            grad_A.data, grad_B.data, grad_output.data, A.data, B.data, C.data, indices_A.data,
-            indices_B.data, indices_output.data, I, nA, nB, nO, K, call.status);
+        void* scratch = nullptr;
+        Plan<scalar_t> plan = make_plan<scalar_t>(call, &scratch, C.data, indices_A.data,
+                                                  indices_B.data, indices_output.data, K, nA, nB,
+                                                  nO, R + 1, false, true);
+        auto kernel = in_smem ? sap_vjp_rows<scalar_t, true> : sap_vjp_rows<scalar_t, false>;
+        allow_smem(kernel, smem);
+        kernel<<<static_cast<unsigned>(ceil_div(I, R)), R, smem, call.stream>>>(
+            grad_A.data, grad_B.data, grad_output.data, A.data, B.data, plan, I, nA, nB, nO,
+            static_cast<int>(K));
+        MOPS_CUDA_OK(cudaGetLastError());
+        scratch_free(call, scratch);
     } else {
         sap_wide<scalar_t><<<static_cast<unsigned>(ceil_div(I, 128)), 128, 0, call.stream>>>(
             1, grad_A.data, grad_B.data, nullptr, nullptr, nullptr, grad_output.data, A.data,
@@ -407,14 +675,22 @@ void mops::cuda::sparse_accumulation_of_products_vjp_vjp(
         return;
     }
     size_t smem = 0;
-    const int R = rows_per_block<scalar_t>(call, 3 * nA + 3 * nB + 2 * nO, &smem);
+    bool in_smem = false;
+    const int R = rows_per_block<scalar_t>(call, 2 * nA + 2 * nB + nO, 3, K, &smem, &in_smem);
     if (R > 0) {
-        allow_smem(sap_vjp_vjp_tile<scalar_t>, smem);
-        sap_vjp_vjp_tile<scalar_t>
-            <<<static_cast<unsigned>(ceil_div(I, R)), R, smem, call.stream>>>(
-                grad_grad_output.data, grad_A_2.data, grad_B_2.data, grad_grad_A.data,
-                grad_grad_B.data, grad_output.data, A.data, B.data, C.data, indices_A.data,
-                indices_B.data, indices_output.data, I, nA, nB, nO, K, call.status);
+        void* scratch = nullptr;
+        Plan<scalar_t> plan = make_plan<scalar_t>(call, &scratch, C.data, indices_A.data,
+                                                  indices_B.data, indices_output.data, K, nA, nB,
+                                                  nO, R + 1, true, true);
+        auto kernel =
+            in_smem ? sap_vjp_vjp_rows<scalar_t, true> : sap_vjp_vjp_rows<scalar_t, false>;
+        allow_smem(kernel, smem);
+        kernel<<<static_cast<unsigned>(ceil_div(I, R)), R, smem, call.stream>>>(
+            grad_grad_output.data, grad_A_2.data, grad_B_2.data, grad_grad_A.data,
+            grad_grad_B.data, grad_output.data, A.data, B.data, plan, I, nA, nB, nO,
+            static_cast<int>(K));
+        MOPS_CUDA_OK(cudaGetLastError());
+        scratch_free(call, scratch);
     } else {
         sap_wide<scalar_t><<<static_cast<unsigned>(ceil_div(I, 128)), 128, 0, call.stream>>>(
             2, grad_grad_output.data, grad_A_2.data, grad_B_2.data, grad_grad_A.data,
