@@ -8,13 +8,21 @@
 // reads and shared-memory atomics.
 //
 // Here the batch dimension is the parallel one. A block takes 32 consecutive rows of A,
-// loads them with coalesced reads and keeps them transposed in shared memory ([factor][row],
-// padded), so that "factor P[j,k] of my row" is a conflict-free read at a warp-uniform
-// offset: lane = row. Monomials are warp-uniform; their indices and coefficients come
-// through L1 as broadcasts. Forward: the block's warps split the monomials and add their
-// partial sums at the end. VJP: each lane owns its row of the gradient tile in shared
-// memory, so the scatter into gA needs no atomics; the K leave-one-out products are built
-// from running prefix and suffix products (2K multiplications instead of K^2).
+// loads them with coalesced asynchronous copies and keeps them transposed in shared memory
+// ([factor][row], padded), so that "factor P[j,k] of my row" is a conflict-free read at a
+// warp-uniform offset: lane = row. The monomial table is the same for every row, so a
+// one-block plan kernel compiles it once per call into packed tables of ready-made
+// shared-memory offsets, which the row kernels stream through double-buffered shared-memory
+// stages (cp.async) and read as 16-byte broadcasts:
+//   forward: the monomials in order; the block's four warps take interleaved monomials and
+//            add their partial sums at the end;
+//   VJP:     the (j,k) incidences grouped by the factor n they differentiate (stable
+//            counting sort), each with the offsets of the monomial's other K-1 factors. Then
+//            gA[i,n] is a plain sum over group n, accumulated in a register and stored once:
+//            no atomics and no read-modify-write chain; the four warps take disjoint ranges
+//            of n, balanced by incidence count.
+#include <algorithm>
+
 #include "checks.hpp"
 #include "device.cuh"
 
@@ -23,8 +31,45 @@ namespace {
 
 constexpr int kRows = 32;       // batch rows per block (one per lane)
 constexpr int kPad = kRows + 1; // shared-memory row stride of a transposed tile
-constexpr int kFwdWarps = 4;
+constexpr int kWarps = 4;
 constexpr int kMaxOrder = 10;
+constexpr int kPlanThreads = 256;
+constexpr int kFwdChunk = 256; // monomials per forward stage (whole block)
+constexpr int kVjpChunk = 64;  // incidences per VJP stage (per warp)
+
+// Offsets of one table row are padded to a power-of-two count (or 12) so that a row is read
+// with 4-, 8- or 16-byte broadcasts.
+__host__ __device__ constexpr int padded(int n) {
+    return n <= 0 ? 0 : n <= 1 ? 1 : n <= 2 ? 2 : n <= 4 ? 4 : n <= 8 ? 8 : 12;
+}
+
+template <int NP> __device__ __forceinline__ void read_offsets(const int32_t* p, int (&o)[NP > 0 ? NP : 1]) {
+    if constexpr (NP == 1) {
+        o[0] = p[0];
+    } else if constexpr (NP == 2) {
+        const int2 v = *reinterpret_cast<const int2*>(p);
+        o[0] = v.x;
+        o[1] = v.y;
+    } else if constexpr (NP >= 4) {
+#pragma unroll
+        for (int q = 0; q < NP / 4; q++) {
+            const int4 v = *reinterpret_cast<const int4*>(p + 4 * q);
+            o[4 * q + 0] = v.x;
+            o[4 * q + 1] = v.y;
+            o[4 * q + 2] = v.z;
+            o[4 * q + 3] = v.w;
+        }
+    }
+}
+
+struct HpePlan {
+    int32_t* fwd_offs; // [J][padded(K)]      tile offsets of every monomial's factors
+    int32_t* vjp_offs; // [J*K][padded(K-1)]  grouped by differentiated factor
+    void* vjp_coef;    // [J*K] scalars       C[j] of each incidence
+    int32_t* n_start;  // [N + 1]             first incidence of every factor
+    int32_t* split;    // [kWarps + 1]        factor ranges of the block's warps
+    int32_t* cursor;   // [N + 1] scratch
+};
 
 // Loads rows [i0, i0+32) of a row-major [I][N] matrix into tile[n*kPad + row].
 template <typename T>
@@ -32,99 +77,293 @@ __device__ __forceinline__ void load_tile_transposed(T* tile, const T* __restric
                                                      int64_t I, int N, int tid, int nthreads) {
     const int64_t rows = I - i0 < kRows ? I - i0 : kRows;
     const int total = kRows * N;
-    const int64_t valid = rows * N;
+    const int valid = static_cast<int>(rows) * N;
     const T* src = M + i0 * N;
+    const int dr = nthreads / N, dn = nthreads - dr * N;
+    int row = tid / N, n = tid - row * N;
     for (int idx = tid; idx < total; idx += nthreads) {
-        const int row = idx / N, n = idx - row * N;
-        tile[n * kPad + row] = idx < valid ? src[idx] : T(0);
+        if (idx < valid)
+            cp_async<sizeof(T)>(tile + n * kPad + row, src + idx);
+        else
+            tile[n * kPad + row] = T(0);
+        row += dr;
+        n += dn;
+        if (n >= N) {
+            n -= N;
+            row++;
+        }
+    }
+}
+
+// Builds the packed tables. One block; the grouping is a stable counting sort done by warp 0
+// (equal factors keep ascending (j,k), so the sums are reproducible).
+template <typename T>
+__global__ void __launch_bounds__(kPlanThreads)
+hpe_plan(HpePlan plan, const T* __restrict__ C, const int32_t* __restrict__ P, int J, int K,
+         int N, bool want_fwd, bool want_vjp, Status st) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int KP = padded(K), KQ = padded(K - 1);
+    const int M = J * K;
+    for (int x = tid; x < M; x += kPlanThreads) {
+        int32_t p = P[x];
+        if (clamp_index(p, N)) report_bad_index(st, 0);
+    }
+    if (want_fwd) {
+        for (int x = tid; x < J * KP; x += kPlanThreads) {
+            const int j = x / KP, k = x - j * KP;
+            int32_t p = 0;
+            if (k < K) {
+                p = P[j * K + k];
+                clamp_index(p, N);
+            }
+            plan.fwd_offs[x] = p * kPad;
+        }
+    }
+    if (!want_vjp || M == 0) return;
+    T* coef = static_cast<T*>(plan.vjp_coef);
+    if (warp == 0) {
+        for (int b = lane; b <= N; b += 32) plan.cursor[b] = 0;
+        __syncwarp();
+        for (int x = lane; x < M; x += 32) {
+            int32_t p = P[x];
+            clamp_index(p, N);
+            atomicAdd(&plan.cursor[p], 1);
+        }
+        __syncwarp();
+        int run = 0;
+        for (int b0 = 0; b0 <= N; b0 += 32) {
+            const int b = b0 + lane;
+            const int v = b < N ? plan.cursor[b] : 0;
+            int incl = v;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_up_sync(kFullMask, incl, o);
+                if (lane >= o) incl += t;
+            }
+            if (b <= N) {
+                plan.n_start[b] = run + incl - v;
+                plan.cursor[b] = run + incl - v;
+            }
+            run += __shfl_sync(kFullMask, incl, 31);
+        }
+        __syncwarp();
+        for (int x0 = 0; x0 < M; x0 += 32) {
+            const int x = x0 + lane;
+            const bool live = x < M;
+            int32_t key = -1 - lane;
+            if (live) {
+                key = P[x];
+                clamp_index(key, N);
+            }
+            const unsigned same = __match_any_sync(kFullMask, key);
+            const int rank = __popc(same & ((1u << lane) - 1));
+            const int leader = __ffs(same) - 1;
+            int base = 0;
+            if (live && lane == leader) {
+                base = plan.cursor[key];
+                plan.cursor[key] = base + __popc(same);
+            }
+            base = __shfl_sync(kFullMask, base, leader);
+            if (live) {
+                const int pos = base + rank, j = x / K, k = x - j * K;
+                coef[pos] = C[j];
+                int q = 0;
+                for (int l = 0; l < K; l++) {
+                    if (l == k) continue;
+                    int32_t p = P[j * K + l];
+                    clamp_index(p, N);
+                    plan.vjp_offs[pos * KQ + q++] = p * kPad;
+                }
+                for (; q < KQ; q++) plan.vjp_offs[pos * KQ + q] = 0;
+            }
+            __syncwarp();
+        }
+        // Factor ranges of the four warps, balanced by incidence count.
+        __syncwarp();
+        if (lane <= kWarps) {
+            int n = 0;
+            if (lane == kWarps) {
+                n = N;
+            } else if (lane > 0) {
+                const int target = static_cast<int>(static_cast<int64_t>(M) * lane / kWarps);
+                int lo = 0, hi = N; // first n with n_start[n] >= target
+                while (lo < hi) {
+                    const int mid = (lo + hi) / 2;
+                    if (plan.n_start[mid] < target)
+                        lo = mid + 1;
+                    else
+                        hi = mid;
+                }
+                n = lo;
+            }
+            plan.split[lane] = n;
+        }
     }
 }
 
 template <typename T, int K>
-__global__ void __launch_bounds__(kFwdWarps * 32)
-hpe_fwd_tile(T* __restrict__ O, const T* __restrict__ A, const T* __restrict__ C,
-             const int32_t* __restrict__ P, int64_t I, int N, int64_t J, Status st) {
+__global__ void __launch_bounds__(kWarps * 32)
+hpe_fwd_rows(T* __restrict__ O, const T* __restrict__ A, const T* __restrict__ C,
+             const int32_t* __restrict__ offs_table, int64_t I, int N, int J) {
+    constexpr int KP = padded(K);
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    T* At = reinterpret_cast<T*>(smem_raw); // [N][kPad]
-    T* partial = At + static_cast<size_t>(N) * kPad; // [kFwdWarps][32]
+    // layout: stage 0 offsets | stage 1 offsets | stage 0 coef | stage 1 coef | A tile | partial
+    int32_t* offs_s = reinterpret_cast<int32_t*>(smem_raw);
+    constexpr int kStageInts = kFwdChunk * (KP > 0 ? KP : 1);
+    T* coef_s = reinterpret_cast<T*>(offs_s + 2 * kStageInts);
+    T* At = coef_s + 2 * kFwdChunk;
+    T* partial = At + static_cast<size_t>(N) * kPad;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int64_t i0 = static_cast<int64_t>(blockIdx.x) * kRows;
-    const bool reporter = blockIdx.x == 0;
 
-    load_tile_transposed(At, A, i0, I, N, tid, kFwdWarps * 32);
-    __syncthreads();
+    auto issue = [&](int stage, int m0) {
+        const int mc = J - m0 < kFwdChunk ? J - m0 : kFwdChunk;
+        if constexpr (KP > 0) {
+            // KP ints per monomial; the table rows are 4*KP bytes, copied in the widest unit
+            constexpr int unit = KP >= 4 ? 16 : KP * 4;
+            constexpr int per_row = KP * 4 / unit;
+            const char* src = reinterpret_cast<const char*>(offs_table + static_cast<int64_t>(m0) * KP);
+            char* dst = reinterpret_cast<char*>(offs_s + stage * kStageInts);
+            for (int x = tid; x < mc * per_row; x += kWarps * 32)
+                cp_async<unit>(dst + x * unit, src + x * unit);
+        }
+        for (int x = tid; x < mc; x += kWarps * 32)
+            cp_async<sizeof(T)>(coef_s + stage * kFwdChunk + x, C + m0 + x);
+        cp_async_commit();
+    };
+
+    load_tile_transposed(At, A, i0, I, N, tid, kWarps * 32);
+    if (J > 0) issue(0, 0);
 
     const T* col = At + lane;
     T acc = T(0);
-#pragma unroll 4
-    for (int64_t j = warp; j < J; j += kFwdWarps) {
-        T prod = __ldg(C + j);
-#pragma unroll
-        for (int k = 0; k < K; k++) {
-            int32_t p = __ldg(P + j * K + k);
-            if (clamp_index(p, N) && reporter && lane == 0) report_bad_index(st, 0);
-            prod *= col[p * kPad];
+    int stage = 0;
+    for (int m0 = 0; m0 < J; m0 += kFwdChunk, stage ^= 1) {
+        const int mc = J - m0 < kFwdChunk ? J - m0 : kFwdChunk;
+        if (m0 + kFwdChunk < J) {
+            issue(stage ^ 1, m0 + kFwdChunk);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
         }
-        acc += prod;
+        __syncthreads();
+        const int32_t* offs = offs_s + stage * kStageInts;
+        const T* coef = coef_s + stage * kFwdChunk;
+#pragma unroll 4
+        for (int m = warp; m < mc; m += kWarps) {
+            T prod = coef[m];
+            if constexpr (K > 0) {
+                int o[KP > 0 ? KP : 1];
+                read_offsets<KP>(offs + m * KP, o);
+#pragma unroll
+                for (int k = 0; k < K; k++) prod *= col[o[k]];
+            }
+            acc += prod;
+        }
+        __syncthreads(); // the stage is overwritten by the copy issued next round
+    }
+    if (J == 0) {
+        cp_async_wait<0>();
+        __syncthreads();
     }
     partial[warp * 32 + lane] = acc;
     __syncthreads();
     if (warp == 0 && i0 + lane < I) {
         T sum = partial[lane];
 #pragma unroll
-        for (int w = 1; w < kFwdWarps; w++) sum += partial[w * 32 + lane];
+        for (int w = 1; w < kWarps; w++) sum += partial[w * 32 + lane];
         O[i0 + lane] = sum;
     }
 }
 
 template <typename T, int K>
-__global__ void __launch_bounds__(32)
-hpe_vjp_tile(T* __restrict__ gA, const T* __restrict__ gO, const T* __restrict__ A,
-             const T* __restrict__ C, const int32_t* __restrict__ P, int64_t I, int N, int64_t J,
-             Status st) {
+__global__ void __launch_bounds__(kWarps * 32)
+hpe_vjp_rows(T* __restrict__ gA, const T* __restrict__ gO, const T* __restrict__ A, HpePlan plan,
+             int64_t I, int N) {
+    constexpr int KQ = padded(K - 1);
+    constexpr int kRowInts = KQ > 0 ? KQ : 1;
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    T* At = reinterpret_cast<T*>(smem_raw);          // [N][kPad]
-    T* Gt = At + static_cast<size_t>(N) * kPad;      // [N][kPad]
-    const int lane = threadIdx.x;
+    // layout: per warp 2 stages of (offsets, coefficients) | A tile
+    constexpr int kStageInts = kVjpChunk * kRowInts;
+    int32_t* offs_all = reinterpret_cast<int32_t*>(smem_raw);
+    T* coef_all = reinterpret_cast<T*>(offs_all + kWarps * 2 * kStageInts);
+    T* At = coef_all + kWarps * 2 * kVjpChunk;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int64_t i0 = static_cast<int64_t>(blockIdx.x) * kRows;
-    const bool reporter = blockIdx.x == 0;
+    int32_t* offs_w = offs_all + warp * 2 * kStageInts;
+    T* coef_w = coef_all + warp * 2 * kVjpChunk;
+    const T* coef_table = static_cast<const T*>(plan.vjp_coef);
 
-    load_tile_transposed(At, A, i0, I, N, lane, 32);
-    for (int idx = lane; idx < N * kPad; idx += 32) Gt[idx] = T(0);
-    __syncwarp();
+    load_tile_transposed(At, A, i0, I, N, tid, kWarps * 32);
+    cp_async_commit();
 
-    const T go = i0 + lane < I ? gO[i0 + lane] : T(0);
-    const T* a_col = At + lane;
-    T* g_col = Gt + lane;
-    for (int64_t j = 0; j < J; j++) {
-        int32_t p[K > 0 ? K : 1];
-        T a[K > 0 ? K : 1];
-#pragma unroll
-        for (int k = 0; k < K; k++) {
-            p[k] = __ldg(P + j * K + k);
-            if (clamp_index(p[k], N) && reporter && lane == 0) report_bad_index(st, 0);
-            a[k] = a_col[p[k] * kPad];
+    const int n_lo = __ldg(plan.split + warp), n_hi = __ldg(plan.split + warp + 1);
+    const int x_lo = __ldg(plan.n_start + n_lo), x_hi = __ldg(plan.n_start + n_hi);
+
+    auto issue = [&](int stage, int x0) {
+        const int xc = x_hi - x0 < kVjpChunk ? x_hi - x0 : kVjpChunk;
+        if constexpr (KQ > 0) {
+            constexpr int unit = KQ >= 4 ? 16 : kRowInts * 4;
+            constexpr int per_row = kRowInts * 4 / unit;
+            const char* src = reinterpret_cast<const char*>(plan.vjp_offs + static_cast<int64_t>(x0) * KQ);
+            char* dst = reinterpret_cast<char*>(offs_w + stage * kStageInts);
+            for (int y = lane; y < xc * per_row; y += 32) cp_async<unit>(dst + y * unit, src + y * unit);
         }
-        // suffix[k] = prod_{l > k} a[l]
-        T suffix[K > 0 ? K : 1];
-        if constexpr (K > 0) suffix[K - 1] = T(1);
-#pragma unroll
-        for (int k = K - 2; k >= 0; k--) suffix[k] = suffix[k + 1] * a[k + 1];
-        T prefix = __ldg(C + j) * go; // times prod_{l < k} a[l]
-#pragma unroll
-        for (int k = 0; k < K; k++) {
-            g_col[p[k] * kPad] += prefix * suffix[k];
-            prefix *= a[k];
+        for (int y = lane; y < xc; y += 32)
+            cp_async<sizeof(T)>(coef_w + stage * kVjpChunk + y, coef_table + x0 + y);
+        cp_async_commit();
+    };
+    if (x_lo < x_hi) issue(0, x_lo);
+    // The A tile was committed first: waiting for "all but the newest group" covers it.
+    if (x_lo < x_hi)
+        cp_async_wait<1>();
+    else
+        cp_async_wait<0>();
+    __syncthreads();
+
+    const bool live = i0 + lane < I;
+    const T go = live ? gO[i0 + lane] : T(0);
+    const T* col = At + lane;
+    T* out = gA + (i0 + lane) * N;
+
+    int n = n_lo;
+    int end_n = n < n_hi ? __ldg(plan.n_start + n + 1) : x_hi;
+    T acc = T(0);
+    int stage = 0;
+    for (int x0 = x_lo; x0 < x_hi; x0 += kVjpChunk, stage ^= 1) {
+        const int xc = x_hi - x0 < kVjpChunk ? x_hi - x0 : kVjpChunk;
+        if (x0 + kVjpChunk < x_hi) {
+            issue(stage ^ 1, x0 + kVjpChunk);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
         }
+        __syncwarp();
+        const int32_t* offs = offs_w + stage * kStageInts;
+        const T* coef = coef_w + stage * kVjpChunk;
+        for (int y = 0; y < xc; y++) {
+            const int x = x0 + y;
+            while (x == end_n) { // group n is complete (possibly empty)
+                if (live) out[n] = go * acc;
+                acc = T(0);
+                n++;
+                end_n = __ldg(plan.n_start + n + 1);
+            }
+            T prod = coef[y];
+            if constexpr (KQ > 0) {
+                int o[kRowInts];
+                read_offsets<KQ>(offs + y * KQ, o);
+#pragma unroll
+                for (int k = 0; k < K - 1; k++) prod *= col[o[k]];
+            }
+            acc += prod;
+        }
+        __syncwarp(); // the stage is overwritten by the copy issued next round
     }
-    __syncwarp();
-
-    const int64_t rows = I - i0 < kRows ? I - i0 : kRows;
-    const int64_t valid = rows * N;
-    T* dst = gA + i0 * N;
-    for (int idx = lane; idx < kRows * N; idx += 32) {
-        const int row = idx / N, n = idx - row * N;
-        if (idx < valid) dst[idx] = Gt[n * kPad + row];
+    // Close the last group and any empty groups after it.
+    for (; n < n_hi; n++) {
+        if (live) out[n] = go * acc;
+        acc = T(0);
     }
 }
 
@@ -178,26 +417,84 @@ __global__ void hpe_vjp_wide(T* __restrict__ gA, const T* __restrict__ gO,
     }
 }
 
-template <typename T, int K>
-void launch_fwd(const Call& call, size_t smem, T* O, const T* A, const T* C, const int32_t* P,
-                int64_t I, int N, int64_t J) {
-    auto kernel = hpe_fwd_tile<T, K>;
-    if (smem > 48 * 1024)
-        MOPS_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          static_cast<int>(smem)));
-    kernel<<<static_cast<unsigned>(ceil_div(I, kRows)), kFwdWarps * 32, smem, call.stream>>>(
-        O, A, C, P, I, N, J, call.status);
+template <typename T, int K> size_t fwd_smem(int N) {
+    constexpr int KP = padded(K);
+    return 2 * kFwdChunk * (KP > 0 ? KP : 1) * sizeof(int32_t) + 2 * kFwdChunk * sizeof(T) +
+           (static_cast<size_t>(N) * kPad + kWarps * 32) * sizeof(T);
+}
+
+template <typename T, int K> size_t vjp_smem(int N) {
+    constexpr int KQ = padded(K - 1);
+    return kWarps * 2 * kVjpChunk * (KQ > 0 ? KQ : 1) * sizeof(int32_t) +
+           kWarps * 2 * kVjpChunk * sizeof(T) + static_cast<size_t>(N) * kPad * sizeof(T);
+}
+
+// Allocates the call-scoped tables and runs the plan kernel.
+template <typename T>
+HpePlan make_plan(const Call& call, void** scratch, const T* C, const int32_t* P, int64_t J,
+                  int K, int N, bool want_fwd, bool want_vjp) {
+    auto up = [](size_t n) { return (n + 255) / 256 * 256; };
+    const int KP = padded(K), KQ = padded(K - 1);
+    const size_t M = static_cast<size_t>(J) * K;
+    const size_t b_fwd = want_fwd ? up(static_cast<size_t>(J) * (KP > 0 ? KP : 1) * sizeof(int32_t)) : 0;
+    const size_t b_voffs = want_vjp ? up(M * (KQ > 0 ? KQ : 1) * sizeof(int32_t)) : 0;
+    const size_t b_vcoef = want_vjp ? up(M * sizeof(T)) : 0;
+    const size_t b_n = up((static_cast<size_t>(N) + 1) * sizeof(int32_t));
+    unsigned char* p = static_cast<unsigned char*>(
+        scratch_alloc(call, b_fwd + b_voffs + b_vcoef + 2 * b_n + 256));
+    *scratch = p;
+    HpePlan plan;
+    plan.fwd_offs = reinterpret_cast<int32_t*>(p);
+    p += b_fwd;
+    plan.vjp_offs = reinterpret_cast<int32_t*>(p);
+    p += b_voffs;
+    plan.vjp_coef = p;
+    p += b_vcoef;
+    plan.n_start = reinterpret_cast<int32_t*>(p);
+    p += b_n;
+    plan.cursor = reinterpret_cast<int32_t*>(p);
+    p += b_n;
+    plan.split = reinterpret_cast<int32_t*>(p);
+    hpe_plan<T><<<1, kPlanThreads, 0, call.stream>>>(plan, C, P, static_cast<int>(J), K, N,
+                                                     want_fwd, want_vjp, call.status);
+    MOPS_CUDA_OK(cudaGetLastError());
+    return plan;
 }
 
 template <typename T, int K>
-void launch_vjp(const Call& call, size_t smem, T* gA, const T* gO, const T* A, const T* C,
-                const int32_t* P, int64_t I, int N, int64_t J) {
-    auto kernel = hpe_vjp_tile<T, K>;
+void launch_fwd(const Call& call, T* O, const T* A, const T* C, const int32_t* P, int64_t I,
+                int N, int64_t J) {
+    const size_t smem = fwd_smem<T, K>(N);
+    void* scratch = nullptr;
+    HpePlan plan = make_plan<T>(call, &scratch, C, P, J, K, N, true, false);
+    auto kernel = hpe_fwd_rows<T, K>;
     if (smem > 48 * 1024)
         MOPS_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           static_cast<int>(smem)));
-    kernel<<<static_cast<unsigned>(ceil_div(I, kRows)), 32, smem, call.stream>>>(
-        gA, gO, A, C, P, I, N, J, call.status);
+    kernel<<<static_cast<unsigned>(ceil_div(I, kRows)), kWarps * 32, smem, call.stream>>>(
+        O, A, C, plan.fwd_offs, I, N, static_cast<int>(J));
+    MOPS_CUDA_OK(cudaGetLastError());
+    scratch_free(call, scratch);
+}
+
+template <typename T, int K>
+void launch_vjp(const Call& call, T* gA, const T* gO, const T* A, const T* C, const int32_t* P,
+                int64_t I, int N, int64_t J) {
+    if (K == 0 || J == 0) { // no factor depends on A
+        MOPS_CUDA_OK(cudaMemsetAsync(gA, 0, I * N * sizeof(T), call.stream));
+        return;
+    }
+    const size_t smem = vjp_smem<T, K>(N);
+    void* scratch = nullptr;
+    HpePlan plan = make_plan<T>(call, &scratch, C, P, J, K, N, false, true);
+    auto kernel = hpe_vjp_rows<T, K>;
+    if (smem > 48 * 1024)
+        MOPS_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          static_cast<int>(smem)));
+    kernel<<<static_cast<unsigned>(ceil_div(I, kRows)), kWarps * 32, smem, call.stream>>>(
+        gA, gO, A, plan, I, N);
+    MOPS_CUDA_OK(cudaGetLastError());
+    scratch_free(call, scratch);
 }
 
 #define MOPS_B200_ORDER_SWITCH(K, CALL)                                                            \
@@ -254,10 +551,10 @@ void mops::cuda::homogeneous_polynomial_evaluation(Tensor<scalar_t, 1> output,
         end_call(call, op.c_str(), kIndexNames, 1);
         return;
     }
-    const size_t smem = (static_cast<size_t>(N) * kPad + kFwdWarps * 32) * sizeof(scalar_t);
+    fits_int32(C.shape[0] * std::max<size_t>(indices_A.shape[1], 1) * 16, "the monomial table", op);
+    const size_t smem = fwd_smem<scalar_t, kMaxOrder>(N); // the largest any order needs
     if (smem <= static_cast<size_t>(max_optin_smem(call.device))) {
-#define CALL(KK)                                                                                   \
-    launch_fwd<scalar_t, KK>(call, smem, output.data, A.data, C.data, indices_A.data, I, N, J)
+#define CALL(KK) launch_fwd<scalar_t, KK>(call, output.data, A.data, C.data, indices_A.data, I, N, J)
         MOPS_B200_ORDER_SWITCH(K, CALL)
 #undef CALL
     } else {
@@ -284,11 +581,12 @@ void mops::cuda::homogeneous_polynomial_evaluation_vjp(Tensor<scalar_t, 2> grad_
     const int N = static_cast<int>(A.shape[1]), K = static_cast<int>(indices_A.shape[1]);
     if (I == 0 || N == 0) return;
     Call call = begin_call();
-    const size_t smem = 2 * static_cast<size_t>(N) * kPad * sizeof(scalar_t);
+    fits_int32(C.shape[0] * std::max<size_t>(indices_A.shape[1], 1) * 16, "the monomial table", op);
+    const size_t smem = vjp_smem<scalar_t, kMaxOrder>(N);
     if (smem <= static_cast<size_t>(max_optin_smem(call.device))) {
 #define CALL(KK)                                                                                   \
-    launch_vjp<scalar_t, KK>(call, smem, grad_A.data, grad_output.data, A.data, C.data,            \
-                             indices_A.data, I, N, J)
+    launch_vjp<scalar_t, KK>(call, grad_A.data, grad_output.data, A.data, C.data, indices_A.data,  \
+                             I, N, J)
         MOPS_B200_ORDER_SWITCH(K, CALL)
 #undef CALL
     } else {
