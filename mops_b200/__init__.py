@@ -82,6 +82,7 @@ class _Arena:
                             "(there is no CPU implementation to fall back to)")
         self.torch = torch
         self.numpy = isinstance(first, np.ndarray)
+        self.pinned = (not self.numpy) and (not first.is_cuda) and first.is_pinned()
         if self.numpy or not first.is_cuda:
             self.device = torch.device("cuda", torch.cuda.current_device())
             self.host = True
@@ -111,10 +112,17 @@ class _Arena:
         return self.torch.empty(tuple(int(s) for s in shape), dtype=self.dtype, device=self.device)
 
     def back(self, t):
+        """Result to where the inputs live. Pinned host inputs get pinned host results (from
+        torch's caching host allocator), so the copy back runs at full PCIe speed."""
         if t is None:
             return None
         if not self.host:
             return t
+        if self.pinned:
+            out = self.torch.empty(t.shape, dtype=t.dtype, device="cpu", pin_memory=True)
+            out.copy_(t, non_blocking=True)
+            self.torch.cuda.current_stream(self.device).synchronize()
+            return out
         t = t.cpu()
         return t.numpy() if self.numpy else t
 

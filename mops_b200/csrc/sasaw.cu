@@ -58,6 +58,8 @@ __global__ void __launch_bounds__(kBuildThreads)
 sasaw_group_coupling(Coupling<T> cp, const T* __restrict__ C, const int32_t* __restrict__ M1,
                      const int32_t* __restrict__ M2, const int32_t* __restrict__ M3, int nA,
                      int nW1, int nO1, Status st) {
+    // cells are numbered m3 * stride + m2; stride > nW1 leaves empty padding cells
+    const int cell_stride = cp.ncell / nO1;
     extern __shared__ int32_t cursor[]; // [ncell]
     __shared__ int32_t chunk_sum[kBuildThreads];
     const int tid = threadIdx.x, N = cp.N, ncell = cp.ncell;
@@ -69,7 +71,7 @@ sasaw_group_coupling(Coupling<T> cp, const T* __restrict__ C, const int32_t* __r
         if (clamp_index(m1, nA)) report_bad_index(st, kBitM1);
         if (clamp_index(m2, nW1)) report_bad_index(st, kBitM2);
         if (clamp_index(m3, nO1)) report_bad_index(st, kBitM3);
-        atomicAdd(&cursor[m3 * nW1 + m2], 1);
+        atomicAdd(&cursor[m3 * cell_stride + m2], 1);
     }
     __syncthreads();
     // Exclusive scan of the per-cell counts: each thread scans a contiguous chunk.
@@ -101,7 +103,7 @@ sasaw_group_coupling(Coupling<T> cp, const T* __restrict__ C, const int32_t* __r
         int32_t m2 = M2[n], m3 = M3[n];
         clamp_index(m2, nW1);
         clamp_index(m3, nO1);
-        cp.order[atomicAdd(&cursor[m3 * nW1 + m2], 1)] = n;
+        cp.order[atomicAdd(&cursor[m3 * cell_stride + m2], 1)] = n;
     }
     __syncthreads();
     // Entries of one cell in ascending n (they were placed in arbitrary order).
@@ -311,6 +313,267 @@ __global__ void sasaw_vjp(T* __restrict__ gA, T* __restrict__ gB, T* __restrict_
     }
 }
 
+// ---------------------------------------------------------------------------- fast kernels
+// For W.shape[1] <= 16. TP is W.shape[1] rounded up to a multiple of four: cells are numbered
+// m3 * TP + m2, so a row of T_e is read with 16-byte broadcasts, and the edge's W values
+// W[J_e, :, b] sit in registers (one load each per edge instead of one per cell).
+
+template <typename T> struct FastShared {
+    T* C;
+    T* warp_base;
+    int32_t* M1;
+    int32_t* cell;
+    int32_t* start;
+};
+
+__host__ __device__ inline size_t round4(size_t n) { return (n + 3) / 4 * 4; }
+
+template <typename T>
+__device__ __forceinline__ FastShared<T> carve_fast(unsigned char* raw, const Coupling<T>& cp,
+                                                    size_t per_warp, int warps, bool with_cell) {
+    FastShared<T> s;
+    s.C = reinterpret_cast<T*>(raw);
+    s.warp_base = s.C + round4(cp.N);
+    T* end = s.warp_base + per_warp * warps;
+    s.M1 = reinterpret_cast<int32_t*>(end);
+    s.cell = s.M1 + cp.N;
+    s.start = with_cell ? s.cell + cp.N : s.cell;
+    return s;
+}
+
+template <typename T>
+__device__ __forceinline__ void load_coupling_fast(const FastShared<T>& s, const Coupling<T>& cp,
+                                                   bool with_cell) {
+    for (int i = threadIdx.x; i < cp.N; i += blockDim.x) {
+        s.C[i] = cp.C[i];
+        s.M1[i] = cp.M1[i];
+        if (with_cell) s.cell[i] = cp.cell[i];
+    }
+    for (int i = threadIdx.x; i <= cp.ncell; i += blockDim.x) s.start[i] = cp.start[i];
+}
+
+template <typename T, int N> struct Vec;
+template <> struct Vec<double, 2> { using type = double2; };
+template <> struct Vec<float, 4> { using type = float4; };
+
+// p = sum_m2 T_row[m2] * w[m2], the row read as 16-byte broadcasts.
+template <typename T, int TP>
+__device__ __forceinline__ T dot_row(const T* __restrict__ row, const T (&w)[TP]) {
+    constexpr int V = 16 / sizeof(T);
+    using VT = typename Vec<T, V>::type;
+    T p = T(0);
+#pragma unroll
+    for (int q = 0; q < TP / V; q++) {
+        union {
+            VT v;
+            T s[V];
+        } u;
+        u.v = *reinterpret_cast<const VT*>(row + q * V);
+#pragma unroll
+        for (int i = 0; i < V; i++) p += u.s[i] * w[q * V + i];
+    }
+    return p;
+}
+
+template <typename T, int TP, bool SEGMENTED>
+__global__ void sasaw_fwd_fast(T* __restrict__ O, const T* __restrict__ A, const T* __restrict__ B,
+                               const T* __restrict__ W, const int32_t* __restrict__ Jw,
+                               const int32_t* __restrict__ Io,
+                               const int64_t* __restrict__ offsets, Coupling<T> cp, int64_t E,
+                               int nA, int L, int64_t nW0, int nW1, int nO1, bool always,
+                               Status st) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int ncell = cp.ncell; // nO1 * TP
+    const size_t rowsize = static_cast<size_t>(nO1) * L;
+    const size_t per_warp = round4(ncell) + (SEGMENTED ? round4(rowsize) : 0) + round4(nA);
+    if (SEGMENTED ? saw_unsorted(st) : (!always && !saw_unsorted(st))) return;
+    FastShared<T> s = carve_fast<T>(smem_raw, cp, per_warp, warps, false);
+    load_coupling_fast(s, cp, false);
+    __syncthreads();
+    T* T_s = s.warp_base + per_warp * warp; // [nO1][TP], 16-byte aligned
+    T* Oacc = T_s + round4(ncell);
+    T* a_s = Oacc + (SEGMENTED ? round4(rowsize) : 0);
+
+    auto edge = [&](int64_t e, int64_t out_row) {
+        int32_t j = __ldg(Jw + e);
+        if (clamp_index(j, static_cast<int32_t>(nW0)) && lane == 0) report_bad_index(st, kBitJ);
+        __syncwarp();
+        for (int m = lane; m < nA; m += 32) a_s[m] = A[e * nA + m];
+        __syncwarp();
+        for (int c = lane; c < ncell; c += 32) {
+            T t = T(0);
+            for (int pos = s.start[c]; pos < s.start[c + 1]; pos++) t += s.C[pos] * a_s[s.M1[pos]];
+            T_s[c] = t;
+        }
+        __syncwarp();
+        const T* wrow = W + static_cast<int64_t>(j) * nW1 * L;
+        for (int b0 = 0; b0 < L; b0 += 32) {
+            const int b = b0 + lane;
+            const bool valid = b < L;
+            T w[TP];
+#pragma unroll
+            for (int m2 = 0; m2 < TP; m2++)
+                w[m2] = (valid && m2 < nW1) ? __ldg(wrow + m2 * L + b) : T(0);
+            const T Bb = valid ? B[e * L + b] : T(0);
+            for (int m3 = 0; m3 < nO1; m3++) {
+                const T p = dot_row<T, TP>(T_s + m3 * TP, w);
+                if (valid) {
+                    if (SEGMENTED)
+                        Oacc[m3 * L + b] += Bb * p;
+                    else
+                        red_add(O + out_row * rowsize + m3 * L + b, Bb * p);
+                }
+            }
+        }
+    };
+
+    if (SEGMENTED) {
+        const int64_t r = static_cast<int64_t>(blockIdx.x) * warps + warp;
+        if (r >= nW0) return;
+        const int64_t begin = offsets[r], end = offsets[r + 1];
+        for (int idx = lane; idx < static_cast<int>(rowsize); idx += 32) Oacc[idx] = T(0);
+        for (int64_t e = begin; e < end; e++) edge(e, r);
+        __syncwarp();
+        T* dst = O + r * rowsize;
+        for (int idx = lane; idx < static_cast<int>(rowsize); idx += 32) dst[idx] = Oacc[idx];
+    } else {
+        const int64_t nwarps = static_cast<int64_t>(gridDim.x) * warps;
+        for (int64_t e = static_cast<int64_t>(blockIdx.x) * warps + warp; e < E; e += nwarps) {
+            int32_t row = __ldg(Io + e);
+            if (clamp_index(row, static_cast<int32_t>(nW0))) {
+                if (lane == 0) report_bad_index(st, kBitI);
+                continue;
+            }
+            edge(e, row);
+        }
+    }
+}
+
+// Sums VP values over the 32 lanes with VP - 1 + log2(32 / VP) shuffles (recursive halving):
+// afterwards every lane holds the total of value number lane >> (5 - log2(VP)).
+template <typename T, int VP> __device__ __forceinline__ T reduce_to_lanes(T (&v)[VP], int lane) {
+    int d = 16;
+#pragma unroll
+    for (int half = VP / 2; half >= 1; half >>= 1, d >>= 1) {
+        const bool upper = (lane & d) != 0;
+#pragma unroll
+        for (int i = 0; i < half; i++) {
+            const T keep = upper ? v[i + half] : v[i];
+            const T send = upper ? v[i] : v[i + half];
+            v[i] = keep + __shfl_xor_sync(kFullMask, send, d);
+        }
+    }
+    T r = v[0];
+    for (; d >= 1; d >>= 1) r += __shfl_xor_sync(kFullMask, r, d);
+    return r;
+}
+
+template <int TP> struct Pow2 { static constexpr int value = TP <= 4 ? 4 : TP <= 8 ? 8 : 16; };
+template <int VP> struct Log2 { static constexpr int value = VP == 4 ? 2 : VP == 8 ? 3 : 4; };
+
+template <typename T, int TP>
+__global__ void sasaw_vjp_fast(T* __restrict__ gA, T* __restrict__ gB, T* __restrict__ gW,
+                               const T* __restrict__ gO, const T* __restrict__ A,
+                               const T* __restrict__ B, const T* __restrict__ W,
+                               const int32_t* __restrict__ Jw, const int32_t* __restrict__ Io,
+                               Coupling<T> cp, int64_t E, int nA, int L, int64_t nW0, int nW1,
+                               int nO1, Status st) {
+    constexpr int VP = Pow2<TP>::value;
+    constexpr int kShift = 5 - Log2<VP>::value;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int ncell = cp.ncell, N = cp.N;
+    const size_t per_warp = 2 * round4(ncell) + round4(nA) + round4(static_cast<size_t>(nA) * 33);
+    FastShared<T> s = carve_fast<T>(smem_raw, cp, per_warp, warps, true);
+    load_coupling_fast(s, cp, true);
+    __syncthreads();
+    T* T_s = s.warp_base + per_warp * warp;
+    T* U_s = T_s + round4(ncell);
+    T* a_s = U_s + round4(ncell);
+    T* ga_priv = a_s + round4(nA); // [nA][33]: one private column per lane
+    const int64_t rowsize = static_cast<int64_t>(nO1) * L;
+    const bool want_a = gA != nullptr, want_b = gB != nullptr, want_w = gW != nullptr;
+    const int my_value = lane >> kShift;
+    const bool writer = (lane & ((1 << kShift) - 1)) == 0 && my_value < nW1;
+
+    const int64_t nwarps = static_cast<int64_t>(gridDim.x) * warps;
+    for (int64_t e = static_cast<int64_t>(blockIdx.x) * warps + warp; e < E; e += nwarps) {
+        int32_t row = __ldg(Io + e), j = __ldg(Jw + e);
+        if (clamp_index(row, static_cast<int32_t>(nW0)) && lane == 0) report_bad_index(st, kBitI);
+        if (clamp_index(j, static_cast<int32_t>(nW0)) && lane == 0) report_bad_index(st, kBitJ);
+        __syncwarp();
+        for (int m = lane; m < nA; m += 32) a_s[m] = A[e * nA + m];
+        __syncwarp();
+        for (int c = lane; c < ncell; c += 32) {
+            T t = T(0);
+            for (int pos = s.start[c]; pos < s.start[c + 1]; pos++) t += s.C[pos] * a_s[s.M1[pos]];
+            T_s[c] = t;
+            U_s[c] = T(0);
+        }
+        __syncwarp();
+        const T* g = gO + static_cast<int64_t>(row) * rowsize;
+        const T* wrow = W + static_cast<int64_t>(j) * nW1 * L;
+        T* gw = want_w ? gW + static_cast<int64_t>(j) * nW1 * L : nullptr;
+        for (int b0 = 0; b0 < L; b0 += 32) {
+            const int b = b0 + lane;
+            const bool valid = b < L;
+            T w[TP], accw[TP];
+#pragma unroll
+            for (int m2 = 0; m2 < TP; m2++) {
+                w[m2] = (valid && m2 < nW1) ? __ldg(wrow + m2 * L + b) : T(0);
+                accw[m2] = T(0);
+            }
+            const T Bb = valid ? B[e * L + b] : T(0);
+            for (int m3 = 0; m3 < nO1; m3++) {
+                const T gv = valid ? __ldg(g + m3 * L + b) : T(0);
+                const T* trow = T_s + m3 * TP;
+                constexpr int V = 16 / sizeof(T);
+                using VT = typename Vec<T, V>::type;
+#pragma unroll
+                for (int q = 0; q < TP / V; q++) {
+                    union {
+                        VT v;
+                        T s[V];
+                    } u;
+                    u.v = *reinterpret_cast<const VT*>(trow + q * V);
+#pragma unroll
+                    for (int i = 0; i < V; i++) accw[q * V + i] += u.s[i] * gv;
+                }
+                if (want_a) {
+                    // U_e[m3, m2] = sum_b gO[m3,b] B[b] W[m2,b]: TP lane-partials, summed over lanes
+                    const T gb_ = gv * Bb;
+                    T up[VP];
+#pragma unroll
+                    for (int m2 = 0; m2 < VP; m2++) up[m2] = m2 < TP ? gb_ * w[m2 < TP ? m2 : 0] : T(0);
+                    const T total = reduce_to_lanes<T, VP>(up, lane);
+                    if (writer) U_s[m3 * TP + my_value] += total;
+                }
+            }
+            T gb = T(0);
+#pragma unroll
+            for (int m2 = 0; m2 < TP; m2++) {
+                gb += w[m2] * accw[m2];
+                if (want_w && valid && m2 < nW1) red_add(gw + m2 * L + b, Bb * accw[m2]);
+            }
+            if (want_b && valid) gB[e * L + b] = gb;
+        }
+        if (want_a) {
+            __syncwarp();
+            for (int idx = lane; idx < nA * 33; idx += 32) ga_priv[idx] = T(0);
+            __syncwarp();
+            for (int pos = lane; pos < N; pos += 32)
+                ga_priv[s.M1[pos] * 33 + lane] += s.C[pos] * U_s[s.cell[pos]];
+            __syncwarp();
+            for (int m = lane; m < nA; m += 32) {
+                T sum = T(0);
+                for (int l = 0; l < 32; l++) sum += ga_priv[m * 33 + l];
+                gA[e * nA + m] = sum;
+            }
+        }
+    }
+}
+
 // Any sizes, no shared memory: one thread per (edge, b) walking the whole coupling table.
 // Needs zero-filled O (forward) / gA, gW (VJP).
 template <typename T>
@@ -395,8 +658,10 @@ template <typename T> struct Problem {
 // Allocates and fills the grouped coupling table; returns false when the grouped kernels
 // cannot be used (cell grid too large for one block's shared memory).
 template <typename T>
-bool build_coupling(const Call& call, const Problem<T>& p, Coupling<T>& cp, void** scratch) {
-    const int64_t ncell64 = static_cast<int64_t>(p.nO1) * p.nW1;
+bool build_coupling(const Call& call, const Problem<T>& p, Coupling<T>& cp, void** scratch,
+                    int cell_stride = 0) {
+    if (cell_stride == 0) cell_stride = p.nW1;
+    const int64_t ncell64 = static_cast<int64_t>(p.nO1) * cell_stride;
     if (ncell64 > 8192 || ncell64 == 0) return false;
     cp.N = p.N;
     cp.ncell = static_cast<int>(ncell64);
@@ -443,12 +708,108 @@ template <typename Kernel> void allow_smem(Kernel kernel, size_t smem) {
                                           static_cast<int>(smem)));
 }
 
+// Shared memory of a fast-kernel block, and the largest warp count (8, 4, 2, 1) that fits.
+template <typename T>
+int pick_warps_fast(const Call& call, const Coupling<T>& cp, size_t per_warp, bool with_cell,
+                    size_t* smem) {
+    for (int warps : {8, 4, 2, 1}) {
+        const size_t bytes = (round4(cp.N) + per_warp * warps) * sizeof(T) +
+                             (static_cast<size_t>(cp.N) * (with_cell ? 2 : 1) + cp.ncell + 1) *
+                                 sizeof(int32_t);
+        const size_t limit = warps == 1 ? static_cast<size_t>(max_optin_smem(call.device)) : 100 * 1024;
+        if (bytes <= limit) {
+            *smem = bytes;
+            return warps;
+        }
+    }
+    return 0;
+}
+
+// Width of a T_e row in the fast kernels: W.shape[1] rounded up to a multiple of four, or 0
+// when the fast kernels do not apply.
+inline int fast_row_width(int nW1) { return nW1 >= 1 && nW1 <= 16 ? (nW1 + 3) / 4 * 4 : 0; }
+
+template <typename T, int TP>
+bool forward_fast(const Call& call, T* O, const Problem<T>& p) {
+    const int64_t rowsize = static_cast<int64_t>(p.nO1) * p.L;
+    const int grid_generic = sm_count(call.device) * 8;
+    Coupling<T> cp{};
+    void* scratch = nullptr;
+    if (!build_coupling(call, p, cp, &scratch, TP)) return false;
+    size_t smem_seg = 0, smem_edge = 0;
+    const size_t base = round4(cp.ncell) + round4(p.nA);
+    const int warps_seg = pick_warps_fast(call, cp, base + round4(rowsize), false, &smem_seg);
+    const int warps_edge = pick_warps_fast(call, cp, base, false, &smem_edge);
+    if (warps_seg == 0 || warps_edge == 0) {
+        scratch_free(call, scratch);
+        return false;
+    }
+    int64_t* offsets = static_cast<int64_t*>(scratch_alloc(call, (p.nW0 + 1) * sizeof(int64_t)));
+    const int64_t pre_blocks = std::min<int64_t>(ceil_div(p.E + 1, 256), grid_generic * 4);
+    segment_offsets<<<static_cast<unsigned>(pre_blocks), 256, 0, call.stream>>>(
+        p.Io, p.E, p.nW0, offsets, call.status);
+    allow_smem(sasaw_fwd_fast<T, TP, true>, smem_seg);
+    sasaw_fwd_fast<T, TP, true><<<static_cast<unsigned>(ceil_div(p.nW0, warps_seg)),
+                                  warps_seg * 32, smem_seg, call.stream>>>(
+        O, p.A, p.B, p.W, p.Jw, p.Io, offsets, cp, p.E, p.nA, p.L, p.nW0, p.nW1, p.nO1, false,
+        call.status);
+    MOPS_CUDA_OK(cudaGetLastError());
+    scratch_free(call, offsets);
+    bool need_fallback = true; // asynchronous calls cannot look: always enqueue
+    if (call.wait) {
+        wait_stream(call);
+        need_fallback = host_saw_unsorted(call);
+    }
+    if (need_fallback) {
+        zero_if_unsorted<T><<<grid_generic, 256, 0, call.stream>>>(O, p.nW0 * rowsize, call.status);
+        allow_smem(sasaw_fwd_fast<T, TP, false>, smem_edge);
+        const int64_t blocks = std::min<int64_t>(ceil_div(p.E, warps_edge), grid_generic);
+        sasaw_fwd_fast<T, TP, false><<<static_cast<unsigned>(blocks), warps_edge * 32, smem_edge,
+                                       call.stream>>>(O, p.A, p.B, p.W, p.Jw, p.Io, nullptr, cp,
+                                                      p.E, p.nA, p.L, p.nW0, p.nW1, p.nO1, false,
+                                                      call.status);
+    }
+    MOPS_CUDA_OK(cudaGetLastError());
+    scratch_free(call, scratch);
+    return true;
+}
+
+template <typename T, int TP>
+bool backward_fast(const Call& call, T* gA, T* gB, T* gW, const T* gO, const Problem<T>& p) {
+    Coupling<T> cp{};
+    void* scratch = nullptr;
+    if (!build_coupling(call, p, cp, &scratch, TP)) return false;
+    size_t smem = 0;
+    const size_t per_warp = 2 * round4(cp.ncell) + round4(p.nA) + round4(static_cast<size_t>(p.nA) * 33);
+    const int warps = pick_warps_fast(call, cp, per_warp, true, &smem);
+    if (warps == 0) {
+        scratch_free(call, scratch);
+        return false;
+    }
+    allow_smem(sasaw_vjp_fast<T, TP>, smem);
+    const int64_t blocks =
+        std::min<int64_t>(ceil_div(p.E, warps), static_cast<int64_t>(sm_count(call.device)) * 16);
+    sasaw_vjp_fast<T, TP><<<static_cast<unsigned>(blocks), warps * 32, smem, call.stream>>>(
+        gA, gB, gW, gO, p.A, p.B, p.W, p.Jw, p.Io, cp, p.E, p.nA, p.L, p.nW0, p.nW1, p.nO1,
+        call.status);
+    MOPS_CUDA_OK(cudaGetLastError());
+    scratch_free(call, scratch);
+    return true;
+}
+
 template <typename T> void forward(const Call& call, T* O, const Problem<T>& p) {
     const int64_t rowsize = static_cast<int64_t>(p.nO1) * p.L;
     if (p.nW0 == 0 || rowsize == 0) return;
     if (p.E == 0 || p.N == 0) {
         MOPS_CUDA_OK(cudaMemsetAsync(O, 0, p.nW0 * rowsize * sizeof(T), call.stream));
         return;
+    }
+    switch (fast_row_width(p.nW1)) {
+    case 4: if (forward_fast<T, 4>(call, O, p)) return; break;
+    case 8: if (forward_fast<T, 8>(call, O, p)) return; break;
+    case 12: if (forward_fast<T, 12>(call, O, p)) return; break;
+    case 16: if (forward_fast<T, 16>(call, O, p)) return; break;
+    default: break;
     }
     const int grid_generic = sm_count(call.device) * 8;
     Coupling<T> cp{};
@@ -499,6 +860,15 @@ void backward(const Call& call, T* gA, T* gB, T* gW, const T* gO, const Problem<
         MOPS_CUDA_OK(cudaMemsetAsync(gW, 0, wsize * sizeof(T), call.stream));
     if (p.E == 0) return;
     const bool empty = p.N == 0 || p.L == 0 || p.nO1 == 0 || p.nW1 == 0 || p.nA == 0;
+    if (!empty) {
+        switch (fast_row_width(p.nW1)) {
+        case 4: if (backward_fast<T, 4>(call, gA, gB, gW, gO, p)) return; break;
+        case 8: if (backward_fast<T, 8>(call, gA, gB, gW, gO, p)) return; break;
+        case 12: if (backward_fast<T, 12>(call, gA, gB, gW, gO, p)) return; break;
+        case 16: if (backward_fast<T, 16>(call, gA, gB, gW, gO, p)) return; break;
+        default: break;
+        }
+    }
     Coupling<T> cp{};
     void* scratch = nullptr;
     const bool grouped = !empty && build_coupling(call, p, cp, &scratch);
