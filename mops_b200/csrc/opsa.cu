@@ -67,8 +67,11 @@ template <typename T, int N> __device__ __forceinline__ void store_vec(T* p, con
 
 // ------------------------------------------------------------------------------ forward
 struct FwdPlan {
-    int TK, TL; // register tile per lane
-    int LL, LK; // lane grid: LL lanes along l, LK along k (LL*LK <= 32)
+    int G;      // lanes that share one entry; 32 / G entries are processed side by side
+    int LL, LK; // lane grid inside a group: LL lanes along l, LK along k (LL*LK <= G)
+    int TK;     // k values per lane (contiguous)
+    int NV;     // l vector chunks per lane (chunk q = ll + v*LL covers l in [q*VEC, q*VEC+VEC))
+    int VEC;    // scalars per l chunk (16-byte loads when > 1)
     int CH;     // entries per staged chunk (<= 32)
     int stage_scalars; // scalars of one stage: CH*L (B) [+ CH*L (W rows)] + CH*K (A) + padding
     size_t smem_per_warp;
@@ -76,10 +79,13 @@ struct FwdPlan {
 
 // One warp per output row. The row's entries [offsets[r], offsets[r+1]) are contiguous in A
 // and B; they stream through two shared-memory stages with cp.async, the next chunk in
-// flight while the current one is consumed. Lane (lk, ll) keeps the TK x TL tile
-// k in [lk*TK, lk*TK+TK), l in [ll*TL, ll*TL+TL) of the K x L result in registers.
-template <typename T, int TK, int TL, bool WEIGHTED>
-__global__ void __launch_bounds__(kFwdWarps * 32)
+// flight while the current one is consumed. The 32 lanes form 32/G groups that take
+// alternate entries; inside a group, lane (lk, ll) keeps a TK x (NV*VEC) tile of the K x L
+// result in registers. Fewer lanes per entry mean larger register tiles, hence fewer
+// shared-memory operand reads per multiply-add (the limiter of this kernel after HBM); the
+// groups' partial tiles are added with shuffles once per row.
+template <typename T, int TK, int NV, int VEC, bool WEIGHTED>
+__global__ void __launch_bounds__(kFwdWarps * 32, 2)
 opsa_fwd_rows(T* __restrict__ O, const T* __restrict__ A, const T* __restrict__ B,
               const T* __restrict__ W, const int32_t* __restrict__ PW,
               const int64_t* __restrict__ offsets, int K, int L, int64_t nO, FwdPlan plan,
@@ -96,7 +102,9 @@ opsa_fwd_rows(T* __restrict__ O, const T* __restrict__ A, const T* __restrict__ 
     const int a_off = (WEIGHTED ? 2 : 1) * CH * L;
     const int64_t begin = offsets[r], end = offsets[r + 1];
 
-    const int ll = lane % plan.LL, lk = lane / plan.LL;
+    const int G = plan.G, slots = 32 / G;
+    const int slot = lane / G, g = lane - slot * G;
+    const int ll = g % plan.LL, lk = g / plan.LL;
     T* Orow = O + r * K * L;
 
     // Issues the copies of chunk [c0, c0+n) into stage `buf`. pw_lane: lane jj holds PW[c0+jj].
@@ -126,15 +134,19 @@ opsa_fwd_rows(T* __restrict__ O, const T* __restrict__ A, const T* __restrict__ 
         return pw;
     };
 
+    const int l_span = plan.LL * NV * VEC; // l values one pass covers
     for (int kb = 0; kb < K; kb += plan.LK * TK) {
-        for (int lb = 0; lb < L; lb += plan.LL * TL) {
-            const int k0 = kb + lk * TK, l0 = lb + ll * TL;
-            const bool active = lk < plan.LK && l0 < L && k0 < K;
-            T acc[TK][TL];
+        for (int lb = 0; lb < L; lb += l_span) {
+            const int k0 = kb + lk * TK;
+            const bool active = lk < plan.LK && k0 < K;
+            int l_of[NV]; // first l of each of this lane's chunks
+#pragma unroll
+            for (int v = 0; v < NV; v++) l_of[v] = lb + (ll + v * plan.LL) * VEC;
+            T acc[TK][NV * VEC];
 #pragma unroll
             for (int t = 0; t < TK; t++)
 #pragma unroll
-                for (int u = 0; u < TL; u++) acc[t][u] = T(0);
+                for (int u = 0; u < NV * VEC; u++) acc[t][u] = T(0);
 
             const int64_t total = end - begin;
             const int nchunks = static_cast<int>((total + CH - 1) / CH);
@@ -164,48 +176,75 @@ opsa_fwd_rows(T* __restrict__ O, const T* __restrict__ A, const T* __restrict__ 
                 }
                 __syncwarp();
                 if (active) {
-                    const T* pb = stage0 + (c & 1) * plan.stage_scalars + l0;
-                    const T* pa = pb - l0 + a_off + k0;
-#pragma unroll 2
-                    for (int jj = 0; jj < n; jj++) {
-                        T a[TK], b[TL];
+                    const T* Bs = stage0 + (c & 1) * plan.stage_scalars;
+                    const T* pb = Bs + slot * L;
+                    const T* pa = Bs + a_off + slot * K + k0;
+                    for (int jj = slot; jj < n; jj += slots) {
+                        T a[TK], b[NV * VEC];
                         // k0+t beyond K reads the next row or the padding: those
                         // accumulators are never stored.
 #pragma unroll
                         for (int t = 0; t < TK; t++) a[t] = pa[t];
-                        if (TL > 1) {
-                            load_vec<T, TL>(pb, b);
-                        } else {
-                            b[0] = pb[0];
-                        }
-                        if (WEIGHTED) {
-                            T w[TL];
-                            if (TL > 1) {
-                                load_vec<T, TL>(pb + CH * L, w);
+#pragma unroll
+                        for (int v = 0; v < NV; v++) {
+                            T bv[VEC];
+                            if (l_of[v] < L) {
+                                if (VEC > 1) {
+                                    load_vec<T, VEC>(pb + l_of[v], bv);
+                                } else {
+                                    bv[0] = pb[l_of[v]];
+                                }
+                                if (WEIGHTED) {
+                                    T wv[VEC];
+                                    if (VEC > 1) {
+                                        load_vec<T, VEC>(pb + CH * L + l_of[v], wv);
+                                    } else {
+                                        wv[0] = pb[CH * L + l_of[v]];
+                                    }
+#pragma unroll
+                                    for (int u = 0; u < VEC; u++) bv[u] *= wv[u];
+                                }
                             } else {
-                                w[0] = pb[CH * L];
+#pragma unroll
+                                for (int u = 0; u < VEC; u++) bv[u] = T(0);
                             }
 #pragma unroll
-                            for (int u = 0; u < TL; u++) b[u] *= w[u];
+                            for (int u = 0; u < VEC; u++) b[v * VEC + u] = bv[u];
                         }
 #pragma unroll
                         for (int t = 0; t < TK; t++)
 #pragma unroll
-                            for (int u = 0; u < TL; u++) acc[t][u] += a[t] * b[u];
-                        pa += K;
-                        pb += L;
+                            for (int u = 0; u < NV * VEC; u++) acc[t][u] += a[t] * b[u];
+                        pa += slots * K;
+                        pb += slots * L;
                     }
                 }
                 __syncwarp(); // stage (c & 1) may be overwritten by the copy issued next round
             }
-            if (active) {
+            // add the groups' partial tiles (all lanes take part in the shuffles)
+            for (int d = G; d < 32; d <<= 1) {
+#pragma unroll
+                for (int t = 0; t < TK; t++)
+#pragma unroll
+                    for (int u = 0; u < NV * VEC; u++)
+                        acc[t][u] += __shfl_xor_sync(kFullMask, acc[t][u], d);
+            }
+            if (active && slot == 0) {
 #pragma unroll
                 for (int t = 0; t < TK; t++) {
                     if (k0 + t < K) {
-                        if (TL > 1) {
-                            store_vec<T, TL>(Orow + (k0 + t) * L + l0, acc[t]);
-                        } else {
-                            Orow[(k0 + t) * L + l0] = acc[t][0];
+#pragma unroll
+                        for (int v = 0; v < NV; v++) {
+                            if (l_of[v] < L) {
+                                T out[VEC];
+#pragma unroll
+                                for (int u = 0; u < VEC; u++) out[u] = acc[t][v * VEC + u];
+                                if (VEC > 1) {
+                                    store_vec<T, VEC>(Orow + (k0 + t) * L + l_of[v], out);
+                                } else {
+                                    Orow[(k0 + t) * L + l_of[v]] = out[0];
+                                }
+                            }
                         }
                     }
                 }
@@ -245,22 +284,61 @@ __global__ void opsa_fwd_atomic(T* __restrict__ O, const T* __restrict__ A,
     }
 }
 
+constexpr int kMaxNV = 3;
+
+// Chooses the lane grouping and register tile that minimise shared-memory operand traffic
+// per entry, within a register budget.
 template <typename T, bool WEIGHTED> FwdPlan plan_forward(int K, int L, bool l_aligned) {
-    FwdPlan p;
+    const int words = static_cast<int>(sizeof(T)) / 4; // 32-bit words per scalar
     const int widest = 16 / static_cast<int>(sizeof(T));
-    p.TL = 1;
-    if (l_aligned) {
-        for (int tl = widest; tl > 1; tl /= 2) {
-            if (L % tl == 0) {
-                p.TL = tl;
-                break;
+    FwdPlan best{};
+    double best_cost = 1e30;
+    for (int VEC : {widest, 1}) {
+        if (VEC > 1 && (!l_aligned || L % VEC != 0)) continue;
+        const int nchunks_l = static_cast<int>(ceil_div(L, VEC));
+        for (int G : {32, 16, 8, 4}) {
+            for (int LL = 1; LL <= G; LL++) {
+                int LK = G / LL;
+                if (LK > K) LK = K;
+                const int NV = static_cast<int>(ceil_div(nchunks_l, LL));
+                const int TK = static_cast<int>(ceil_div(K, LK));
+                if (NV > kMaxNV || TK > kMaxTK) continue;
+                const int acc = TK * NV * VEC;
+                if (acc * words > 64) continue; // register budget: two 8-warp blocks per SM
+                // shared-memory passes per entry: a w-byte load costs w/4 of a 32-lane pass
+                const double operand =
+                    (TK + (WEIGHTED ? 2 : 1) * NV * VEC) * words * (G / 32.0);
+                // shuffles that add the 32/G partial tiles, spread over ~48 entries per row
+                int steps = 0;
+                for (int d = G; d < 32; d <<= 1) steps++;
+                const double reduce = acc * words * steps / 48.0;
+                // idle lanes and padded tile elements waste issue slots
+                const double waste = 0.02 * (TK * LK * NV * LL * VEC) / std::max(1, K * L);
+                const double cost = operand + reduce + waste;
+                if (cost < best_cost) {
+                    best_cost = cost;
+                    best.G = G;
+                    best.LL = LL;
+                    best.LK = LK;
+                    best.TK = TK;
+                    best.NV = NV;
+                    best.VEC = VEC;
+                }
             }
         }
+        if (best_cost < 1e30) break; // the widest usable vector is always the better choice
     }
-    p.LL = static_cast<int>(std::min<int64_t>(32, ceil_div(L, p.TL)));
-    p.LK = 32 / p.LL;
-    if (p.LK > K) p.LK = K;
-    p.TK = static_cast<int>(std::min<int64_t>(kMaxTK, ceil_div(K, p.LK)));
+    if (best_cost >= 1e30) {
+        // very large K x L: tile in passes with the largest tile
+        best.VEC = (l_aligned && L % widest == 0) ? widest : 1;
+        best.G = 32;
+        best.LL = static_cast<int>(std::min<int64_t>(32, ceil_div(ceil_div(L, best.VEC), kMaxNV)));
+        best.LK = std::max(1, 32 / best.LL);
+        best.NV = static_cast<int>(std::min<int64_t>(kMaxNV, ceil_div(ceil_div(L, best.VEC), best.LL)));
+        best.TK = static_cast<int>(std::min<int64_t>(kMaxTK, ceil_div(K, best.LK)));
+        while (best.TK * best.NV * best.VEC * words > 64 && best.TK > 1) best.TK--;
+    }
+    FwdPlan p = best;
     // Two stages per warp, about 9 KB together, so that three 8-warp blocks share an SM.
     const size_t row_bytes = (static_cast<size_t>(K) + (WEIGHTED ? 2 : 1) * L) * sizeof(T);
     p.CH = 32;
@@ -275,11 +353,11 @@ template <typename T, bool WEIGHTED> FwdPlan plan_forward(int K, int L, bool l_a
     return p;
 }
 
-template <typename T, int TK, int TL, bool WEIGHTED>
+template <typename T, int TK, int NV, int VEC, bool WEIGHTED>
 void launch_fwd_tile(const Call& call, const FwdPlan& plan, T* O, const T* A, const T* B,
                      const T* W, const int32_t* PW, const int64_t* offsets, int K, int L,
                      int64_t nO) {
-    auto kernel = opsa_fwd_rows<T, TK, TL, WEIGHTED>;
+    auto kernel = opsa_fwd_rows<T, TK, NV, VEC, WEIGHTED>;
     const size_t smem = plan.smem_per_warp * kFwdWarps;
     if (smem > 48 * 1024) {
         MOPS_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -290,17 +368,26 @@ void launch_fwd_tile(const Call& call, const FwdPlan& plan, T* O, const T* A, co
         O, A, B, W, PW, offsets, K, L, nO, plan, call.status);
 }
 
-template <typename T, int TL, bool WEIGHTED, typename... Args>
+template <typename T, int NV, int VEC, bool WEIGHTED, typename... Args>
 void dispatch_tk(int TK, Args... args) {
     switch (TK) {
-    case 1: launch_fwd_tile<T, 1, TL, WEIGHTED>(args...); break;
-    case 2: launch_fwd_tile<T, 2, TL, WEIGHTED>(args...); break;
-    case 3: launch_fwd_tile<T, 3, TL, WEIGHTED>(args...); break;
-    case 4: launch_fwd_tile<T, 4, TL, WEIGHTED>(args...); break;
-    case 5: launch_fwd_tile<T, 5, TL, WEIGHTED>(args...); break;
-    case 6: launch_fwd_tile<T, 6, TL, WEIGHTED>(args...); break;
-    case 7: launch_fwd_tile<T, 7, TL, WEIGHTED>(args...); break;
-    default: launch_fwd_tile<T, 8, TL, WEIGHTED>(args...); break;
+    case 1: launch_fwd_tile<T, 1, NV, VEC, WEIGHTED>(args...); break;
+    case 2: launch_fwd_tile<T, 2, NV, VEC, WEIGHTED>(args...); break;
+    case 3: launch_fwd_tile<T, 3, NV, VEC, WEIGHTED>(args...); break;
+    case 4: launch_fwd_tile<T, 4, NV, VEC, WEIGHTED>(args...); break;
+    case 5: launch_fwd_tile<T, 5, NV, VEC, WEIGHTED>(args...); break;
+    case 6: launch_fwd_tile<T, 6, NV, VEC, WEIGHTED>(args...); break;
+    case 7: launch_fwd_tile<T, 7, NV, VEC, WEIGHTED>(args...); break;
+    default: launch_fwd_tile<T, 8, NV, VEC, WEIGHTED>(args...); break;
+    }
+}
+
+template <typename T, int VEC, bool WEIGHTED, typename... Args>
+void dispatch_nv(int NV, int TK, Args... args) {
+    switch (NV) {
+    case 1: dispatch_tk<T, 1, VEC, WEIGHTED>(TK, args...); break;
+    case 2: dispatch_tk<T, 2, VEC, WEIGHTED>(TK, args...); break;
+    default: dispatch_tk<T, 3, VEC, WEIGHTED>(TK, args...); break;
     }
 }
 
@@ -327,19 +414,13 @@ void forward(const Call& call, T* O, const T* A, const T* B, const T* W, const i
         segment_offsets<<<static_cast<unsigned>(pre_blocks), 256, 0, call.stream>>>(
             P, J, nO, offsets, call.status);
         MOPS_CUDA_OK(cudaGetLastError());
-        if constexpr (sizeof(T) == 8) {
-            if (plan.TL == 2)
-                dispatch_tk<T, 2, WEIGHTED>(plan.TK, call, plan, O, A, B, W, PW, offsets, K, L, nO);
-            else
-                dispatch_tk<T, 1, WEIGHTED>(plan.TK, call, plan, O, A, B, W, PW, offsets, K, L, nO);
-        } else {
-            if (plan.TL == 4)
-                dispatch_tk<T, 4, WEIGHTED>(plan.TK, call, plan, O, A, B, W, PW, offsets, K, L, nO);
-            else if (plan.TL == 2)
-                dispatch_tk<T, 2, WEIGHTED>(plan.TK, call, plan, O, A, B, W, PW, offsets, K, L, nO);
-            else
-                dispatch_tk<T, 1, WEIGHTED>(plan.TK, call, plan, O, A, B, W, PW, offsets, K, L, nO);
-        }
+        constexpr int widest = 16 / static_cast<int>(sizeof(T));
+        if (plan.VEC == widest)
+            dispatch_nv<T, widest, WEIGHTED>(plan.NV, plan.TK, call, plan, O, A, B, W, PW, offsets,
+                                             K, L, nO);
+        else
+            dispatch_nv<T, 1, WEIGHTED>(plan.NV, plan.TK, call, plan, O, A, B, W, PW, offsets, K,
+                                        L, nO);
         MOPS_CUDA_OK(cudaGetLastError());
         scratch_free(call, offsets);
         bool need_fallback = true; // asynchronous calls cannot look: always enqueue

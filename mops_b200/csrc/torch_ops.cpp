@@ -107,6 +107,13 @@ template <typename F> void on_stream_of(const Tensor& like, F&& body) {
 
 Tensor maybe_empty_like(const Tensor& t) { return t.requires_grad() ? torch::empty_like(t) : Tensor(); }
 
+// Outputs of an autograd Function must be defined tensors: a gradient that was not requested
+// is returned as an empty placeholder and turned back into "no gradient" by the caller.
+Tensor defined(const Tensor& t, const Tensor& like) {
+    return t.defined() ? t : torch::empty({0}, like.options());
+}
+Tensor requested(const Tensor& t) { return t.defined() && t.numel() == 0 ? Tensor() : t; }
+
 [[noreturn]] void no_second_derivative(const char* op) {
     C10_THROW_ERROR(NotImplementedError,
                     std::string("second derivatives are not supported in CUDA for ") + op);
@@ -129,7 +136,7 @@ struct HpeBackward : torch::autograd::Function<HpeBackward> {
             });
         });
         (void)ctx;
-        return {grad_A, Tensor()};
+        return {defined(grad_A, A)};
     }
     static tensor_list backward(AutogradContext*, tensor_list) {
         no_second_derivative("homogeneous_polynomial_evaluation");
@@ -163,7 +170,7 @@ struct Hpe : torch::autograd::Function<Hpe> {
     static tensor_list backward(AutogradContext* ctx, tensor_list grad_outputs) {
         auto saved = ctx->get_saved_variables();
         auto results = HpeBackward::apply(grad_outputs[0].contiguous(), saved[0], saved[1], saved[2]);
-        return {results[0], Tensor(), Tensor()};
+        return {requested(results[0]), Tensor(), Tensor()};
     }
 };
 
@@ -189,14 +196,17 @@ struct SapBackward : torch::autograd::Function<SapBackward> {
         if (grad_output.requires_grad() || A.requires_grad() || B.requires_grad()) {
             ctx->save_for_backward({grad_output, A, B, C, indices_A, indices_B, indices_output});
         }
-        return {grad_A, grad_B};
+        return {defined(grad_A, A), defined(grad_B, A)};
     }
     static tensor_list backward(AutogradContext* ctx, tensor_list grads) {
         auto saved = ctx->get_saved_variables();
         Tensor grad_output = saved[0], A = saved[1], B = saved[2], C = saved[3];
         Tensor indices_A = saved[4], indices_B = saved[5], indices_output = saved[6];
-        Tensor gg_A = grads[0].defined() ? grads[0].contiguous() : Tensor();
-        Tensor gg_B = grads[1].defined() ? grads[1].contiguous() : Tensor();
+        // a placeholder output (gradient not requested in the first backward) has no gradient
+        Tensor gg_A = grads[0].defined() && grads[0].sizes() == A.sizes() ? grads[0].contiguous()
+                                                                           : Tensor();
+        Tensor gg_B = grads[1].defined() && grads[1].sizes() == B.sizes() ? grads[1].contiguous()
+                                                                           : Tensor();
         Tensor gg_output = maybe_empty_like(grad_output);
         Tensor grad_A_2 = maybe_empty_like(A), grad_B_2 = maybe_empty_like(B);
         on_stream_of(A, [&] {
@@ -250,7 +260,7 @@ struct Sap : torch::autograd::Function<Sap> {
     static tensor_list backward(AutogradContext* ctx, tensor_list grad_outputs) {
         auto s = ctx->get_saved_variables();
         auto r = SapBackward::apply(grad_outputs[0].contiguous(), s[0], s[1], s[2], s[3], s[4], s[5]);
-        return {r[0], r[1], Tensor(), Tensor(), Tensor(), Tensor(), Tensor()};
+        return {requested(r[0]), requested(r[1]), Tensor(), Tensor(), Tensor(), Tensor(), Tensor()};
     }
 };
 
@@ -267,7 +277,7 @@ struct OpsaBackward : torch::autograd::Function<OpsaBackward> {
                     view<int32_t, 1>(indices_output));
             });
         });
-        return {grad_A, grad_B};
+        return {defined(grad_A, A), defined(grad_B, A)};
     }
     static tensor_list backward(AutogradContext*, tensor_list) {
         no_second_derivative("outer_product_scatter_add");
@@ -302,7 +312,7 @@ struct Opsa : torch::autograd::Function<Opsa> {
     static tensor_list backward(AutogradContext* ctx, tensor_list grad_outputs) {
         auto s = ctx->get_saved_variables();
         auto r = OpsaBackward::apply(grad_outputs[0].contiguous(), s[0], s[1], s[2]);
-        return {r[0], r[1], Tensor(), Tensor()};
+        return {requested(r[0]), requested(r[1]), Tensor(), Tensor()};
     }
 };
 
@@ -321,7 +331,7 @@ struct OpsawBackward : torch::autograd::Function<OpsawBackward> {
                     view<int32_t, 1>(indices_output));
             });
         });
-        return {grad_A, grad_B, grad_W};
+        return {defined(grad_A, A), defined(grad_B, A), defined(grad_W, A)};
     }
     static tensor_list backward(AutogradContext*, tensor_list) {
         no_second_derivative("outer_product_scatter_add_with_weights");
@@ -363,7 +373,7 @@ struct Opsaw : torch::autograd::Function<Opsaw> {
     static tensor_list backward(AutogradContext* ctx, tensor_list grad_outputs) {
         auto s = ctx->get_saved_variables();
         auto r = OpsawBackward::apply(grad_outputs[0].contiguous(), s[0], s[1], s[2], s[3], s[4]);
-        return {r[0], r[1], r[2], Tensor(), Tensor()};
+        return {requested(r[0]), requested(r[1]), requested(r[2]), Tensor(), Tensor()};
     }
 };
 
@@ -391,7 +401,7 @@ struct SasawBackward : torch::autograd::Function<SasawBackward> {
                         view<int32_t, 1>(indices_output_1), view<int32_t, 1>(indices_output_2));
                 });
         });
-        return {grad_A, grad_B, grad_W};
+        return {defined(grad_A, A), defined(grad_B, A), defined(grad_W, A)};
     }
     static tensor_list backward(AutogradContext*, tensor_list) {
         no_second_derivative("sparse_accumulation_scatter_add_with_weights");
@@ -446,7 +456,7 @@ struct Sasaw : torch::autograd::Function<Sasaw> {
         auto s = ctx->get_saved_variables();
         auto r = SasawBackward::apply(grad_outputs[0].contiguous(), s[0], s[1], s[2], s[3], s[4],
                                       s[5], s[6], s[7], s[8]);
-        return {r[0], r[1], Tensor(), r[2], Tensor(), Tensor(), Tensor(), Tensor(), Tensor(), Tensor()};
+        return {requested(r[0]), requested(r[1]), Tensor(), requested(r[2]), Tensor(), Tensor(), Tensor(), Tensor(), Tensor(), Tensor()};
     }
 };
 
