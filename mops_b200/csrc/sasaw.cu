@@ -49,6 +49,10 @@ template <typename T> struct Coupling {
     int32_t* start; // [ncell + 1]  first grouped position of each cell
     int32_t* order; // [N]  scratch for the sort
     int N, ncell;
+    // Optional dense form for the fast kernels: D[cc][m1] = sum of C[n] over the entries of
+    // compact cell cc = m3 * nW1 + m2 with M1[n] = m1; rows of d_stride scalars.
+    T* D;
+    int d_stride;
 };
 
 constexpr int kBuildThreads = 256;
@@ -127,6 +131,17 @@ sasaw_group_coupling(Coupling<T> cp, const T* __restrict__ C, const int32_t* __r
         clamp_index(m1, nA);
         cp.C[pos] = C[n];
         cp.M1[pos] = m1;
+    }
+    if (cp.D != nullptr) {
+        __syncthreads();
+        // one thread per cell, entries in ascending n: reproducible sums
+        for (int c = tid; c < ncell; c += kBuildThreads) {
+            const int m3 = c / cell_stride, m2 = c - m3 * cell_stride;
+            if (m2 >= nW1) continue;
+            T* row = cp.D + static_cast<size_t>(m3 * nW1 + m2) * cp.d_stride;
+            for (int m = 0; m < cp.d_stride; m++) row[m] = T(0);
+            for (int pos = cp.start[c]; pos < cp.start[c + 1]; pos++) row[cp.M1[pos]] += cp.C[pos];
+        }
     }
 }
 
@@ -314,49 +329,71 @@ __global__ void sasaw_vjp(T* __restrict__ gA, T* __restrict__ gB, T* __restrict_
 }
 
 // ---------------------------------------------------------------------------- fast kernels
-// For W.shape[1] <= 16. TP is W.shape[1] rounded up to a multiple of four: cells are numbered
-// m3 * TP + m2, so a row of T_e is read with 16-byte broadcasts, and the edge's W values
-// W[J_e, :, b] sit in registers (one load each per edge instead of one per cell).
-
-template <typename T> struct FastShared {
-    T* C;
-    T* warp_base;
-    int32_t* M1;
-    int32_t* cell;
-    int32_t* start;
-};
+// For A.shape[1] <= 16 and W.shape[1] <= 16 (angular channels up to l = 3). Template
+// parameters: TP = W.shape[1] rounded up to a multiple of four, NAP = A.shape[1] rounded up
+// likewise. Differences from the general kernels above:
+//   * the coupling table is used in dense form D[cell][m1] (built once per call), so that
+//     T_e = D a_e is a branch-free matrix-vector product with lanes over cells and the A row
+//     in registers, and the reverse contraction gA_e = D^T U_e likewise;
+//   * T_e rows are padded to TP and read as 16-byte broadcasts;
+//   * the edge's W values W[J_e, :, b] sit in registers (one load each per edge instead of
+//     one per cell);
+//   * sums over the 32 lanes (U_e, gA_e) use a recursive-halving shuffle reduction.
 
 __host__ __device__ inline size_t round4(size_t n) { return (n + 3) / 4 * 4; }
-
-template <typename T>
-__device__ __forceinline__ FastShared<T> carve_fast(unsigned char* raw, const Coupling<T>& cp,
-                                                    size_t per_warp, int warps, bool with_cell) {
-    FastShared<T> s;
-    s.C = reinterpret_cast<T*>(raw);
-    s.warp_base = s.C + round4(cp.N);
-    T* end = s.warp_base + per_warp * warps;
-    s.M1 = reinterpret_cast<int32_t*>(end);
-    s.cell = s.M1 + cp.N;
-    s.start = with_cell ? s.cell + cp.N : s.cell;
-    return s;
-}
-
-template <typename T>
-__device__ __forceinline__ void load_coupling_fast(const FastShared<T>& s, const Coupling<T>& cp,
-                                                   bool with_cell) {
-    for (int i = threadIdx.x; i < cp.N; i += blockDim.x) {
-        s.C[i] = cp.C[i];
-        s.M1[i] = cp.M1[i];
-        if (with_cell) s.cell[i] = cp.cell[i];
-    }
-    for (int i = threadIdx.x; i <= cp.ncell; i += blockDim.x) s.start[i] = cp.start[i];
-}
 
 template <typename T, int N> struct Vec;
 template <> struct Vec<double, 2> { using type = double2; };
 template <> struct Vec<float, 4> { using type = float4; };
 
-// p = sum_m2 T_row[m2] * w[m2], the row read as 16-byte broadcasts.
+// Block-shared part of the fast kernels' shared memory.
+template <typename T> struct Dense {
+    T* D;          // [ncc][ds]
+    int32_t* tpos; // [ncc] position of compact cell cc in a padded T_e / U_e
+    T* warp_base;  // per-warp scalars start here (16-byte aligned)
+};
+
+template <typename T>
+__device__ __forceinline__ Dense<T> carve_dense(unsigned char* raw, int ncc, int ds) {
+    Dense<T> d;
+    d.D = reinterpret_cast<T*>(raw);
+    const size_t d_scalars = round4(static_cast<size_t>(ncc) * ds);
+    d.warp_base = d.D + d_scalars;
+    d.tpos = nullptr; // set by the caller after the per-warp area
+    return d;
+}
+
+template <typename T>
+__device__ __forceinline__ void load_dense(const Dense<T>& d, const Coupling<T>& cp, int ncc,
+                                           int ds, int nW1, int TP) {
+    for (int i = threadIdx.x; i < ncc * ds; i += blockDim.x) d.D[i] = cp.D[i];
+    for (int cc = threadIdx.x; cc < ncc; cc += blockDim.x) {
+        const int m3 = cc / nW1;
+        d.tpos[cc] = m3 * TP + (cc - m3 * nW1);
+    }
+}
+
+// T_e = D a_e: lanes over compact cells, the A row in registers.
+template <typename T, int NAP>
+__device__ __forceinline__ void dense_contract(const Dense<T>& d, int ncc, int ds,
+                                               const T* __restrict__ a_row, int nA, T* T_s,
+                                               T* U_s, int lane) {
+    T a[NAP];
+#pragma unroll
+    for (int m = 0; m < NAP; m++) a[m] = m < nA ? __ldg(a_row + m) : T(0);
+    __syncwarp(); // the previous edge's readers of T_s / U_s are done
+    for (int cc = lane; cc < ncc; cc += 32) {
+        const T* row = d.D + cc * ds;
+        T t = T(0);
+#pragma unroll
+        for (int m = 0; m < NAP; m++) t += row[m] * a[m];
+        const int pos = d.tpos[cc];
+        T_s[pos] = t;
+        if (U_s != nullptr) U_s[pos] = T(0);
+    }
+    __syncwarp();
+}
+
 template <typename T, int TP>
 __device__ __forceinline__ T dot_row(const T* __restrict__ row, const T (&w)[TP]) {
     constexpr int V = 16 / sizeof(T);
@@ -375,7 +412,7 @@ __device__ __forceinline__ T dot_row(const T* __restrict__ row, const T (&w)[TP]
     return p;
 }
 
-template <typename T, int TP, bool SEGMENTED>
+template <typename T, int TP, int NAP, bool SEGMENTED>
 __global__ void sasaw_fwd_fast(T* __restrict__ O, const T* __restrict__ A, const T* __restrict__ B,
                                const T* __restrict__ W, const int32_t* __restrict__ Jw,
                                const int32_t* __restrict__ Io,
@@ -384,29 +421,22 @@ __global__ void sasaw_fwd_fast(T* __restrict__ O, const T* __restrict__ A, const
                                Status st) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int ncell = cp.ncell; // nO1 * TP
+    const int ncc = nO1 * nW1, ds = cp.d_stride, tsize = nO1 * TP;
     const size_t rowsize = static_cast<size_t>(nO1) * L;
-    const size_t per_warp = round4(ncell) + (SEGMENTED ? round4(rowsize) : 0) + round4(nA);
+    const size_t per_warp = round4(tsize) + (SEGMENTED ? round4(rowsize) : 0);
     if (SEGMENTED ? saw_unsorted(st) : (!always && !saw_unsorted(st))) return;
-    FastShared<T> s = carve_fast<T>(smem_raw, cp, per_warp, warps, false);
-    load_coupling_fast(s, cp, false);
+    Dense<T> d = carve_dense<T>(smem_raw, ncc, ds);
+    d.tpos = reinterpret_cast<int32_t*>(d.warp_base + per_warp * warps);
+    load_dense(d, cp, ncc, ds, nW1, TP);
+    T* T_s = d.warp_base + per_warp * warp; // [nO1][TP], 16-byte aligned
+    T* Oacc = T_s + round4(tsize);
+    for (int i = lane; i < tsize; i += 32) T_s[i] = T(0); // padding columns stay zero
     __syncthreads();
-    T* T_s = s.warp_base + per_warp * warp; // [nO1][TP], 16-byte aligned
-    T* Oacc = T_s + round4(ncell);
-    T* a_s = Oacc + (SEGMENTED ? round4(rowsize) : 0);
 
     auto edge = [&](int64_t e, int64_t out_row) {
         int32_t j = __ldg(Jw + e);
         if (clamp_index(j, static_cast<int32_t>(nW0)) && lane == 0) report_bad_index(st, kBitJ);
-        __syncwarp();
-        for (int m = lane; m < nA; m += 32) a_s[m] = A[e * nA + m];
-        __syncwarp();
-        for (int c = lane; c < ncell; c += 32) {
-            T t = T(0);
-            for (int pos = s.start[c]; pos < s.start[c + 1]; pos++) t += s.C[pos] * a_s[s.M1[pos]];
-            T_s[c] = t;
-        }
-        __syncwarp();
+        dense_contract<T, NAP>(d, ncc, ds, A + e * nA, nA, T_s, static_cast<T*>(nullptr), lane);
         const T* wrow = W + static_cast<int64_t>(j) * nW1 * L;
         for (int b0 = 0; b0 < L; b0 += 32) {
             const int b = b0 + lane;
@@ -472,7 +502,7 @@ template <typename T, int VP> __device__ __forceinline__ T reduce_to_lanes(T (&v
 template <int TP> struct Pow2 { static constexpr int value = TP <= 4 ? 4 : TP <= 8 ? 8 : 16; };
 template <int VP> struct Log2 { static constexpr int value = VP == 4 ? 2 : VP == 8 ? 3 : 4; };
 
-template <typename T, int TP>
+template <typename T, int TP, int NAP>
 __global__ void sasaw_vjp_fast(T* __restrict__ gA, T* __restrict__ gB, T* __restrict__ gW,
                                const T* __restrict__ gO, const T* __restrict__ A,
                                const T* __restrict__ B, const T* __restrict__ W,
@@ -483,15 +513,15 @@ __global__ void sasaw_vjp_fast(T* __restrict__ gA, T* __restrict__ gB, T* __rest
     constexpr int kShift = 5 - Log2<VP>::value;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int ncell = cp.ncell, N = cp.N;
-    const size_t per_warp = 2 * round4(ncell) + round4(nA) + round4(static_cast<size_t>(nA) * 33);
-    FastShared<T> s = carve_fast<T>(smem_raw, cp, per_warp, warps, true);
-    load_coupling_fast(s, cp, true);
+    const int ncc = nO1 * nW1, ds = cp.d_stride, tsize = nO1 * TP;
+    const size_t per_warp = 2 * round4(tsize);
+    Dense<T> d = carve_dense<T>(smem_raw, ncc, ds);
+    d.tpos = reinterpret_cast<int32_t*>(d.warp_base + per_warp * warps);
+    load_dense(d, cp, ncc, ds, nW1, TP);
+    T* T_s = d.warp_base + per_warp * warp;
+    T* U_s = T_s + round4(tsize);
+    for (int i = lane; i < tsize; i += 32) T_s[i] = T(0);
     __syncthreads();
-    T* T_s = s.warp_base + per_warp * warp;
-    T* U_s = T_s + round4(ncell);
-    T* a_s = U_s + round4(ncell);
-    T* ga_priv = a_s + round4(nA); // [nA][33]: one private column per lane
     const int64_t rowsize = static_cast<int64_t>(nO1) * L;
     const bool want_a = gA != nullptr, want_b = gB != nullptr, want_w = gW != nullptr;
     const int my_value = lane >> kShift;
@@ -502,16 +532,7 @@ __global__ void sasaw_vjp_fast(T* __restrict__ gA, T* __restrict__ gB, T* __rest
         int32_t row = __ldg(Io + e), j = __ldg(Jw + e);
         if (clamp_index(row, static_cast<int32_t>(nW0)) && lane == 0) report_bad_index(st, kBitI);
         if (clamp_index(j, static_cast<int32_t>(nW0)) && lane == 0) report_bad_index(st, kBitJ);
-        __syncwarp();
-        for (int m = lane; m < nA; m += 32) a_s[m] = A[e * nA + m];
-        __syncwarp();
-        for (int c = lane; c < ncell; c += 32) {
-            T t = T(0);
-            for (int pos = s.start[c]; pos < s.start[c + 1]; pos++) t += s.C[pos] * a_s[s.M1[pos]];
-            T_s[c] = t;
-            U_s[c] = T(0);
-        }
-        __syncwarp();
+        dense_contract<T, NAP>(d, ncc, ds, A + e * nA, nA, T_s, U_s, lane);
         const T* g = gO + static_cast<int64_t>(row) * rowsize;
         const T* wrow = W + static_cast<int64_t>(j) * nW1 * L;
         T* gw = want_w ? gW + static_cast<int64_t>(j) * nW1 * L : nullptr;
@@ -559,17 +580,20 @@ __global__ void sasaw_vjp_fast(T* __restrict__ gA, T* __restrict__ gB, T* __rest
             if (want_b && valid) gB[e * L + b] = gb;
         }
         if (want_a) {
+            // gA_e = D^T U_e: lanes over cells, then one sum over lanes per component
             __syncwarp();
-            for (int idx = lane; idx < nA * 33; idx += 32) ga_priv[idx] = T(0);
-            __syncwarp();
-            for (int pos = lane; pos < N; pos += 32)
-                ga_priv[s.M1[pos] * 33 + lane] += s.C[pos] * U_s[s.cell[pos]];
-            __syncwarp();
-            for (int m = lane; m < nA; m += 32) {
-                T sum = T(0);
-                for (int l = 0; l < 32; l++) sum += ga_priv[m * 33 + l];
-                gA[e * nA + m] = sum;
+            T ga[16];
+#pragma unroll
+            for (int m = 0; m < 16; m++) ga[m] = T(0);
+            for (int cc = lane; cc < ncc; cc += 32) {
+                const T u = U_s[d.tpos[cc]];
+                const T* drow = d.D + cc * ds;
+#pragma unroll
+                for (int m = 0; m < NAP; m++) ga[m] += drow[m] * u;
             }
+            const T total = reduce_to_lanes<T, 16>(ga, lane);
+            const int m = lane >> 1;
+            if ((lane & 1) == 0 && m < nA) gA[e * nA + m] = total;
         }
     }
 }
@@ -659,7 +683,7 @@ template <typename T> struct Problem {
 // cannot be used (cell grid too large for one block's shared memory).
 template <typename T>
 bool build_coupling(const Call& call, const Problem<T>& p, Coupling<T>& cp, void** scratch,
-                    int cell_stride = 0) {
+                    int cell_stride = 0, int d_stride = 0) {
     if (cell_stride == 0) cell_stride = p.nW1;
     const int64_t ncell64 = static_cast<int64_t>(p.nO1) * cell_stride;
     if (ncell64 > 8192 || ncell64 == 0) return false;
@@ -667,9 +691,15 @@ bool build_coupling(const Call& call, const Problem<T>& p, Coupling<T>& cp, void
     cp.ncell = static_cast<int>(ncell64);
     const size_t nT = (static_cast<size_t>(p.N) * sizeof(T) + 15) / 16 * 16;
     const size_t nI = static_cast<size_t>(p.N) * sizeof(int32_t);
-    const size_t bytes = nT + 3 * nI + (cp.ncell + 1) * sizeof(int32_t) + 16;
+    const size_t nStart = ((cp.ncell + 1) * sizeof(int32_t) + 15) / 16 * 16;
+    const size_t nD = static_cast<size_t>(d_stride) * p.nO1 * p.nW1 * sizeof(T);
+    const size_t bytes = nT + 3 * nI + nStart + 16 + nD;
     unsigned char* base = static_cast<unsigned char*>(scratch_alloc(call, bytes));
     *scratch = base;
+    cp.d_stride = d_stride;
+    cp.D = d_stride > 0
+               ? reinterpret_cast<T*>(base + (nT + 3 * nI + nStart + 15) / 16 * 16)
+               : nullptr;
     cp.C = reinterpret_cast<T*>(base);
     cp.M1 = reinterpret_cast<int32_t*>(base + nT);
     cp.cell = cp.M1 + p.N;
@@ -710,12 +740,10 @@ template <typename Kernel> void allow_smem(Kernel kernel, size_t smem) {
 
 // Shared memory of a fast-kernel block, and the largest warp count (8, 4, 2, 1) that fits.
 template <typename T>
-int pick_warps_fast(const Call& call, const Coupling<T>& cp, size_t per_warp, bool with_cell,
-                    size_t* smem) {
+int pick_warps_fast(const Call& call, int ncc, int ds, size_t per_warp, size_t* smem) {
     for (int warps : {8, 4, 2, 1}) {
-        const size_t bytes = (round4(cp.N) + per_warp * warps) * sizeof(T) +
-                             (static_cast<size_t>(cp.N) * (with_cell ? 2 : 1) + cp.ncell + 1) *
-                                 sizeof(int32_t);
+        const size_t bytes = (round4(static_cast<size_t>(ncc) * ds) + per_warp * warps) * sizeof(T) +
+                             static_cast<size_t>(ncc) * sizeof(int32_t);
         const size_t limit = warps == 1 ? static_cast<size_t>(max_optin_smem(call.device)) : 100 * 1024;
         if (bytes <= limit) {
             *smem = bytes;
@@ -725,32 +753,30 @@ int pick_warps_fast(const Call& call, const Coupling<T>& cp, size_t per_warp, bo
     return 0;
 }
 
-// Width of a T_e row in the fast kernels: W.shape[1] rounded up to a multiple of four, or 0
-// when the fast kernels do not apply.
-inline int fast_row_width(int nW1) { return nW1 >= 1 && nW1 <= 16 ? (nW1 + 3) / 4 * 4 : 0; }
+// Padded widths used by the fast kernels (0: not applicable).
+inline int fast_width(int n) { return n >= 1 && n <= 16 ? (n + 3) / 4 * 4 : 0; }
 
-template <typename T, int TP>
+template <typename T, int TP, int NAP>
 bool forward_fast(const Call& call, T* O, const Problem<T>& p) {
     const int64_t rowsize = static_cast<int64_t>(p.nO1) * p.L;
+    const int ncc = p.nO1 * p.nW1, ds = NAP + 1; // odd row stride: conflict-free row-per-lane reads
+    if (static_cast<int64_t>(p.nO1) * p.nW1 > 1024) return false;
     const int grid_generic = sm_count(call.device) * 8;
+    size_t smem_seg = 0, smem_edge = 0;
+    const size_t tsize = round4(static_cast<size_t>(p.nO1) * TP);
+    const int warps_seg = pick_warps_fast<T>(call, ncc, ds, tsize + round4(rowsize), &smem_seg);
+    const int warps_edge = pick_warps_fast<T>(call, ncc, ds, tsize, &smem_edge);
+    if (warps_seg == 0 || warps_edge == 0) return false;
     Coupling<T> cp{};
     void* scratch = nullptr;
-    if (!build_coupling(call, p, cp, &scratch, TP)) return false;
-    size_t smem_seg = 0, smem_edge = 0;
-    const size_t base = round4(cp.ncell) + round4(p.nA);
-    const int warps_seg = pick_warps_fast(call, cp, base + round4(rowsize), false, &smem_seg);
-    const int warps_edge = pick_warps_fast(call, cp, base, false, &smem_edge);
-    if (warps_seg == 0 || warps_edge == 0) {
-        scratch_free(call, scratch);
-        return false;
-    }
+    if (!build_coupling(call, p, cp, &scratch, TP, ds)) return false;
     int64_t* offsets = static_cast<int64_t*>(scratch_alloc(call, (p.nW0 + 1) * sizeof(int64_t)));
     const int64_t pre_blocks = std::min<int64_t>(ceil_div(p.E + 1, 256), grid_generic * 4);
     segment_offsets<<<static_cast<unsigned>(pre_blocks), 256, 0, call.stream>>>(
         p.Io, p.E, p.nW0, offsets, call.status);
-    allow_smem(sasaw_fwd_fast<T, TP, true>, smem_seg);
-    sasaw_fwd_fast<T, TP, true><<<static_cast<unsigned>(ceil_div(p.nW0, warps_seg)),
-                                  warps_seg * 32, smem_seg, call.stream>>>(
+    allow_smem(sasaw_fwd_fast<T, TP, NAP, true>, smem_seg);
+    sasaw_fwd_fast<T, TP, NAP, true><<<static_cast<unsigned>(ceil_div(p.nW0, warps_seg)),
+                                       warps_seg * 32, smem_seg, call.stream>>>(
         O, p.A, p.B, p.W, p.Jw, p.Io, offsets, cp, p.E, p.nA, p.L, p.nW0, p.nW1, p.nO1, false,
         call.status);
     MOPS_CUDA_OK(cudaGetLastError());
@@ -762,40 +788,64 @@ bool forward_fast(const Call& call, T* O, const Problem<T>& p) {
     }
     if (need_fallback) {
         zero_if_unsorted<T><<<grid_generic, 256, 0, call.stream>>>(O, p.nW0 * rowsize, call.status);
-        allow_smem(sasaw_fwd_fast<T, TP, false>, smem_edge);
+        allow_smem(sasaw_fwd_fast<T, TP, NAP, false>, smem_edge);
         const int64_t blocks = std::min<int64_t>(ceil_div(p.E, warps_edge), grid_generic);
-        sasaw_fwd_fast<T, TP, false><<<static_cast<unsigned>(blocks), warps_edge * 32, smem_edge,
-                                       call.stream>>>(O, p.A, p.B, p.W, p.Jw, p.Io, nullptr, cp,
-                                                      p.E, p.nA, p.L, p.nW0, p.nW1, p.nO1, false,
-                                                      call.status);
+        sasaw_fwd_fast<T, TP, NAP, false><<<static_cast<unsigned>(blocks), warps_edge * 32,
+                                            smem_edge, call.stream>>>(
+            O, p.A, p.B, p.W, p.Jw, p.Io, nullptr, cp, p.E, p.nA, p.L, p.nW0, p.nW1, p.nO1, false,
+            call.status);
     }
     MOPS_CUDA_OK(cudaGetLastError());
     scratch_free(call, scratch);
     return true;
 }
 
-template <typename T, int TP>
+template <typename T, int TP, int NAP>
 bool backward_fast(const Call& call, T* gA, T* gB, T* gW, const T* gO, const Problem<T>& p) {
+    const int ncc = p.nO1 * p.nW1, ds = NAP + 1;
+    if (static_cast<int64_t>(p.nO1) * p.nW1 > 1024) return false;
+    size_t smem = 0;
+    const int warps =
+        pick_warps_fast<T>(call, ncc, ds, 2 * round4(static_cast<size_t>(p.nO1) * TP), &smem);
+    if (warps == 0) return false;
     Coupling<T> cp{};
     void* scratch = nullptr;
-    if (!build_coupling(call, p, cp, &scratch, TP)) return false;
-    size_t smem = 0;
-    const size_t per_warp = 2 * round4(cp.ncell) + round4(p.nA) + round4(static_cast<size_t>(p.nA) * 33);
-    const int warps = pick_warps_fast(call, cp, per_warp, true, &smem);
-    if (warps == 0) {
-        scratch_free(call, scratch);
-        return false;
-    }
-    allow_smem(sasaw_vjp_fast<T, TP>, smem);
+    if (!build_coupling(call, p, cp, &scratch, TP, ds)) return false;
+    allow_smem(sasaw_vjp_fast<T, TP, NAP>, smem);
     const int64_t blocks =
         std::min<int64_t>(ceil_div(p.E, warps), static_cast<int64_t>(sm_count(call.device)) * 16);
-    sasaw_vjp_fast<T, TP><<<static_cast<unsigned>(blocks), warps * 32, smem, call.stream>>>(
+    sasaw_vjp_fast<T, TP, NAP><<<static_cast<unsigned>(blocks), warps * 32, smem, call.stream>>>(
         gA, gB, gW, gO, p.A, p.B, p.W, p.Jw, p.Io, cp, p.E, p.nA, p.L, p.nW0, p.nW1, p.nO1,
         call.status);
     MOPS_CUDA_OK(cudaGetLastError());
     scratch_free(call, scratch);
     return true;
 }
+
+// Dispatch on the two padded widths; returns false when the fast kernels do not apply.
+#define MOPS_B200_SASAW_FAST(FN, ...)                                                              \
+    [&]() -> bool {                                                                                \
+        const int tp = fast_width(p.nW1), nap = fast_width(p.nA);                                  \
+        if (tp == 0 || nap == 0) return false;                                                     \
+        switch (tp * 100 + nap) {                                                                  \
+        case 404: return FN<T, 4, 4>(__VA_ARGS__);                                                 \
+        case 408: return FN<T, 4, 8>(__VA_ARGS__);                                                 \
+        case 412: return FN<T, 4, 12>(__VA_ARGS__);                                                \
+        case 416: return FN<T, 4, 16>(__VA_ARGS__);                                                \
+        case 804: return FN<T, 8, 4>(__VA_ARGS__);                                                 \
+        case 808: return FN<T, 8, 8>(__VA_ARGS__);                                                 \
+        case 812: return FN<T, 8, 12>(__VA_ARGS__);                                                \
+        case 816: return FN<T, 8, 16>(__VA_ARGS__);                                                \
+        case 1204: return FN<T, 12, 4>(__VA_ARGS__);                                               \
+        case 1208: return FN<T, 12, 8>(__VA_ARGS__);                                               \
+        case 1212: return FN<T, 12, 12>(__VA_ARGS__);                                              \
+        case 1216: return FN<T, 12, 16>(__VA_ARGS__);                                              \
+        case 1604: return FN<T, 16, 4>(__VA_ARGS__);                                               \
+        case 1608: return FN<T, 16, 8>(__VA_ARGS__);                                               \
+        case 1612: return FN<T, 16, 12>(__VA_ARGS__);                                              \
+        default: return FN<T, 16, 16>(__VA_ARGS__);                                                \
+        }                                                                                          \
+    }()
 
 template <typename T> void forward(const Call& call, T* O, const Problem<T>& p) {
     const int64_t rowsize = static_cast<int64_t>(p.nO1) * p.L;
@@ -804,13 +854,7 @@ template <typename T> void forward(const Call& call, T* O, const Problem<T>& p) 
         MOPS_CUDA_OK(cudaMemsetAsync(O, 0, p.nW0 * rowsize * sizeof(T), call.stream));
         return;
     }
-    switch (fast_row_width(p.nW1)) {
-    case 4: if (forward_fast<T, 4>(call, O, p)) return; break;
-    case 8: if (forward_fast<T, 8>(call, O, p)) return; break;
-    case 12: if (forward_fast<T, 12>(call, O, p)) return; break;
-    case 16: if (forward_fast<T, 16>(call, O, p)) return; break;
-    default: break;
-    }
+    if (MOPS_B200_SASAW_FAST(forward_fast, call, O, p)) return;
     const int grid_generic = sm_count(call.device) * 8;
     Coupling<T> cp{};
     void* scratch = nullptr;
@@ -860,15 +904,7 @@ void backward(const Call& call, T* gA, T* gB, T* gW, const T* gO, const Problem<
         MOPS_CUDA_OK(cudaMemsetAsync(gW, 0, wsize * sizeof(T), call.stream));
     if (p.E == 0) return;
     const bool empty = p.N == 0 || p.L == 0 || p.nO1 == 0 || p.nW1 == 0 || p.nA == 0;
-    if (!empty) {
-        switch (fast_row_width(p.nW1)) {
-        case 4: if (backward_fast<T, 4>(call, gA, gB, gW, gO, p)) return; break;
-        case 8: if (backward_fast<T, 8>(call, gA, gB, gW, gO, p)) return; break;
-        case 12: if (backward_fast<T, 12>(call, gA, gB, gW, gO, p)) return; break;
-        case 16: if (backward_fast<T, 16>(call, gA, gB, gW, gO, p)) return; break;
-        default: break;
-        }
-    }
+    if (!empty && MOPS_B200_SASAW_FAST(backward_fast, call, gA, gB, gW, gO, p)) return;
     Coupling<T> cp{};
     void* scratch = nullptr;
     const bool grouped = !empty && build_coupling(call, p, cp, &scratch);
