@@ -29,6 +29,7 @@
 // accumulated with RED because indices_W_1 is not sorted.
 #include <algorithm>
 #include <mutex>
+#include <type_traits>
 
 #include "checks.hpp"
 #include "device.cuh"
@@ -363,13 +364,14 @@ __device__ __forceinline__ Dense<T> carve_dense(unsigned char* raw, int ncc, int
     return d;
 }
 
+// `stride`: row stride of the per-edge T_e buffer; `transposed`: T_e stored as [m2][m3].
 template <typename T>
 __device__ __forceinline__ void load_dense(const Dense<T>& d, const Coupling<T>& cp, int ncc,
-                                           int ds, int nW1, int TP) {
+                                           int ds, int nW1, int stride, bool transposed = false) {
     for (int i = threadIdx.x; i < ncc * ds; i += blockDim.x) d.D[i] = cp.D[i];
     for (int cc = threadIdx.x; cc < ncc; cc += blockDim.x) {
-        const int m3 = cc / nW1;
-        d.tpos[cc] = m3 * TP + (cc - m3 * nW1);
+        const int m3 = cc / nW1, m2 = cc - m3 * nW1;
+        d.tpos[cc] = transposed ? m2 * stride + m3 : m3 * stride + m2;
     }
 }
 
@@ -390,6 +392,21 @@ __device__ __forceinline__ void dense_contract(const Dense<T>& d, int ncc, int d
         const int pos = d.tpos[cc];
         T_s[pos] = t;
         if (U_s != nullptr) U_s[pos] = T(0);
+    }
+    __syncwarp();
+}
+
+// Same, with the A row already in registers.
+template <typename T, int NAP>
+__device__ __forceinline__ void dense_contract_regs(const Dense<T>& d, int ncc, int ds,
+                                                    const T (&a)[NAP], T* T_s, int lane) {
+    __syncwarp(); // the previous edge's readers of T_s are done
+    for (int cc = lane; cc < ncc; cc += 32) {
+        const T* row = d.D + cc * ds;
+        T t = T(0);
+#pragma unroll
+        for (int m = 0; m < NAP; m++) t += row[m] * a[m];
+        T_s[d.tpos[cc]] = t;
     }
     __syncwarp();
 }
@@ -594,6 +611,200 @@ __global__ void sasaw_vjp_fast(T* __restrict__ gA, T* __restrict__ gB, T* __rest
             const T total = reduce_to_lanes<T, 16>(ga, lane);
             const int m = lane >> 1;
             if ((lane & 1) == 0 && m < nA) gA[e * nA + m] = total;
+        }
+    }
+}
+
+// ------------------------------------------------------------------- tensor-core kernels
+// Forward, f64 only, A.shape[1], W.shape[1] and output_size all <= 16. Profiling the kernel
+// above showed the dense contraction
+//     P[m3, b] = sum_m2 T_e[m3, m2] W[J_e, m2, b]          (9x9 by 9x32 at the benchmark shape)
+// and its operand reads dominating the instruction stream. It runs here on the FP64
+// tensor-core path (mma.sync m8n8k4: 256 multiply-adds per warp instruction instead of 32):
+// the W rows arrive in shared memory by cp.async one edge ahead, in a bank-conflict-free
+// layout, and the output row is accumulated in registers across the whole segment.
+// (The same was tried for the VJP's U_e = X W^T contraction; with the extra staging it was
+// slower than the shuffle reduction at the occupancy its shared memory allows, so the VJP
+// stays on the kernel above.)
+// Fragment layout of m8n8k4 (lane = 4*qr + qc): A[qr][qc], B[k = qc][n = qr],
+// C[qr][2*qc + {0,1}].
+
+__device__ __forceinline__ void dmma(double (&c)[2], double a, double b) {
+    asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};\n"
+                 : "+d"(c[0]), "+d"(c[1])
+                 : "d"(a), "d"(b));
+}
+
+// Row stride for an A-operand matrix read as 8 rows x 4 columns per fragment: a multiple of
+// four that is 4 or 12 modulo 16, so that the eight rows fall on distinct banks.
+__host__ __device__ constexpr int a_stride(int cols4) { return cols4 % 8 == 4 ? cols4 : cols4 + 4; }
+constexpr int kBStride = 40; // B-operand matrix read as 4 rows x 8 columns per fragment
+
+// Per-warp shared memory of the forward kernel, in doubles.
+template <int TP, int NAP> struct FwdMmaLayout {
+    static constexpr int TS = a_stride(TP);
+    static constexpr int T = 0;                          // [16][TS]        T_e
+    static constexpr int W = 16 * TS;                    // [2][TP][kBStride] W[J_e] rows, two stages
+    static constexpr int B = W + 2 * TP * kBStride;      // [2][32]         B[e, b0..b0+31]
+    static constexpr int A = B + 2 * 32;                 // [2][NAP]        A[e, :]
+    static constexpr int total = (A + 2 * NAP + 3) / 4 * 4;
+};
+
+template <int TP, int NAP, bool SEGMENTED>
+__global__ void __launch_bounds__(256, 2)
+sasaw_fwd_mma(double* __restrict__ O, const double* __restrict__ A, const double* __restrict__ B,
+              const double* __restrict__ W, const int32_t* __restrict__ Jw,
+              const int32_t* __restrict__ Io, const int64_t* __restrict__ offsets,
+              Coupling<double> cp, int64_t E, int nA, int L, int64_t nW0, int nW1, int nO1,
+              bool always, Status st) {
+    using T = double;
+    using Lay = FwdMmaLayout<TP, NAP>;
+    constexpr int TS = Lay::TS;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int qr = lane >> 2, qc = lane & 3;
+    const int ncc = nO1 * nW1, ds = cp.d_stride;
+    constexpr size_t per_warp = Lay::total;
+    if (SEGMENTED ? saw_unsorted(st) : (!always && !saw_unsorted(st))) return;
+    Dense<T> d = carve_dense<T>(smem_raw, ncc, ds);
+    d.tpos = reinterpret_cast<int32_t*>(d.warp_base + per_warp * warps);
+    load_dense(d, cp, ncc, ds, nW1, TS);
+    T* base = d.warp_base + per_warp * warp;
+    T* T_s = base + Lay::T; // rows >= nO1 and columns >= nW1 stay zero
+    T* w_st = base + Lay::W; // rows >= nW1 and columns >= L stay zero
+    T* b_st = base + Lay::B;
+    T* a_st = base + Lay::A; // entries >= nA stay zero
+    for (int i = lane; i < static_cast<int>(per_warp); i += 32) base[i] = T(0);
+    __syncthreads();
+    const size_t rowsize = static_cast<size_t>(nO1) * L;
+    const int mtiles = nO1 > 8 ? 2 : 1;
+
+    T acc[2][4][2];
+    auto clear = [&] {
+#pragma unroll
+        for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+            for (int nt = 0; nt < 4; nt++) acc[mt][nt][0] = acc[mt][nt][1] = T(0);
+    };
+    auto read_j = [&](int64_t e) -> int32_t {
+        int32_t j = __ldg(Jw + e);
+        if (clamp_index(j, static_cast<int32_t>(nW0)) && lane == 0) report_bad_index(st, kBitJ);
+        return j;
+    };
+    // Asynchronous copies of one edge's operands into stage `s` (one commit group).
+    auto issue = [&](int s, int64_t e, int32_t j, int b0) {
+        const int b = b0 + lane;
+        if (b < L) {
+            const T* wrow = W + static_cast<int64_t>(j) * nW1 * L + b;
+            T* dst = w_st + s * TP * kBStride + lane;
+            for (int m2 = 0; m2 < nW1; m2++) cp_async<8>(dst + m2 * kBStride, wrow + m2 * L);
+            cp_async<8>(b_st + s * 32 + lane, B + e * L + b);
+        }
+        if (lane < nA) cp_async<8>(a_st + s * NAP + lane, A + e * nA + lane);
+        cp_async_commit();
+    };
+    // acc += (T_e W[J_e]) scaled per column by B[e, b]
+    auto compute = [&](int s) {
+        T a[NAP];
+#pragma unroll
+        for (int m = 0; m < NAP; m++) a[m] = a_st[s * NAP + m];
+        dense_contract_regs<T, NAP>(d, ncc, ds, a, T_s, lane);
+        const T* w_s = w_st + s * TP * kBStride;
+        T p[2][4][2];
+#pragma unroll
+        for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+            for (int nt = 0; nt < 4; nt++) p[mt][nt][0] = p[mt][nt][1] = T(0);
+#pragma unroll
+        for (int ks = 0; ks < TP / 4; ks++) {
+            T af[2], bf[4];
+            af[0] = T_s[qr * TS + 4 * ks + qc];
+            af[1] = mtiles > 1 ? T_s[(8 + qr) * TS + 4 * ks + qc] : T(0);
+#pragma unroll
+            for (int nt = 0; nt < 4; nt++) bf[nt] = w_s[(4 * ks + qc) * kBStride + 8 * nt + qr];
+#pragma unroll
+            for (int nt = 0; nt < 4; nt++) {
+                dmma(p[0][nt], af[0], bf[nt]);
+                if (mtiles > 1) dmma(p[1][nt], af[1], bf[nt]);
+            }
+        }
+#pragma unroll
+        for (int nt = 0; nt < 4; nt++) {
+            const double2 bb = *reinterpret_cast<const double2*>(b_st + s * 32 + 8 * nt + 2 * qc);
+#pragma unroll
+            for (int mt = 0; mt < 2; mt++) {
+                acc[mt][nt][0] += bb.x * p[mt][nt][0];
+                acc[mt][nt][1] += bb.y * p[mt][nt][1];
+            }
+        }
+    };
+    // fragment element (mt, nt, u) is output element [m3 = 8*mt + qr][b = b0 + 8*nt + 2*qc + u]
+    auto flush = [&](int64_t out_row, int b0, bool atomic) {
+        T* dst = O + out_row * rowsize;
+#pragma unroll
+        for (int mt = 0; mt < 2; mt++) {
+            const int m3 = 8 * mt + qr;
+            if (m3 >= nO1) continue;
+#pragma unroll
+            for (int nt = 0; nt < 4; nt++) {
+#pragma unroll
+                for (int u = 0; u < 2; u++) {
+                    const int b = b0 + 8 * nt + 2 * qc + u;
+                    if (b < L) {
+                        if (atomic)
+                            red_add(dst + m3 * L + b, acc[mt][nt][u]);
+                        else
+                            dst[m3 * L + b] = acc[mt][nt][u];
+                    }
+                }
+            }
+        }
+    };
+
+    if (SEGMENTED) {
+        const int64_t r = static_cast<int64_t>(blockIdx.x) * warps + warp;
+        if (r >= nW0) return;
+        const int64_t begin = offsets[r], end = offsets[r + 1];
+        for (int b0 = 0; b0 < L; b0 += 32) {
+            clear();
+            int32_t j_next = 0;
+            __syncwarp();
+            if (begin < end) {
+                issue(0, begin, read_j(begin), b0);
+                if (begin + 1 < end) j_next = read_j(begin + 1);
+            }
+            int s = 0;
+            for (int64_t e = begin; e < end; e++, s ^= 1) {
+                if (e + 1 < end) {
+                    issue(s ^ 1, e + 1, j_next, b0);
+                    if (e + 2 < end) j_next = read_j(e + 2);
+                    cp_async_wait<1>();
+                } else {
+                    cp_async_wait<0>();
+                }
+                __syncwarp();
+                compute(s);
+                __syncwarp(); // stage s is overwritten by the copies issued next round
+            }
+            flush(r, b0, false);
+        }
+    } else {
+        const int64_t nwarps = static_cast<int64_t>(gridDim.x) * warps;
+        for (int64_t e = static_cast<int64_t>(blockIdx.x) * warps + warp; e < E; e += nwarps) {
+            int32_t row = __ldg(Io + e);
+            if (clamp_index(row, static_cast<int32_t>(nW0))) {
+                if (lane == 0) report_bad_index(st, kBitI);
+                continue;
+            }
+            for (int b0 = 0; b0 < L; b0 += 32) {
+                clear();
+                __syncwarp();
+                issue(0, e, read_j(e), b0);
+                cp_async_wait<0>();
+                __syncwarp();
+                compute(0);
+                flush(row, b0, true);
+            }
         }
     }
 }
@@ -822,6 +1033,55 @@ bool backward_fast(const Call& call, T* gA, T* gB, T* gW, const T* gO, const Pro
     return true;
 }
 
+// Tensor-core variants (f64, output_size <= 16 as well).
+template <typename T, int TP, int NAP>
+bool forward_mma(const Call& call, T* O, const Problem<T>& p) {
+    if constexpr (!std::is_same<T, double>::value) {
+        return false;
+    } else {
+        if (p.nO1 > 16) return false;
+        const int64_t rowsize = static_cast<int64_t>(p.nO1) * p.L;
+        const int ncc = p.nO1 * p.nW1, ds = NAP + 1;
+        const int grid_generic = sm_count(call.device) * 8;
+        size_t smem = 0;
+        const size_t per_warp = FwdMmaLayout<TP, NAP>::total;
+        const int warps = pick_warps_fast<T>(call, ncc, ds, per_warp, &smem);
+        if (warps == 0) return false;
+        Coupling<T> cp{};
+        void* scratch = nullptr;
+        if (!build_coupling(call, p, cp, &scratch, TP, ds)) return false;
+        int64_t* offsets = static_cast<int64_t*>(scratch_alloc(call, (p.nW0 + 1) * sizeof(int64_t)));
+        const int64_t pre_blocks = std::min<int64_t>(ceil_div(p.E + 1, 256), grid_generic * 4);
+        segment_offsets<<<static_cast<unsigned>(pre_blocks), 256, 0, call.stream>>>(
+            p.Io, p.E, p.nW0, offsets, call.status);
+        allow_smem(sasaw_fwd_mma<TP, NAP, true>, smem);
+        sasaw_fwd_mma<TP, NAP, true><<<static_cast<unsigned>(ceil_div(p.nW0, warps)), warps * 32,
+                                       smem, call.stream>>>(
+            O, p.A, p.B, p.W, p.Jw, p.Io, offsets, cp, p.E, p.nA, p.L, p.nW0, p.nW1, p.nO1, false,
+            call.status);
+        MOPS_CUDA_OK(cudaGetLastError());
+        scratch_free(call, offsets);
+        bool need_fallback = true; // asynchronous calls cannot look: always enqueue
+        if (call.wait) {
+            wait_stream(call);
+            need_fallback = host_saw_unsorted(call);
+        }
+        if (need_fallback) {
+            zero_if_unsorted<T><<<grid_generic, 256, 0, call.stream>>>(O, p.nW0 * rowsize,
+                                                                       call.status);
+            allow_smem(sasaw_fwd_mma<TP, NAP, false>, smem);
+            const int64_t blocks = std::min<int64_t>(ceil_div(p.E, warps), grid_generic);
+            sasaw_fwd_mma<TP, NAP, false><<<static_cast<unsigned>(blocks), warps * 32, smem,
+                                            call.stream>>>(O, p.A, p.B, p.W, p.Jw, p.Io, nullptr,
+                                                           cp, p.E, p.nA, p.L, p.nW0, p.nW1, p.nO1,
+                                                           false, call.status);
+        }
+        MOPS_CUDA_OK(cudaGetLastError());
+        scratch_free(call, scratch);
+        return true;
+    }
+}
+
 // Dispatch on the two padded widths; returns false when the fast kernels do not apply.
 #define MOPS_B200_SASAW_FAST(FN, ...)                                                              \
     [&]() -> bool {                                                                                \
@@ -854,6 +1114,7 @@ template <typename T> void forward(const Call& call, T* O, const Problem<T>& p) 
         MOPS_CUDA_OK(cudaMemsetAsync(O, 0, p.nW0 * rowsize * sizeof(T), call.stream));
         return;
     }
+    if (MOPS_B200_SASAW_FAST(forward_mma, call, O, p)) return;
     if (MOPS_B200_SASAW_FAST(forward_fast, call, O, p)) return;
     const int grid_generic = sm_count(call.device) * 8;
     Coupling<T> cp{};
