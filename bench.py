@@ -54,8 +54,9 @@ CASES = {
 }
 BATCH_KEYS = {"hpe": ("I",), "sap": ("I",), "opsa": ("J", "nO"), "opsaw": ("E", "n"),
               "sasaw": ("E", "n")}
-# kernels of this library launched by one forward / one VJP call (sorted input, waiting calls)
-LAUNCHES = {"hpe": (1, 1), "sap": (1, 1), "opsa": (1, 1), "opsaw": (1, 1), "sasaw": (2, 2)}
+# kernels of this library launched by one forward / one VJP call (sorted input, waiting calls):
+# plan or segment-offset kernel + the row/entry kernel (SASAW forward: both + the row kernel)
+LAUNCHES = {"hpe": (2, 2), "sap": (2, 2), "opsa": (2, 1), "opsaw": (2, 1), "sasaw": (3, 2)}
 # DRAM traffic per launch of the main kernel measured with ncu (bytes read + written), by
 # case and level; None until a capture exists. See profiles/.
 MEASURED_TRAFFIC = {}
