@@ -57,9 +57,24 @@ BATCH_KEYS = {"hpe": ("I",), "sap": ("I",), "opsa": ("J", "nO"), "opsaw": ("E", 
 # kernels of this library launched by one forward / one VJP call (sorted input, waiting calls):
 # plan or segment-offset kernel + the row/entry kernel (SASAW forward: both + the row kernel)
 LAUNCHES = {"hpe": (2, 2), "sap": (2, 2), "opsa": (2, 1), "opsaw": (2, 1), "sasaw": (3, 2)}
-# DRAM traffic per launch of the main kernel measured with ncu (bytes read + written), by
-# case and level; None until a capture exists. See profiles/.
-MEASURED_TRAFFIC = {}
+# DRAM traffic per launch of the main kernel (dram__bytes_read.sum + dram__bytes_write.sum of
+# one ncu capture), by case and level. Captured with every batch dimension divided by 8 (the
+# full-size step is too large for a multi-pass capture) and multiplied by 8 here: all
+# operands and results of these kernels scale with the batch. The summaries under profiles/
+# hold the captured figures.
+MEASURED_TRAFFIC = {
+    ("hpe", "fwd"): 8 * 108.4e6, ("hpe", "vjp"): 8 * 181.0e6,
+    ("sap", "fwd"): 8 * 346.0e6, ("sap", "vjp"): 8 * 405.0e6,
+    ("opsa", "fwd"): 8 * 614.4e6, ("opsa", "vjp"): 8 * 1138.0e6,
+    ("opsa_f32", "fwd"): 8 * 304.6e6, ("opsa_f32", "vjp"): 8 * 554.9e6,
+    ("opsaw", "fwd"): 8 * 211.3e6, ("opsaw", "vjp"): 8 * 376.8e6,
+    ("sasaw", "fwd"): 8 * 207.4e6, ("sasaw", "vjp"): 8 * 403.2e6,
+}
+
+
+def traffic(name, level):
+    t = MEASURED_TRAFFIC.get((name, level))
+    return None if t is None else t / SCALE
 
 
 def selected_cases(which):
@@ -410,14 +425,16 @@ def main():
         per_op[n] = {"fwd_ms": f_ms, "vjp_ms": v_ms, "fwd_GBps": bf / f_ms / 1e6,
                      "vjp_GBps": bv / v_ms / 1e6, "fwd_frac_of_hbm": bf / f_ms / 1e6 / peak,
                      "vjp_frac_of_hbm": bv / v_ms / 1e6 / peak,
-                     "fwd_items_per_s": items / f_ms * 1e3, "vjp_items_per_s": items / v_ms * 1e3}
+                     "fwd_items_per_s": items / f_ms * 1e3, "vjp_items_per_s": items / v_ms * 1e3,
+                     "fwd_bytes": bf, "vjp_bytes": bv,
+                     "fwd_traffic": traffic(n, "fwd"), "vjp_traffic": traffic(n, "vjp")}
         for lvl, ms, b in (("fwd", f_ms, bf), ("vjp", v_ms, bv)):
             if dominant is None or ms > dominant[2]:
                 dominant = (n, lvl, ms, b)
     dn, dl, dms, db = dominant
     roofline = {"bound": "hbm", "kernel": f"{dn} {dl}", "achieved": db / dms / 1e6, "peak": peak,
                 "peak_source": peak_src, "unit": "GB/s", "frac": db / dms / 1e6 / peak,
-                "traffic": MEASURED_TRAFFIC.get((dn, dl))}
+                "traffic": traffic(dn, dl)}
     launches = sum(sum(LAUNCHES[CASES[n][0]]) for n in names) * args.steps
     line = {"metric": "algorithmic_GBps_fwd_plus_vjp", "value": value, "unit": "GB/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
