@@ -52,8 +52,11 @@ template <typename T> struct Coupling {
     int N, ncell;
     // Optional dense form for the fast kernels: D[cc][m1] = sum of C[n] over the entries of
     // compact cell cc = m3 * nW1 + m2 with M1[n] = m1; rows of d_stride scalars.
+    // With d_padded the rows are numbered like the cells (m3 * cell_stride + m2) and the rows
+    // of padding cells are zero.
     T* D;
     int d_stride;
+    bool d_padded;
 };
 
 constexpr int kBuildThreads = 256;
@@ -138,8 +141,8 @@ sasaw_group_coupling(Coupling<T> cp, const T* __restrict__ C, const int32_t* __r
         // one thread per cell, entries in ascending n: reproducible sums
         for (int c = tid; c < ncell; c += kBuildThreads) {
             const int m3 = c / cell_stride, m2 = c - m3 * cell_stride;
-            if (m2 >= nW1) continue;
-            T* row = cp.D + static_cast<size_t>(m3 * nW1 + m2) * cp.d_stride;
+            if (m2 >= nW1 && !cp.d_padded) continue;
+            T* row = cp.D + static_cast<size_t>(cp.d_padded ? c : m3 * nW1 + m2) * cp.d_stride;
             for (int m = 0; m < cp.d_stride; m++) row[m] = T(0);
             for (int pos = cp.start[c]; pos < cp.start[c + 1]; pos++) row[cp.M1[pos]] += cp.C[pos];
         }
@@ -809,6 +812,401 @@ sasaw_fwd_mma(double* __restrict__ O, const double* __restrict__ A, const double
     }
 }
 
+// VJP, f64 only, A.shape[1], W.shape[1] and output_size all <= 16. The shuffle reductions of
+// the kernel above made it issue-bound (about 2600 warp instructions per edge). Here every
+// contraction runs on the FP64 tensor-core path and a warp works on eight consecutive edges at
+// a time:
+//   phase A  T[cell, e] = sum_m D[cell, m] A[e, m] for the eight edges at once (edges are the
+//            n dimension of the MMA), written to one shared-memory slot per edge;
+//   phase B  per edge: X^T[b, m2] = sum_m3 gO[I_e, m3, b] T_e[m3, m2]  -> grad_B, grad_W,
+//            U_e[m3, m2] = sum_b gO[I_e, m3, b] (B[e, b] W[J_e, m2, b]) -> the edge's slot;
+//   phase C  grad_A[e, m] = sum_cell U[e, cell] D[cell, m] for the eight edges at once.
+// The gO fragments stay in registers while consecutive edges share the output row (always, for
+// a sorted scatter index); W rows and B arrive by cp.async one edge ahead. Cells are numbered
+// m3 * TS + m2 (padding cells have zero rows in D), so T_e and U_e share one layout.
+
+template <int TP> struct VjpMma {
+    static constexpr int TS = a_stride(TP);  // row stride of T_e / U_e
+    static constexpr int WS = 36;            // row stride of a staged W[J_e] chunk
+    static constexpr int NT2 = TP > 8 ? 2 : 1;  // 8-wide tiles over m2
+    __host__ __device__ static int ncell(int nO1) { return nO1 * TS; }
+    // Distance between the slots of consecutive edges: 4 modulo 8, so that the eight slots read
+    // or written by one fragment access fall on distinct banks. Cells are written in whole
+    // tiles of eight; the last of the four spare scalars is never written and serves as the
+    // zero that out-of-range fragment elements read.
+    __host__ __device__ static int slot(int nO1) { return (ncell(nO1) + 7) / 8 * 8 + 4; }
+    // One stage: rows 0..nW1-1 a 32-wide chunk of W[J_e], row nW1 the chunk of B[e], row
+    // nW1+1 zeros.
+    __host__ __device__ static int stage(int nW1) { return (nW1 + 2) * WS; }
+    __host__ __device__ static size_t per_warp(int nO1, int nW1) {
+        return 8 * static_cast<size_t>(slot(nO1)) + 2 * static_cast<size_t>(stage(nW1));
+    }
+    // row stride of D: A.shape[1] rounded up to 4 or 12 modulo 16
+    __host__ __device__ static int d_stride(int nA) { return a_stride((nA + 3) / 4 * 4); }
+    __host__ __device__ static size_t d_scalars(int nO1, int nA) {
+        return static_cast<size_t>((ncell(nO1) + 7) / 8 * 8) * d_stride(nA);
+    }
+};
+
+// c = a b (no accumulator input)
+__device__ __forceinline__ void dmma0(double (&c)[2], double a, double b) {
+    asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%4,%4};\n"
+                 : "=d"(c[0]), "=d"(c[1])
+                 : "d"(a), "d"(b), "d"(0.0));
+}
+
+// KS3 = number of four-row k-steps that cover output_size.
+// Predicated forms (one instruction each, no branch around them).
+template <int BYTE_OFFSET>
+__device__ __forceinline__ void red_add_if(bool p, double* addr, double v) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %2, 0;\n @p red.global.add.f64 [%0 + %3], %1;\n}\n"
+                 :: "l"(addr), "d"(v), "r"(static_cast<int>(p)), "n"(BYTE_OFFSET)
+                 : "memory");
+}
+template <int BYTE_OFFSET> __device__ __forceinline__ void red_add_at(double* addr, double v) {
+    asm volatile("red.global.add.f64 [%0 + %2], %1;\n" ::"l"(addr), "d"(v), "n"(BYTE_OFFSET) : "memory");
+}
+// Copies 16 bytes if p; src_bytes = 0 writes zeros instead of reading.
+__device__ __forceinline__ void cp_async16_if(bool p, void* smem_dst, const void* global_src,
+                                              int src_bytes) {
+    const unsigned dst = static_cast<unsigned>(__cvta_generic_to_shared(smem_dst));
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %3, 0;\n"
+                 " @p cp.async.ca.shared.global [%0], [%1], 16, %2;\n}\n"
+                 :: "r"(dst), "l"(global_src), "r"(src_bytes), "r"(static_cast<int>(p))
+                 : "memory");
+}
+
+template <int TP, int KS3>
+__global__ void __launch_bounds__(128, 3)
+sasaw_vjp_mma(double* __restrict__ gA, double* __restrict__ gB, double* __restrict__ gW,
+              const double* __restrict__ gO, const double* __restrict__ A,
+              const double* __restrict__ B, const double* __restrict__ W,
+              const int32_t* __restrict__ Jw, const int32_t* __restrict__ Io,
+              Coupling<double> cp, int64_t E, int nA, int L, int64_t nW0, int nW1, int nO1,
+              bool wide_copies, Status st) {
+    using T = double;
+    using Lay = VjpMma<TP>;
+    constexpr int TS = Lay::TS, WS = Lay::WS, NT2 = Lay::NT2;
+    constexpr int MT3 = KS3 > 2 ? 2 : 1; // 8-high tiles over m3
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    // the shuffle tells the compiler that the warp number is the same in all lanes, so that
+    // everything derived from it (edge ranges, loop counts) stays in uniform control flow
+    const int warps = blockDim.x >> 5, lane = threadIdx.x & 31;
+    const int warp = __shfl_sync(kFullMask, threadIdx.x >> 5, 0);
+    const int qr = lane >> 2, qc = lane & 3;
+    const int ncell = Lay::ncell(nO1), nct = (ncell + 7) / 8, ES = Lay::slot(nO1);
+    const int stage = Lay::stage(nW1), DS = cp.d_stride;
+    T* D_s = reinterpret_cast<T*>(smem_raw); // [8 * nct][DS], rows >= ncell zero
+    const int d_scalars = static_cast<int>(Lay::d_scalars(nO1, nA));
+    const size_t per_warp = Lay::per_warp(nO1, nW1);
+    T* slots = D_s + d_scalars + per_warp * warp; // [8][ES]
+    T* stages = slots + 8 * ES;                   // [2][nW1 + 2][WS]
+    for (int i = threadIdx.x; i < d_scalars; i += blockDim.x)
+        D_s[i] = i < ncell * DS ? cp.D[i] : T(0);
+    for (int i = lane; i < static_cast<int>(per_warp); i += 32) slots[i] = T(0);
+    __syncthreads();
+
+    const bool want_a = gA != nullptr, want_bw = gB != nullptr || gW != nullptr;
+    const int64_t rowsize = static_cast<int64_t>(nO1) * L;
+    const int nchunks = (L + 31) / 32;
+    const int ksa = (nA + 3) / 4;    // k-steps over m1
+    const int nta = nA > 8 ? 2 : 1;  // 8-wide tiles over m1
+
+    // Per-lane offsets of the fragment elements, fixed for the whole kernel; elements outside
+    // the operands point at a zero.
+    int t_off[KS3][NT2]; // T_e[m3 = 4 ks + qc][m2 = 8 nt + qr] in a slot
+#pragma unroll
+    for (int ks = 0; ks < KS3; ks++)
+#pragma unroll
+        for (int nt = 0; nt < NT2; nt++) {
+            const int m3 = 4 * ks + qc, m2 = 8 * nt + qr;
+            t_off[ks][nt] = (m3 < nO1 && m2 < nW1) ? m3 * TS + m2 : ES - 1;
+        }
+    int wk_off[NT2]; // W chunk [m2 = 8 nt + qr][qc + 4 kb]
+#pragma unroll
+    for (int nt = 0; nt < NT2; nt++)
+        wk_off[nt] = (8 * nt + qr < nW1 ? 8 * nt + qr : nW1 + 1) * WS + qc;
+    int wc_off[NT2][2]; // W chunk [m2 = 8 nt + 2 qc + h][qr + 8 mt]
+#pragma unroll
+    for (int nt = 0; nt < NT2; nt++)
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int m2 = 8 * nt + 2 * qc + h;
+            wc_off[nt][h] = (m2 < nW1 ? m2 : nW1 + 1) * WS + qr;
+        }
+
+    // this warp's contiguous range of eight-edge batches
+    const int64_t nwarps = static_cast<int64_t>(gridDim.x) * warps;
+    const int64_t gwarp = static_cast<int64_t>(blockIdx.x) * warps + warp;
+    const int64_t nbatch = (E + 7) / 8;
+    const int64_t e_begin = nbatch * gwarp / nwarps * 8;
+    const int64_t e_end = min(nbatch * (gwarp + 1) / nwarps * 8, E);
+    if (e_begin >= e_end) return;
+
+    // Indices of the batch's edges (lane & 7 holds edge number lane & 7).
+    auto load_meta = [&](int64_t eb, int32_t& jv, int32_t& rv) {
+        const int64_t e = eb + (lane & 7);
+        jv = 0, rv = 0;
+        if (e < E) {
+            jv = __ldg(Jw + e);
+            rv = __ldg(Io + e);
+            if (clamp_index(jv, static_cast<int32_t>(nW0)) && lane < 8) report_bad_index(st, kBitJ);
+            if (clamp_index(rv, static_cast<int32_t>(nW0)) && lane < 8) report_bad_index(st, kBitI);
+        }
+    };
+    // A fragments of phase A: edge qr of the batch, component 4 ks + qc.
+    auto load_a = [&](int64_t eb, T (&af)[4]) {
+        const int64_t ea = eb + qr;
+#pragma unroll
+        for (int ks = 0; ks < 4; ks++) {
+            const int m = 4 * ks + qc;
+            af[ks] = (ea < E && m < nA) ? __ldg(A + ea * nA + m) : T(0);
+        }
+    };
+    // Asynchronous copies of W[j, :, b0..b0+31] and B[e, b0..b0+31] into stage s. With
+    // wide_copies (L even, 16-byte aligned operands) a lane moves two scalars per copy and the
+    // B chunk rides along as row nW1.
+    auto issue = [&](int s, int64_t e, int32_t j, int b0) {
+        T* w_s = stages + s * stage;
+        const T* wsrc = W + static_cast<int64_t>(j) * nW1 * L + b0;
+        const T* bsrc = B + e * L + b0;
+        if (wide_copies) {
+            const int col = 2 * (lane & 15);
+            const int bytes = b0 + col < L ? 16 : 0; // 0: zero fill
+            const int scol = bytes != 0 ? col : 0;   // keeps the unused source address valid
+            int r = lane >> 4;
+            const T* src = wsrc + r * L + scol;
+            T* dst = w_s + r * WS + col;
+#pragma unroll
+            for (int it = 0; it < TP / 2; it++, r += 2, src += 2 * L, dst += 2 * WS)
+                if (2 * it < nW1) cp_async16_if(r < nW1, dst, src, bytes);
+            cp_async16_if(lane < 16, w_s + nW1 * WS + col, bsrc + scol, bytes);
+        } else {
+            const bool inside = b0 + lane < L;
+            for (int r = 0; r <= nW1; r++) {
+                T* dst = w_s + r * WS + lane;
+                if (inside)
+                    cp_async<8>(dst, (r < nW1 ? wsrc + r * L : bsrc) + lane);
+                else
+                    dst[0] = T(0);
+            }
+        }
+        cp_async_commit();
+    };
+
+    // gO fragments of one (row, chunk): gt[mt][ks] = gO[row, 4 ks + qc, b0 + 8 mt + qr] (the A
+    // operand of X^T), gu[mt][kb] = gO[row, 8 mt + qr, b0 + 4 kb + qc] (the A operand of U).
+    T gt[4][KS3], gu[MT3][8];
+    auto load_g = [&](int32_t row, int b0) {
+        const T* g = gO + static_cast<int64_t>(row) * rowsize;
+#pragma unroll
+        for (int mt = 0; mt < 4; mt++)
+#pragma unroll
+            for (int ks = 0; ks < KS3; ks++) {
+                const int m3 = 4 * ks + qc, b = b0 + 8 * mt + qr;
+                gt[mt][ks] = (want_bw && m3 < nO1 && b < L) ? __ldg(g + m3 * L + b) : T(0);
+            }
+#pragma unroll
+        for (int mt = 0; mt < MT3; mt++)
+#pragma unroll
+            for (int kb = 0; kb < 8; kb++) {
+                const int m3 = 8 * mt + qr, b = b0 + 4 * kb + qc;
+                gu[mt][kb] = (want_a && m3 < nO1 && b < L) ? __ldg(g + m3 * L + b) : T(0);
+            }
+    };
+
+    int32_t jv, rv, jv_n = 0, rv_n = 0;
+    load_meta(e_begin, jv, rv);
+    issue(0, e_begin, __shfl_sync(kFullMask, jv, 0), 0);
+    int s = 0;
+    int32_t cached_row = -1;
+
+    for (int64_t eb = e_begin; eb < e_end; eb += 8) {
+        const int nvalid = static_cast<int>(min(static_cast<int64_t>(8), e_end - eb));
+        const bool more = eb + 8 < e_end;
+        if (more) load_meta(eb + 8, jv_n, rv_n);
+
+        // ---- phase A: T for the eight edges
+        if (want_bw) {
+            T af[4];
+            load_a(eb, af);
+            const T* drow = D_s + qr * DS + qc;
+            T* dst = slots + (2 * qc) * ES + qr;
+            for (int t = 0; t < nct; t++, drow += 8 * DS, dst += 8) {
+                T c[2];
+                dmma0(c, drow[0], af[0]);
+#pragma unroll
+                for (int ks = 1; ks < 4; ks++)
+                    if (ks < ksa) dmma(c, drow[4 * ks], af[ks]);
+                dst[0] = c[0]; // cells >= ncell of the last tile get zeros
+                dst[ES] = c[1];
+            }
+        }
+        __syncwarp();
+
+        // ---- phase B: edge by edge
+        for (int i = 0; i < nvalid; i++) {
+            const int64_t e = eb + i;
+            const int32_t j = __shfl_sync(kFullMask, jv, i);
+            const int32_t row = __shfl_sync(kFullMask, rv, i);
+            T* slot = slots + i * ES;
+            T u[MT3][NT2][2];
+
+            for (int c = 0; c < nchunks; c++) {
+                const int b0 = 32 * c;
+                // the copies of the next (edge, chunk) go out before this one is used
+                bool has_next = true;
+                if (c + 1 < nchunks)
+                    issue(s ^ 1, e, j, b0 + 32);
+                else if (i + 1 < nvalid)
+                    issue(s ^ 1, e + 1, __shfl_sync(kFullMask, jv, i + 1), 0);
+                else if (more)
+                    issue(s ^ 1, eb + 8, __shfl_sync(kFullMask, jv_n, 0), 0);
+                else
+                    has_next = false;
+                if (has_next)
+                    cp_async_wait<1>();
+                else
+                    cp_async_wait<0>();
+                __syncwarp();
+                if (nchunks > 1 || row != cached_row) {
+                    load_g(row, b0);
+                    cached_row = row;
+                }
+                const T* w_s = stages + s * stage;
+                const T* b_s = w_s + nW1 * WS;
+
+                if (want_bw) {
+                    // X^T[b = 8 mt + qr][m2 = 8 nt + 2 qc + {0,1}]
+                    T x[4][NT2][2];
+#pragma unroll
+                    for (int ks = 0; ks < KS3; ks++) {
+                        T bt[NT2];
+#pragma unroll
+                        for (int nt = 0; nt < NT2; nt++) bt[nt] = slot[t_off[ks][nt]];
+#pragma unroll
+                        for (int mt = 0; mt < 4; mt++)
+#pragma unroll
+                            for (int nt = 0; nt < NT2; nt++) {
+                                if (ks == 0)
+                                    dmma0(x[mt][nt], gt[mt][ks], bt[nt]);
+                                else
+                                    dmma(x[mt][nt], gt[mt][ks], bt[nt]);
+                            }
+                    }
+                    T part[4] = {T(0), T(0), T(0), T(0)};
+                    T bv[4];
+#pragma unroll
+                    for (int mt = 0; mt < 4; mt++) bv[mt] = b_s[8 * mt + qr];
+                    const int width = L - b0; // columns of this chunk
+                    T* gw = gW != nullptr
+                                ? gW + static_cast<int64_t>(j) * nW1 * L + b0 + 2 * qc * L + qr
+                                : nullptr;
+#pragma unroll
+                    for (int nt = 0; nt < NT2; nt++)
+#pragma unroll
+                        for (int h = 0; h < 2; h++) {
+                            if (8 * nt + h >= nW1) continue; // no lane has a valid m2
+                            const T* wcol = w_s + wc_off[nt][h];
+#pragma unroll
+                            for (int mt = 0; mt < 4; mt++) part[mt] += x[mt][nt][h] * wcol[8 * mt];
+                            if (gw == nullptr) continue;
+                            T* gdst = gw + (8 * nt + h) * L;
+                            if (8 * nt + 8 <= nW1 && width >= 32) { // every lane has an element
+                                red_add_at<0>(gdst, x[0][nt][h] * bv[0]);
+                                red_add_at<64>(gdst, x[1][nt][h] * bv[1]);
+                                red_add_at<128>(gdst, x[2][nt][h] * bv[2]);
+                                red_add_at<192>(gdst, x[3][nt][h] * bv[3]);
+                            } else {
+                                const bool ok = 8 * nt + 2 * qc + h < nW1;
+                                red_add_if<0>(ok && qr < width, gdst, x[0][nt][h] * bv[0]);
+                                red_add_if<64>(ok && 8 + qr < width, gdst, x[1][nt][h] * bv[1]);
+                                red_add_if<128>(ok && 16 + qr < width, gdst, x[2][nt][h] * bv[2]);
+                                red_add_if<192>(ok && 24 + qr < width, gdst, x[3][nt][h] * bv[3]);
+                            }
+                        }
+                    if (gB != nullptr) {
+                        // sum over the four lanes of a quad; lane (qr, qc) ends with b = 8 qc + qr
+                        const bool up2 = (qc & 2) != 0, up1 = (qc & 1) != 0;
+                        const T r0 = (up2 ? part[2] : part[0]) +
+                                     __shfl_xor_sync(kFullMask, up2 ? part[0] : part[2], 2);
+                        const T r1 = (up2 ? part[3] : part[1]) +
+                                     __shfl_xor_sync(kFullMask, up2 ? part[1] : part[3], 2);
+                        const T gb = (up1 ? r1 : r0) + __shfl_xor_sync(kFullMask, up1 ? r0 : r1, 1);
+                        const int b = b0 + 8 * qc + qr;
+                        if (b < L) gB[e * L + b] = gb;
+                    }
+                }
+                if (want_a) {
+                    // U[m3 = 8 mt + qr][m2 = 8 nt + 2 qc + {0,1}] += sum_b gO[m3, b] (B[b] W[m2, b])
+#pragma unroll
+                    for (int kb = 0; kb < 8; kb++) {
+                        const T bb = b_s[4 * kb + qc];
+                        T bw[NT2];
+#pragma unroll
+                        for (int nt = 0; nt < NT2; nt++) bw[nt] = w_s[wk_off[nt] + 4 * kb] * bb;
+#pragma unroll
+                        for (int nt = 0; nt < NT2; nt++) {
+#pragma unroll
+                            for (int mt = 0; mt < MT3; mt++) {
+                                if (kb == 0 && c == 0)
+                                    dmma0(u[mt][nt], gu[mt][kb], bw[nt]);
+                                else
+                                    dmma(u[mt][nt], gu[mt][kb], bw[nt]);
+                            }
+                        }
+                    }
+                }
+                __syncwarp(); // stage s is overwritten by the copies issued next round
+                s ^= 1;
+            }
+            if (want_a) {
+                // T_e is no longer needed: the slot now holds U_e (padding cells stay zero)
+#pragma unroll
+                for (int mt = 0; mt < MT3; mt++)
+#pragma unroll
+                    for (int nt = 0; nt < NT2; nt++) {
+                        const int m3 = 8 * mt + qr, m2 = 8 * nt + 2 * qc;
+                        T* dst = slot + m3 * TS + m2;
+                        if (8 * mt + 8 <= nO1 && 8 * nt + 8 <= nW1) { // whole tile inside
+                            *reinterpret_cast<double2*>(dst) = make_double2(u[mt][nt][0], u[mt][nt][1]);
+                        } else {
+                            if (m3 < nO1 && m2 < nW1) dst[0] = u[mt][nt][0];
+                            if (m3 < nO1 && m2 + 1 < nW1) dst[1] = u[mt][nt][1];
+                        }
+                    }
+            }
+        }
+
+        // ---- phase C: grad_A for the eight edges
+        if (want_a) {
+            __syncwarp();
+            T ga[2][2] = {{T(0), T(0)}, {T(0), T(0)}};
+            const T* urow = slots + qr * ES + qc;
+            const T* dcol = D_s + qc * DS + qr;
+#pragma unroll 3
+            for (int kc = 0; kc < ncell / 4; kc++, dcol += 4 * DS) {
+                const T au = urow[4 * kc];
+                dmma(ga[0], au, dcol[0]);
+                if (nta > 1) dmma(ga[1], au, dcol[8]);
+            }
+            const int64_t ea = eb + qr;
+            if (ea < e_end) {
+#pragma unroll
+                for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+                    for (int h = 0; h < 2; h++) {
+                        const int m = 8 * nt + 2 * qc + h;
+                        if (m < nA) gA[ea * nA + m] = ga[nt][h];
+                    }
+            }
+        }
+        __syncwarp(); // the slots are rewritten by the next batch's phase A
+        jv = jv_n;
+        rv = rv_n;
+    }
+}
+
 // Any sizes, no shared memory: one thread per (edge, b) walking the whole coupling table.
 // Needs zero-filled O (forward) / gA, gW (VJP).
 template <typename T>
@@ -894,7 +1292,7 @@ template <typename T> struct Problem {
 // cannot be used (cell grid too large for one block's shared memory).
 template <typename T>
 bool build_coupling(const Call& call, const Problem<T>& p, Coupling<T>& cp, void** scratch,
-                    int cell_stride = 0, int d_stride = 0) {
+                    int cell_stride = 0, int d_stride = 0, bool d_padded = false) {
     if (cell_stride == 0) cell_stride = p.nW1;
     const int64_t ncell64 = static_cast<int64_t>(p.nO1) * cell_stride;
     if (ncell64 > 8192 || ncell64 == 0) return false;
@@ -903,11 +1301,13 @@ bool build_coupling(const Call& call, const Problem<T>& p, Coupling<T>& cp, void
     const size_t nT = (static_cast<size_t>(p.N) * sizeof(T) + 15) / 16 * 16;
     const size_t nI = static_cast<size_t>(p.N) * sizeof(int32_t);
     const size_t nStart = ((cp.ncell + 1) * sizeof(int32_t) + 15) / 16 * 16;
-    const size_t nD = static_cast<size_t>(d_stride) * p.nO1 * p.nW1 * sizeof(T);
+    const size_t nD =
+        static_cast<size_t>(d_stride) * p.nO1 * (d_padded ? cell_stride : p.nW1) * sizeof(T);
     const size_t bytes = nT + 3 * nI + nStart + 16 + nD;
     unsigned char* base = static_cast<unsigned char*>(scratch_alloc(call, bytes));
     *scratch = base;
     cp.d_stride = d_stride;
+    cp.d_padded = d_padded;
     cp.D = d_stride > 0
                ? reinterpret_cast<T*>(base + (nT + 3 * nI + nStart + 15) / 16 * 16)
                : nullptr;
@@ -1082,6 +1482,50 @@ bool forward_mma(const Call& call, T* O, const Problem<T>& p) {
     }
 }
 
+template <typename T, int TP, int KS3>
+bool backward_mma_launch(const Call& call, T* gA, T* gB, T* gW, const T* gO, const Problem<T>& p) {
+    using Lay = VjpMma<TP>;
+    const int warps = 4;
+    const size_t smem =
+        (Lay::d_scalars(p.nO1, p.nA) + Lay::per_warp(p.nO1, p.nW1) * warps) * sizeof(T);
+    if (smem > 74 * 1024) return false; // three blocks per SM
+    Coupling<T> cp{};
+    void* scratch = nullptr;
+    if (!build_coupling(call, p, cp, &scratch, Lay::TS, Lay::d_stride(p.nA), true)) return false;
+    allow_smem(sasaw_vjp_mma<TP, KS3>, smem);
+    const bool wide_copies = p.L % 2 == 0 && reinterpret_cast<uintptr_t>(p.W) % 16 == 0 &&
+                             reinterpret_cast<uintptr_t>(p.B) % 16 == 0;
+    const int64_t blocks = std::min<int64_t>(ceil_div(ceil_div(p.E, 8), warps),
+                                             static_cast<int64_t>(sm_count(call.device)) * 3);
+    sasaw_vjp_mma<TP, KS3><<<static_cast<unsigned>(blocks), warps * 32, smem, call.stream>>>(
+        gA, gB, gW, gO, p.A, p.B, p.W, p.Jw, p.Io, cp, p.E, p.nA, p.L, p.nW0, p.nW1, p.nO1,
+        wide_copies, call.status);
+    MOPS_CUDA_OK(cudaGetLastError());
+    scratch_free(call, scratch);
+    return true;
+}
+
+// Tensor-core VJP: f64, A.shape[1], W.shape[1] and output_size all between 1 and 16.
+template <typename T>
+bool backward_mma(const Call& call, T* gA, T* gB, T* gW, const T* gO, const Problem<T>& p) {
+    if constexpr (!std::is_same<T, double>::value) {
+        return false;
+    } else {
+        const int tp = fast_width(p.nW1), op = fast_width(p.nO1);
+        if (tp == 0 || op == 0 || fast_width(p.nA) == 0) return false;
+        switch (tp * 100 + op) {
+#define MOPS_B200_CASE(TP_, OP_)                                                                   \
+    case TP_ * 100 + OP_: return backward_mma_launch<T, TP_, OP_ / 4>(call, gA, gB, gW, gO, p);
+            MOPS_B200_CASE(4, 4) MOPS_B200_CASE(4, 8) MOPS_B200_CASE(4, 12) MOPS_B200_CASE(4, 16)
+            MOPS_B200_CASE(8, 4) MOPS_B200_CASE(8, 8) MOPS_B200_CASE(8, 12) MOPS_B200_CASE(8, 16)
+            MOPS_B200_CASE(12, 4) MOPS_B200_CASE(12, 8) MOPS_B200_CASE(12, 12) MOPS_B200_CASE(12, 16)
+            MOPS_B200_CASE(16, 4) MOPS_B200_CASE(16, 8) MOPS_B200_CASE(16, 12) MOPS_B200_CASE(16, 16)
+#undef MOPS_B200_CASE
+        default: return false;
+        }
+    }
+}
+
 // Dispatch on the two padded widths; returns false when the fast kernels do not apply.
 #define MOPS_B200_SASAW_FAST(FN, ...)                                                              \
     [&]() -> bool {                                                                                \
@@ -1165,6 +1609,7 @@ void backward(const Call& call, T* gA, T* gB, T* gW, const T* gO, const Problem<
         MOPS_CUDA_OK(cudaMemsetAsync(gW, 0, wsize * sizeof(T), call.stream));
     if (p.E == 0) return;
     const bool empty = p.N == 0 || p.L == 0 || p.nO1 == 0 || p.nW1 == 0 || p.nA == 0;
+    if (!empty && backward_mma(call, gA, gB, gW, gO, p)) return;
     if (!empty && MOPS_B200_SASAW_FAST(backward_fast, call, gA, gB, gW, gO, p)) return;
     Coupling<T> cp{};
     void* scratch = nullptr;

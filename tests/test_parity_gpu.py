@@ -146,6 +146,45 @@ def test_sasaw_shapes(oracle):
         compare("sasaw", d, np.float64, oracle, what=f"sasaw {kw}")
 
 
+@pytest.mark.parametrize("kw", [
+    dict(E=1, nA=9, L=32, n=3, N=100, nW2=9, nO2=9),
+    dict(E=7, nA=9, L=32, n=3, N=100, nW2=9, nO2=9),
+    dict(E=501, nA=16, L=32, n=11, N=900, nW2=16, nO2=16),
+    dict(E=1003, nA=5, L=40, n=17, N=70, nW2=7, nO2=12),
+    dict(E=333, nA=3, L=96, n=5, N=50, nW2=5, nO2=8),
+    dict(E=260, nA=12, L=17, n=40, N=200, nW2=12, nO2=4),
+    dict(E=90, nA=8, L=31, n=4, N=64, nW2=8, nO2=1),
+], ids=lambda kw: "-".join(f"{k}{v}" for k, v in kw.items()))
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shuffled", [False, True])
+def test_sasaw_small_channel_kernels(oracle, kw, dtype, shuffled):
+    """Shapes served by the tensor-core (f64) and register-tile (f32) SASAW kernels: ragged
+    edge counts (batches of eight edges), several 32-wide chunks of B, every padded width, and
+    edges both sorted by output row and in random order."""
+    d = workloads.sasaw(**kw)
+    if shuffled:
+        order = np.random.default_rng(7).permutation(kw["E"])
+        for k in ("A", "B", "indices_W_1", "indices_output_1"):
+            d[k] = d[k][order]
+    compare("sasaw", d, dtype, oracle, what=f"sasaw {kw} shuffled={shuffled}")
+
+
+def test_sasaw_skipped_gradients(oracle):
+    import mops_b200 as M
+    d = workloads.sasaw(E=700, n=20)
+    t = to_dev(d, np.float64)
+    want = run_checker(oracle, "sasaw", d, np.float64)
+    for need in [(True, False, False), (False, True, False), (False, False, True),
+                 (True, True, False), (False, True, True)]:
+        got = M.sparse_accumulation_scatter_add_with_weights_vjp(
+            t["grad_output"], t["A"], t["B"], t["C"], t["W"], t["indices_A"], t["indices_W_1"],
+            t["indices_W_2"], t["indices_output_1"], t["indices_output_2"], *need)
+        for g, name, n in zip(got, ("grad_A", "grad_B", "grad_W"), need):
+            assert (g is not None) == n
+            if n:
+                assert_parity(g.cpu().numpy(), want[name], f"{name} with {need}")
+
+
 def test_empty_inputs():
     import torch
     import mops_b200 as M
