@@ -619,16 +619,11 @@ __global__ void sasaw_vjp_fast(T* __restrict__ gA, T* __restrict__ gB, T* __rest
 }
 
 // ------------------------------------------------------------------- tensor-core kernels
-// Forward, f64 only, A.shape[1], W.shape[1] and output_size all <= 16. Profiling the kernel
-// above showed the dense contraction
-//     P[m3, b] = sum_m2 T_e[m3, m2] W[J_e, m2, b]          (9x9 by 9x32 at the benchmark shape)
-// and its operand reads dominating the instruction stream. It runs here on the FP64
-// tensor-core path (mma.sync m8n8k4: 256 multiply-adds per warp instruction instead of 32):
-// the W rows arrive in shared memory by cp.async one edge ahead, in a bank-conflict-free
-// layout, and the output row is accumulated in registers across the whole segment.
-// (The same was tried for the VJP's U_e = X W^T contraction; with the extra staging it was
-// slower than the shuffle reduction at the occupancy its shared memory allows, so the VJP
-// stays on the kernel above.)
+// f64 only, A.shape[1], W.shape[1] and output_size all <= 16. Profiling the kernels above
+// showed the small dense contractions per edge (9x9 by 9x32 at the benchmark shape), their
+// operand reads and, in the VJP, the shuffle reductions dominating the instruction stream.
+// The kernels below run every contraction on the FP64 tensor-core path (mma.sync m8n8k4: 256
+// multiply-adds per warp instruction instead of 32).
 // Fragment layout of m8n8k4 (lane = 4*qr + qc): A[qr][qc], B[k = qc][n = qr],
 // C[qr][2*qc + {0,1}].
 
@@ -641,177 +636,6 @@ __device__ __forceinline__ void dmma(double (&c)[2], double a, double b) {
 // Row stride for an A-operand matrix read as 8 rows x 4 columns per fragment: a multiple of
 // four that is 4 or 12 modulo 16, so that the eight rows fall on distinct banks.
 __host__ __device__ constexpr int a_stride(int cols4) { return cols4 % 8 == 4 ? cols4 : cols4 + 4; }
-constexpr int kBStride = 40; // B-operand matrix read as 4 rows x 8 columns per fragment
-
-// Per-warp shared memory of the forward kernel, in doubles.
-template <int TP, int NAP> struct FwdMmaLayout {
-    static constexpr int TS = a_stride(TP);
-    static constexpr int T = 0;                          // [16][TS]        T_e
-    static constexpr int W = 16 * TS;                    // [2][TP][kBStride] W[J_e] rows, two stages
-    static constexpr int B = W + 2 * TP * kBStride;      // [2][32]         B[e, b0..b0+31]
-    static constexpr int A = B + 2 * 32;                 // [2][NAP]        A[e, :]
-    static constexpr int total = (A + 2 * NAP + 3) / 4 * 4;
-};
-
-template <int TP, int NAP, bool SEGMENTED>
-__global__ void __launch_bounds__(256, 2)
-sasaw_fwd_mma(double* __restrict__ O, const double* __restrict__ A, const double* __restrict__ B,
-              const double* __restrict__ W, const int32_t* __restrict__ Jw,
-              const int32_t* __restrict__ Io, const int64_t* __restrict__ offsets,
-              Coupling<double> cp, int64_t E, int nA, int L, int64_t nW0, int nW1, int nO1,
-              bool always, Status st) {
-    using T = double;
-    using Lay = FwdMmaLayout<TP, NAP>;
-    constexpr int TS = Lay::TS;
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int qr = lane >> 2, qc = lane & 3;
-    const int ncc = nO1 * nW1, ds = cp.d_stride;
-    constexpr size_t per_warp = Lay::total;
-    if (SEGMENTED ? saw_unsorted(st) : (!always && !saw_unsorted(st))) return;
-    Dense<T> d = carve_dense<T>(smem_raw, ncc, ds);
-    d.tpos = reinterpret_cast<int32_t*>(d.warp_base + per_warp * warps);
-    load_dense(d, cp, ncc, ds, nW1, TS);
-    T* base = d.warp_base + per_warp * warp;
-    T* T_s = base + Lay::T; // rows >= nO1 and columns >= nW1 stay zero
-    T* w_st = base + Lay::W; // rows >= nW1 and columns >= L stay zero
-    T* b_st = base + Lay::B;
-    T* a_st = base + Lay::A; // entries >= nA stay zero
-    for (int i = lane; i < static_cast<int>(per_warp); i += 32) base[i] = T(0);
-    __syncthreads();
-    const size_t rowsize = static_cast<size_t>(nO1) * L;
-    const int mtiles = nO1 > 8 ? 2 : 1;
-
-    T acc[2][4][2];
-    auto clear = [&] {
-#pragma unroll
-        for (int mt = 0; mt < 2; mt++)
-#pragma unroll
-            for (int nt = 0; nt < 4; nt++) acc[mt][nt][0] = acc[mt][nt][1] = T(0);
-    };
-    auto read_j = [&](int64_t e) -> int32_t {
-        int32_t j = __ldg(Jw + e);
-        if (clamp_index(j, static_cast<int32_t>(nW0)) && lane == 0) report_bad_index(st, kBitJ);
-        return j;
-    };
-    // Asynchronous copies of one edge's operands into stage `s` (one commit group).
-    auto issue = [&](int s, int64_t e, int32_t j, int b0) {
-        const int b = b0 + lane;
-        if (b < L) {
-            const T* wrow = W + static_cast<int64_t>(j) * nW1 * L + b;
-            T* dst = w_st + s * TP * kBStride + lane;
-            for (int m2 = 0; m2 < nW1; m2++) cp_async<8>(dst + m2 * kBStride, wrow + m2 * L);
-            cp_async<8>(b_st + s * 32 + lane, B + e * L + b);
-        }
-        if (lane < nA) cp_async<8>(a_st + s * NAP + lane, A + e * nA + lane);
-        cp_async_commit();
-    };
-    // acc += (T_e W[J_e]) scaled per column by B[e, b]
-    auto compute = [&](int s) {
-        T a[NAP];
-#pragma unroll
-        for (int m = 0; m < NAP; m++) a[m] = a_st[s * NAP + m];
-        dense_contract_regs<T, NAP>(d, ncc, ds, a, T_s, lane);
-        const T* w_s = w_st + s * TP * kBStride;
-        T p[2][4][2];
-#pragma unroll
-        for (int mt = 0; mt < 2; mt++)
-#pragma unroll
-            for (int nt = 0; nt < 4; nt++) p[mt][nt][0] = p[mt][nt][1] = T(0);
-#pragma unroll
-        for (int ks = 0; ks < TP / 4; ks++) {
-            T af[2], bf[4];
-            af[0] = T_s[qr * TS + 4 * ks + qc];
-            af[1] = mtiles > 1 ? T_s[(8 + qr) * TS + 4 * ks + qc] : T(0);
-#pragma unroll
-            for (int nt = 0; nt < 4; nt++) bf[nt] = w_s[(4 * ks + qc) * kBStride + 8 * nt + qr];
-#pragma unroll
-            for (int nt = 0; nt < 4; nt++) {
-                dmma(p[0][nt], af[0], bf[nt]);
-                if (mtiles > 1) dmma(p[1][nt], af[1], bf[nt]);
-            }
-        }
-#pragma unroll
-        for (int nt = 0; nt < 4; nt++) {
-            const double2 bb = *reinterpret_cast<const double2*>(b_st + s * 32 + 8 * nt + 2 * qc);
-#pragma unroll
-            for (int mt = 0; mt < 2; mt++) {
-                acc[mt][nt][0] += bb.x * p[mt][nt][0];
-                acc[mt][nt][1] += bb.y * p[mt][nt][1];
-            }
-        }
-    };
-    // fragment element (mt, nt, u) is output element [m3 = 8*mt + qr][b = b0 + 8*nt + 2*qc + u]
-    auto flush = [&](int64_t out_row, int b0, bool atomic) {
-        T* dst = O + out_row * rowsize;
-#pragma unroll
-        for (int mt = 0; mt < 2; mt++) {
-            const int m3 = 8 * mt + qr;
-            if (m3 >= nO1) continue;
-#pragma unroll
-            for (int nt = 0; nt < 4; nt++) {
-#pragma unroll
-                for (int u = 0; u < 2; u++) {
-                    const int b = b0 + 8 * nt + 2 * qc + u;
-                    if (b < L) {
-                        if (atomic)
-                            red_add(dst + m3 * L + b, acc[mt][nt][u]);
-                        else
-                            dst[m3 * L + b] = acc[mt][nt][u];
-                    }
-                }
-            }
-        }
-    };
-
-    if (SEGMENTED) {
-        const int64_t r = static_cast<int64_t>(blockIdx.x) * warps + warp;
-        if (r >= nW0) return;
-        const int64_t begin = offsets[r], end = offsets[r + 1];
-        for (int b0 = 0; b0 < L; b0 += 32) {
-            clear();
-            int32_t j_next = 0;
-            __syncwarp();
-            if (begin < end) {
-                issue(0, begin, read_j(begin), b0);
-                if (begin + 1 < end) j_next = read_j(begin + 1);
-            }
-            int s = 0;
-            for (int64_t e = begin; e < end; e++, s ^= 1) {
-                if (e + 1 < end) {
-                    issue(s ^ 1, e + 1, j_next, b0);
-                    if (e + 2 < end) j_next = read_j(e + 2);
-                    cp_async_wait<1>();
-                } else {
-                    cp_async_wait<0>();
-                }
-                __syncwarp();
-                compute(s);
-                __syncwarp(); // stage s is overwritten by the copies issued next round
-            }
-            flush(r, b0, false);
-        }
-    } else {
-        const int64_t nwarps = static_cast<int64_t>(gridDim.x) * warps;
-        for (int64_t e = static_cast<int64_t>(blockIdx.x) * warps + warp; e < E; e += nwarps) {
-            int32_t row = __ldg(Io + e);
-            if (clamp_index(row, static_cast<int32_t>(nW0))) {
-                if (lane == 0) report_bad_index(st, kBitI);
-                continue;
-            }
-            for (int b0 = 0; b0 < L; b0 += 32) {
-                clear();
-                __syncwarp();
-                issue(0, e, read_j(e), b0);
-                cp_async_wait<0>();
-                __syncwarp();
-                compute(0);
-                flush(row, b0, true);
-            }
-        }
-    }
-}
-
 // VJP, f64 only, A.shape[1], W.shape[1] and output_size all <= 16. The shuffle reductions of
 // the kernel above made it issue-bound (about 2600 warp instructions per edge). Here every
 // contraction runs on the FP64 tensor-core path and a warp works on eight consecutive edges at
@@ -1207,6 +1031,245 @@ sasaw_vjp_mma(double* __restrict__ gA, double* __restrict__ gB, double* __restri
     }
 }
 
+// Forward, f64, A.shape[1], W.shape[1] and output_size all <= 16: the same eight-edge batches
+// as the VJP above. Phase A builds T_e for eight edges with one pass of MMAs; then, per edge,
+//     O[I_e, m3, b] += sum_m2 T_e[m3, m2] (B[e, b] W[J_e, m2, b])
+// accumulates straight into the output fragments, which stay in registers for the whole
+// segment of edges that share the output row (SEGMENTED, one plain store per element), or
+// are flushed with atomics after every edge (unsorted scatter index).
+template <int TP, bool SEGMENTED>
+__global__ void __launch_bounds__(128, 3)
+sasaw_fwd_mma(double* __restrict__ O, const double* __restrict__ A, const double* __restrict__ B,
+              const double* __restrict__ W, const int32_t* __restrict__ Jw,
+              const int32_t* __restrict__ Io, const int64_t* __restrict__ offsets,
+              Coupling<double> cp, int64_t E, int nA, int L, int64_t nW0, int nW1, int nO1,
+              bool wide_copies, Status st) {
+    using T = double;
+    using Lay = VjpMma<TP>;
+    constexpr int TS = Lay::TS, WS = Lay::WS, KS2 = TP / 4;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int warps = blockDim.x >> 5, lane = threadIdx.x & 31;
+    const int warp = __shfl_sync(kFullMask, threadIdx.x >> 5, 0); // uniform for the compiler
+    const int qr = lane >> 2, qc = lane & 3;
+    if (SEGMENTED ? saw_unsorted(st) : !saw_unsorted(st)) return;
+    const int ncell = Lay::ncell(nO1), nct = (ncell + 7) / 8, ES = Lay::slot(nO1);
+    const int stage = Lay::stage(nW1), DS = cp.d_stride;
+    T* D_s = reinterpret_cast<T*>(smem_raw); // [8 * nct][DS], rows >= ncell zero
+    const int d_scalars = static_cast<int>(Lay::d_scalars(nO1, nA));
+    const size_t per_warp = Lay::per_warp(nO1, nW1);
+    T* slots = D_s + d_scalars + per_warp * warp; // [8][ES]
+    T* stages = slots + 8 * ES;                   // [2][nW1 + 2][WS]
+    for (int i = threadIdx.x; i < d_scalars; i += blockDim.x)
+        D_s[i] = i < ncell * DS ? cp.D[i] : T(0);
+    for (int i = lane; i < static_cast<int>(per_warp); i += 32) slots[i] = T(0);
+    __syncthreads();
+
+    const size_t rowsize = static_cast<size_t>(nO1) * L;
+    const int ksa = (nA + 3) / 4;
+    const bool two_tiles = nO1 > 8; // 8-high tiles over m3
+
+    // Per-lane fragment offsets: T_e[m3 = 8 mt + qr][m2 = 4 ks + qc] in a slot (rows past the
+    // output read the slot's zero) and W chunk row 4 ks + qc (rows past W read the zero row).
+    int t_off[2][KS2], w_off[KS2];
+#pragma unroll
+    for (int ks = 0; ks < KS2; ks++) {
+#pragma unroll
+        for (int mt = 0; mt < 2; mt++)
+            t_off[mt][ks] = 8 * mt + qr < nO1 ? (8 * mt + qr) * TS + 4 * ks + qc : ES - 1;
+        w_off[ks] = (4 * ks + qc < nW1 ? 4 * ks + qc : nW1 + 1) * WS + qr;
+    }
+
+    auto load_meta = [&](int64_t eb, int64_t hi, int32_t& jv, int32_t& rv) {
+        const int64_t e = eb + (lane & 7);
+        jv = 0, rv = 0;
+        if (e < hi) {
+            jv = __ldg(Jw + e);
+            if (clamp_index(jv, static_cast<int32_t>(nW0)) && lane < 8) report_bad_index(st, kBitJ);
+            if (!SEGMENTED) {
+                rv = __ldg(Io + e);
+                if (clamp_index(rv, static_cast<int32_t>(nW0)) && lane < 8) {
+                    report_bad_index(st, kBitI);
+                    rv = -1; // skipped below
+                }
+            }
+        }
+    };
+    auto load_a = [&](int64_t eb, int64_t hi, T (&af)[4]) {
+        const int64_t ea = eb + qr;
+#pragma unroll
+        for (int ks = 0; ks < 4; ks++) {
+            const int m = 4 * ks + qc;
+            af[ks] = (ea < hi && m < nA) ? __ldg(A + ea * nA + m) : T(0);
+        }
+    };
+    auto issue = [&](int s, int64_t e, int32_t j, int b0) {
+        T* w_s = stages + s * stage;
+        const T* wsrc = W + static_cast<int64_t>(j) * nW1 * L + b0;
+        const T* bsrc = B + e * L + b0;
+        if (wide_copies) {
+            const int col = 2 * (lane & 15);
+            const int bytes = b0 + col < L ? 16 : 0; // 0: zero fill
+            const int scol = bytes != 0 ? col : 0;   // keeps the unused source address valid
+            int r = lane >> 4;
+            const T* src = wsrc + r * L + scol;
+            T* dst = w_s + r * WS + col;
+#pragma unroll
+            for (int it = 0; it < TP / 2; it++, r += 2, src += 2 * L, dst += 2 * WS)
+                if (2 * it < nW1) cp_async16_if(r < nW1, dst, src, bytes);
+            cp_async16_if(lane < 16, w_s + nW1 * WS + col, bsrc + scol, bytes);
+        } else {
+            const bool inside = b0 + lane < L;
+            for (int r = 0; r <= nW1; r++) {
+                T* dst = w_s + r * WS + lane;
+                if (inside)
+                    cp_async<8>(dst, (r < nW1 ? wsrc + r * L : bsrc) + lane);
+                else
+                    dst[0] = T(0);
+            }
+        }
+        cp_async_commit();
+    };
+
+    // fragment element (mt, nt, h) is output element [m3 = 8 mt + qr][b = b0 + 8 nt + 2 qc + h]
+    T acc[2][4][2];
+    auto clear = [&] {
+#pragma unroll
+        for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+            for (int nt = 0; nt < 4; nt++) acc[mt][nt][0] = acc[mt][nt][1] = T(0);
+    };
+    auto flush = [&](int64_t out_row, int b0) {
+        T* dst = O + out_row * rowsize + b0 + 2 * qc;
+        const int width = L - b0;
+#pragma unroll
+        for (int mt = 0; mt < 2; mt++) {
+            const int m3 = 8 * mt + qr;
+            if (m3 >= nO1) continue;
+#pragma unroll
+            for (int nt = 0; nt < 4; nt++) {
+                T* d2 = dst + m3 * L + 8 * nt;
+                if (SEGMENTED) {
+                    if (wide_copies && width >= 32) {
+                        *reinterpret_cast<double2*>(d2) = make_double2(acc[mt][nt][0], acc[mt][nt][1]);
+                    } else {
+                        if (8 * nt + 2 * qc < width) d2[0] = acc[mt][nt][0];
+                        if (8 * nt + 2 * qc + 1 < width) d2[1] = acc[mt][nt][1];
+                    }
+                } else {
+                    if (8 * nt + 2 * qc < width) red_add(d2, acc[mt][nt][0]);
+                    if (8 * nt + 2 * qc + 1 < width) red_add(d2 + 1, acc[mt][nt][1]);
+                }
+            }
+        }
+    };
+
+    // All edges of [lo, hi) for one 32-wide chunk of b.
+    auto run = [&](int64_t lo, int64_t hi, int64_t out_row, int b0) {
+        int32_t jv, rv, jv_n = 0, rv_n = 0;
+        T af[4], af_n[4];
+        load_meta(lo, hi, jv, rv);
+        load_a(lo, hi, af);
+        __syncwarp();
+        issue(0, lo, __shfl_sync(kFullMask, jv, 0), b0);
+        int s = 0;
+        for (int64_t eb = lo; eb < hi; eb += 8) {
+            const int nvalid = static_cast<int>(min(static_cast<int64_t>(8), hi - eb));
+            const bool more = eb + 8 < hi;
+            if (more) {
+                load_meta(eb + 8, hi, jv_n, rv_n);
+                load_a(eb + 8, hi, af_n);
+            }
+            // ---- phase A: T for the eight edges
+            {
+                const T* drow = D_s + qr * DS + qc;
+                T* dst = slots + (2 * qc) * ES + qr;
+                for (int t = 0; t < nct; t++, drow += 8 * DS, dst += 8) {
+                    T c[2];
+                    dmma0(c, drow[0], af[0]);
+#pragma unroll
+                    for (int ks = 1; ks < 4; ks++)
+                        if (ks < ksa) dmma(c, drow[4 * ks], af[ks]);
+                    dst[0] = c[0]; // cells >= ncell of the last tile get zeros
+                    dst[ES] = c[1];
+                }
+            }
+            __syncwarp();
+            // ---- phase B: edge by edge
+            for (int i = 0; i < nvalid; i++) {
+                bool has_next = true;
+                if (i + 1 < nvalid)
+                    issue(s ^ 1, eb + i + 1, __shfl_sync(kFullMask, jv, i + 1), b0);
+                else if (more)
+                    issue(s ^ 1, eb + 8, __shfl_sync(kFullMask, jv_n, 0), b0);
+                else
+                    has_next = false;
+                if (has_next)
+                    cp_async_wait<1>();
+                else
+                    cp_async_wait<0>();
+                __syncwarp();
+                const T* slot = slots + i * ES;
+                const T* w_s = stages + s * stage;
+                const T* b_s = w_s + nW1 * WS;
+                T bb[4];
+#pragma unroll
+                for (int nt = 0; nt < 4; nt++) bb[nt] = b_s[8 * nt + qr];
+#pragma unroll
+                for (int ks = 0; ks < KS2; ks++) {
+                    if (4 * ks < nW1) {
+                        const T a0 = slot[t_off[0][ks]];
+                        const T a1 = two_tiles ? slot[t_off[1][ks]] : T(0);
+                        const T* wrow = w_s + w_off[ks];
+#pragma unroll
+                        for (int nt = 0; nt < 4; nt++) {
+                            const T bw = wrow[8 * nt] * bb[nt];
+                            dmma(acc[0][nt], a0, bw);
+                            if (two_tiles) dmma(acc[1][nt], a1, bw);
+                        }
+                    }
+                }
+                if (!SEGMENTED) {
+                    const int32_t row = __shfl_sync(kFullMask, rv, i);
+                    if (row >= 0) flush(row, b0);
+                    clear();
+                }
+                __syncwarp(); // stage s is overwritten by the copies issued next round
+                s ^= 1;
+            }
+            __syncwarp(); // the slots are rewritten by the next batch's phase A
+            jv = jv_n;
+            rv = rv_n;
+#pragma unroll
+            for (int ks = 0; ks < 4; ks++) af[ks] = af_n[ks];
+        }
+        if (SEGMENTED) flush(out_row, b0);
+    };
+
+    const int64_t nwarps = static_cast<int64_t>(gridDim.x) * warps;
+    const int64_t gwarp = static_cast<int64_t>(blockIdx.x) * warps + warp;
+    if (SEGMENTED) {
+        for (int64_t r = gwarp; r < nW0; r += nwarps) {
+            const int64_t lo = offsets[r], hi = offsets[r + 1];
+            for (int b0 = 0; b0 < L; b0 += 32) {
+                clear();
+                if (lo < hi)
+                    run(lo, hi, r, b0);
+                else
+                    flush(r, b0);
+            }
+        }
+    } else {
+        const int64_t nbatch = (E + 7) / 8;
+        const int64_t lo = nbatch * gwarp / nwarps * 8;
+        const int64_t hi = min(nbatch * (gwarp + 1) / nwarps * 8, E);
+        if (lo < hi)
+            for (int b0 = 0; b0 < L; b0 += 32) {
+                clear();
+                run(lo, hi, 0, b0);
+            }
+    }
+}
+
 // Any sizes, no shared memory: one thread per (edge, b) walking the whole coupling table.
 // Needs zero-filled O (forward) / gA, gW (VJP).
 template <typename T>
@@ -1434,51 +1497,61 @@ bool backward_fast(const Call& call, T* gA, T* gB, T* gW, const T* gO, const Pro
 }
 
 // Tensor-core variants (f64, output_size <= 16 as well).
-template <typename T, int TP, int NAP>
-bool forward_mma(const Call& call, T* O, const Problem<T>& p) {
+template <typename T, int TP> bool forward_mma_launch(const Call& call, T* O, const Problem<T>& p) {
+    using Lay = VjpMma<TP>;
+    const int warps = 4;
+    const size_t smem =
+        (Lay::d_scalars(p.nO1, p.nA) + Lay::per_warp(p.nO1, p.nW1) * warps) * sizeof(T);
+    if (smem > 74 * 1024) return false; // three blocks per SM
+    const int64_t rowsize = static_cast<int64_t>(p.nO1) * p.L;
+    const int sms = sm_count(call.device);
+    Coupling<T> cp{};
+    void* scratch = nullptr;
+    if (!build_coupling(call, p, cp, &scratch, Lay::TS, Lay::d_stride(p.nA), true)) return false;
+    int64_t* offsets = static_cast<int64_t*>(scratch_alloc(call, (p.nW0 + 1) * sizeof(int64_t)));
+    const int64_t pre_blocks = std::min<int64_t>(ceil_div(p.E + 1, 256), sms * 32);
+    segment_offsets<<<static_cast<unsigned>(pre_blocks), 256, 0, call.stream>>>(
+        p.Io, p.E, p.nW0, offsets, call.status);
+    const bool wide_copies = p.L % 2 == 0 && reinterpret_cast<uintptr_t>(p.W) % 16 == 0 &&
+                             reinterpret_cast<uintptr_t>(p.B) % 16 == 0 &&
+                             reinterpret_cast<uintptr_t>(O) % 16 == 0;
+    allow_smem(sasaw_fwd_mma<TP, true>, smem);
+    const int64_t seg_blocks = std::min<int64_t>(ceil_div(p.nW0, warps), sms * 3);
+    sasaw_fwd_mma<TP, true><<<static_cast<unsigned>(seg_blocks), warps * 32, smem, call.stream>>>(
+        O, p.A, p.B, p.W, p.Jw, p.Io, offsets, cp, p.E, p.nA, p.L, p.nW0, p.nW1, p.nO1,
+        wide_copies, call.status);
+    MOPS_CUDA_OK(cudaGetLastError());
+    scratch_free(call, offsets);
+    bool need_fallback = true; // asynchronous calls cannot look: always enqueue
+    if (call.wait) {
+        wait_stream(call);
+        need_fallback = host_saw_unsorted(call);
+    }
+    if (need_fallback) {
+        zero_if_unsorted<T><<<sms * 8, 256, 0, call.stream>>>(O, p.nW0 * rowsize, call.status);
+        allow_smem(sasaw_fwd_mma<TP, false>, smem);
+        const int64_t blocks = std::min<int64_t>(ceil_div(ceil_div(p.E, 8), warps), sms * 3);
+        sasaw_fwd_mma<TP, false><<<static_cast<unsigned>(blocks), warps * 32, smem, call.stream>>>(
+            O, p.A, p.B, p.W, p.Jw, p.Io, nullptr, cp, p.E, p.nA, p.L, p.nW0, p.nW1, p.nO1,
+            wide_copies, call.status);
+    }
+    MOPS_CUDA_OK(cudaGetLastError());
+    scratch_free(call, scratch);
+    return true;
+}
+
+template <typename T> bool forward_mma(const Call& call, T* O, const Problem<T>& p) {
     if constexpr (!std::is_same<T, double>::value) {
         return false;
     } else {
-        if (p.nO1 > 16) return false;
-        const int64_t rowsize = static_cast<int64_t>(p.nO1) * p.L;
-        const int ncc = p.nO1 * p.nW1, ds = NAP + 1;
-        const int grid_generic = sm_count(call.device) * 8;
-        size_t smem = 0;
-        const size_t per_warp = FwdMmaLayout<TP, NAP>::total;
-        const int warps = pick_warps_fast<T>(call, ncc, ds, per_warp, &smem);
-        if (warps == 0) return false;
-        Coupling<T> cp{};
-        void* scratch = nullptr;
-        if (!build_coupling(call, p, cp, &scratch, TP, ds)) return false;
-        int64_t* offsets = static_cast<int64_t*>(scratch_alloc(call, (p.nW0 + 1) * sizeof(int64_t)));
-        const int64_t pre_blocks = std::min<int64_t>(ceil_div(p.E + 1, 256), grid_generic * 4);
-        segment_offsets<<<static_cast<unsigned>(pre_blocks), 256, 0, call.stream>>>(
-            p.Io, p.E, p.nW0, offsets, call.status);
-        allow_smem(sasaw_fwd_mma<TP, NAP, true>, smem);
-        sasaw_fwd_mma<TP, NAP, true><<<static_cast<unsigned>(ceil_div(p.nW0, warps)), warps * 32,
-                                       smem, call.stream>>>(
-            O, p.A, p.B, p.W, p.Jw, p.Io, offsets, cp, p.E, p.nA, p.L, p.nW0, p.nW1, p.nO1, false,
-            call.status);
-        MOPS_CUDA_OK(cudaGetLastError());
-        scratch_free(call, offsets);
-        bool need_fallback = true; // asynchronous calls cannot look: always enqueue
-        if (call.wait) {
-            wait_stream(call);
-            need_fallback = host_saw_unsorted(call);
+        if (fast_width(p.nO1) == 0 || fast_width(p.nA) == 0) return false;
+        switch (fast_width(p.nW1)) {
+        case 4: return forward_mma_launch<T, 4>(call, O, p);
+        case 8: return forward_mma_launch<T, 8>(call, O, p);
+        case 12: return forward_mma_launch<T, 12>(call, O, p);
+        case 16: return forward_mma_launch<T, 16>(call, O, p);
+        default: return false;
         }
-        if (need_fallback) {
-            zero_if_unsorted<T><<<grid_generic, 256, 0, call.stream>>>(O, p.nW0 * rowsize,
-                                                                       call.status);
-            allow_smem(sasaw_fwd_mma<TP, NAP, false>, smem);
-            const int64_t blocks = std::min<int64_t>(ceil_div(p.E, warps), grid_generic);
-            sasaw_fwd_mma<TP, NAP, false><<<static_cast<unsigned>(blocks), warps * 32, smem,
-                                            call.stream>>>(O, p.A, p.B, p.W, p.Jw, p.Io, nullptr,
-                                                           cp, p.E, p.nA, p.L, p.nW0, p.nW1, p.nO1,
-                                                           false, call.status);
-        }
-        MOPS_CUDA_OK(cudaGetLastError());
-        scratch_free(call, scratch);
-        return true;
     }
 }
 
@@ -1558,7 +1631,7 @@ template <typename T> void forward(const Call& call, T* O, const Problem<T>& p) 
         MOPS_CUDA_OK(cudaMemsetAsync(O, 0, p.nW0 * rowsize * sizeof(T), call.stream));
         return;
     }
-    if (MOPS_B200_SASAW_FAST(forward_mma, call, O, p)) return;
+    if (forward_mma(call, O, p)) return;
     if (MOPS_B200_SASAW_FAST(forward_fast, call, O, p)) return;
     const int grid_generic = sm_count(call.device) * 8;
     Coupling<T> cp{};
