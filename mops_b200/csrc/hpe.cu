@@ -37,38 +37,57 @@ constexpr int kPlanThreads = 256;
 constexpr int kFwdChunk = 256; // monomials per forward stage (whole block)
 constexpr int kVjpChunk = 64;  // incidences per VJP stage (per warp)
 
-// Offsets of one table row are padded to a power-of-two count (or 12) so that a row is read
-// with 4-, 8- or 16-byte broadcasts.
-__host__ __device__ constexpr int padded(int n) {
-    return n <= 0 ? 0 : n <= 1 ? 1 : n <= 2 ? 2 : n <= 4 ? 4 : n <= 8 ? 8 : 12;
+// One table record: a coefficient followed by NF 16-bit tile offsets (in scalars: column
+// n of the transposed tile starts at n * kPad, which fits 16 bits for every tile that fits in
+// shared memory), padded to 8, 16 or 32 bytes so that one or two broadcast loads fetch it.
+__host__ __device__ constexpr int record_bytes(int scalar_bytes, int nf) {
+    const int raw = scalar_bytes + 2 * (nf > 0 ? nf : 0);
+    return raw <= 8 ? 8 : raw <= 16 ? 16 : 32;
 }
+constexpr int kMaxTileColumns = 65535 / kPad;
 
-template <int NP> __device__ __forceinline__ void read_offsets(const int32_t* p, int (&o)[NP > 0 ? NP : 1]) {
-    if constexpr (NP == 1) {
-        o[0] = p[0];
-    } else if constexpr (NP == 2) {
-        const int2 v = *reinterpret_cast<const int2*>(p);
-        o[0] = v.x;
-        o[1] = v.y;
-    } else if constexpr (NP >= 4) {
+template <typename T, int NF>
+__device__ __forceinline__ T read_record(const unsigned char* rec, int (&o)[NF > 0 ? NF : 1]) {
+    constexpr int B = record_bytes(sizeof(T), NF);
+    unsigned w[B / 4];
+    if constexpr (B == 8) {
+        const uint2 v = *reinterpret_cast<const uint2*>(rec);
+        w[0] = v.x, w[1] = v.y;
+    } else {
 #pragma unroll
-        for (int q = 0; q < NP / 4; q++) {
-            const int4 v = *reinterpret_cast<const int4*>(p + 4 * q);
-            o[4 * q + 0] = v.x;
-            o[4 * q + 1] = v.y;
-            o[4 * q + 2] = v.z;
-            o[4 * q + 3] = v.w;
+        for (int q = 0; q < B / 16; q++) {
+            const uint4 v = *reinterpret_cast<const uint4*>(rec + 16 * q);
+            w[4 * q] = v.x, w[4 * q + 1] = v.y, w[4 * q + 2] = v.z, w[4 * q + 3] = v.w;
         }
     }
+    constexpr int first = sizeof(T) / 4; // word where the offsets start
+#pragma unroll
+    for (int k = 0; k < NF; k++) {
+        const unsigned word = w[first + k / 2];
+        o[k] = (k & 1) ? (word >> 16) : (word & 0xffffu);
+    }
+    if constexpr (sizeof(T) == 8)
+        return __hiloint2double(static_cast<int>(w[1]), static_cast<int>(w[0]));
+    else
+        return __uint_as_float(w[0]);
+}
+
+template <typename T>
+__device__ __forceinline__ void write_record(unsigned char* rec, int bytes, T coef) {
+    for (int q = 0; q < bytes / 4; q++) reinterpret_cast<unsigned*>(rec)[q] = 0u;
+    *reinterpret_cast<T*>(rec) = coef;
+}
+template <typename T>
+__device__ __forceinline__ void write_offset(unsigned char* rec, int q, int offset) {
+    reinterpret_cast<uint16_t*>(rec + sizeof(T))[q] = static_cast<uint16_t>(offset);
 }
 
 struct HpePlan {
-    int32_t* fwd_offs; // [J][padded(K)]      tile offsets of every monomial's factors
-    int32_t* vjp_offs; // [J*K][padded(K-1)]  grouped by differentiated factor
-    void* vjp_coef;    // [J*K] scalars       C[j] of each incidence
-    int32_t* n_start;  // [N + 1]             first incidence of every factor
-    int32_t* split;    // [kWarps + 1]        factor ranges of the block's warps
-    int32_t* cursor;   // [N + 1] scratch
+    unsigned char* fwd_rec; // [J]    C[j] and the tile offsets of monomial j's K factors
+    unsigned char* vjp_rec; // [J*K]  grouped by differentiated factor: C[j], the other K-1 offsets
+    int32_t* n_start;       // [N + 1]       first incidence of every factor
+    int32_t* split;         // [kWarps + 1]  factor ranges of the block's warps
+    int32_t* cursor;        // [N + 1] scratch
 };
 
 // Loads rows [i0, i0+32) of a row-major [I][N] matrix into tile[n*kPad + row].
@@ -102,25 +121,24 @@ __global__ void __launch_bounds__(kPlanThreads)
 hpe_plan(HpePlan plan, const T* __restrict__ C, const int32_t* __restrict__ P, int J, int K,
          int N, bool want_fwd, bool want_vjp, Status st) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int KP = padded(K), KQ = padded(K - 1);
+    const int fwd_bytes = record_bytes(sizeof(T), K), vjp_bytes = record_bytes(sizeof(T), K - 1);
     const int M = J * K;
     for (int x = tid; x < M; x += kPlanThreads) {
         int32_t p = P[x];
         if (clamp_index(p, N)) report_bad_index(st, 0);
     }
     if (want_fwd) {
-        for (int x = tid; x < J * KP; x += kPlanThreads) {
-            const int j = x / KP, k = x - j * KP;
-            int32_t p = 0;
-            if (k < K) {
-                p = P[j * K + k];
+        for (int j = tid; j < J; j += kPlanThreads) {
+            unsigned char* rec = plan.fwd_rec + static_cast<size_t>(j) * fwd_bytes;
+            write_record<T>(rec, fwd_bytes, C[j]);
+            for (int k = 0; k < K; k++) {
+                int32_t p = P[j * K + k];
                 clamp_index(p, N);
+                write_offset<T>(rec, k, p * kPad);
             }
-            plan.fwd_offs[x] = p * kPad;
         }
     }
     if (!want_vjp || M == 0) return;
-    T* coef = static_cast<T*>(plan.vjp_coef);
     if (warp == 0) {
         for (int b = lane; b <= N; b += 32) plan.cursor[b] = 0;
         __syncwarp();
@@ -166,15 +184,15 @@ hpe_plan(HpePlan plan, const T* __restrict__ C, const int32_t* __restrict__ P, i
             base = __shfl_sync(kFullMask, base, leader);
             if (live) {
                 const int pos = base + rank, j = x / K, k = x - j * K;
-                coef[pos] = C[j];
+                unsigned char* rec = plan.vjp_rec + static_cast<size_t>(pos) * vjp_bytes;
+                write_record<T>(rec, vjp_bytes, C[j]);
                 int q = 0;
                 for (int l = 0; l < K; l++) {
                     if (l == k) continue;
                     int32_t p = P[j * K + l];
                     clamp_index(p, N);
-                    plan.vjp_offs[pos * KQ + q++] = p * kPad;
+                    write_offset<T>(rec, q++, p * kPad);
                 }
-                for (; q < KQ; q++) plan.vjp_offs[pos * KQ + q] = 0;
             }
             __syncwarp();
         }
@@ -203,32 +221,23 @@ hpe_plan(HpePlan plan, const T* __restrict__ C, const int32_t* __restrict__ P, i
 
 template <typename T, int K>
 __global__ void __launch_bounds__(kWarps * 32)
-hpe_fwd_rows(T* __restrict__ O, const T* __restrict__ A, const T* __restrict__ C,
-             const int32_t* __restrict__ offs_table, int64_t I, int N, int J) {
-    constexpr int KP = padded(K);
+hpe_fwd_rows(T* __restrict__ O, const T* __restrict__ A, const unsigned char* __restrict__ records,
+             int64_t I, int N, int J) {
+    constexpr int RB = record_bytes(sizeof(T), K);
+    constexpr int kStageBytes = kFwdChunk * RB;
+    constexpr int unit = RB >= 16 ? 16 : 8;
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    // layout: stage 0 offsets | stage 1 offsets | stage 0 coef | stage 1 coef | A tile | partial
-    int32_t* offs_s = reinterpret_cast<int32_t*>(smem_raw);
-    constexpr int kStageInts = kFwdChunk * (KP > 0 ? KP : 1);
-    T* coef_s = reinterpret_cast<T*>(offs_s + 2 * kStageInts);
-    T* At = coef_s + 2 * kFwdChunk;
+    // layout: stage 0 records | stage 1 records | A tile | partial
+    T* At = reinterpret_cast<T*>(smem_raw + 2 * kStageBytes);
     T* partial = At + static_cast<size_t>(N) * kPad;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int64_t i0 = static_cast<int64_t>(blockIdx.x) * kRows;
 
     auto issue = [&](int stage, int m0) {
         const int mc = J - m0 < kFwdChunk ? J - m0 : kFwdChunk;
-        if constexpr (KP > 0) {
-            // KP ints per monomial; the table rows are 4*KP bytes, copied in the widest unit
-            constexpr int unit = KP >= 4 ? 16 : KP * 4;
-            constexpr int per_row = KP * 4 / unit;
-            const char* src = reinterpret_cast<const char*>(offs_table + static_cast<int64_t>(m0) * KP);
-            char* dst = reinterpret_cast<char*>(offs_s + stage * kStageInts);
-            for (int x = tid; x < mc * per_row; x += kWarps * 32)
-                cp_async<unit>(dst + x * unit, src + x * unit);
-        }
-        for (int x = tid; x < mc; x += kWarps * 32)
-            cp_async<sizeof(T)>(coef_s + stage * kFwdChunk + x, C + m0 + x);
+        const unsigned char* src = records + static_cast<int64_t>(m0) * RB;
+        unsigned char* dst = smem_raw + stage * kStageBytes;
+        for (int x = tid * unit; x < mc * RB; x += kWarps * 32 * unit) cp_async<unit>(dst + x, src + x);
         cp_async_commit();
     };
 
@@ -247,17 +256,13 @@ hpe_fwd_rows(T* __restrict__ O, const T* __restrict__ A, const T* __restrict__ C
             cp_async_wait<0>();
         }
         __syncthreads();
-        const int32_t* offs = offs_s + stage * kStageInts;
-        const T* coef = coef_s + stage * kFwdChunk;
+        const unsigned char* recs = smem_raw + stage * kStageBytes;
 #pragma unroll 4
         for (int m = warp; m < mc; m += kWarps) {
-            T prod = coef[m];
-            if constexpr (K > 0) {
-                int o[KP > 0 ? KP : 1];
-                read_offsets<KP>(offs + m * KP, o);
+            int o[K > 0 ? K : 1];
+            T prod = read_record<T, K>(recs + m * RB, o);
 #pragma unroll
-                for (int k = 0; k < K; k++) prod *= col[o[k]];
-            }
+            for (int k = 0; k < K; k++) prod *= col[o[k]];
             acc += prod;
         }
         __syncthreads(); // the stage is overwritten by the copy issued next round
@@ -280,19 +285,19 @@ template <typename T, int K>
 __global__ void __launch_bounds__(kWarps * 32)
 hpe_vjp_rows(T* __restrict__ gA, const T* __restrict__ gO, const T* __restrict__ A, HpePlan plan,
              int64_t I, int N) {
-    constexpr int KQ = padded(K - 1);
-    constexpr int kRowInts = KQ > 0 ? KQ : 1;
+    constexpr int NF = K - 1 > 0 ? K - 1 : 0;
+    constexpr int RB = record_bytes(sizeof(T), NF);
+    constexpr int kStageBytes = kVjpChunk * RB;
+    constexpr int unit = RB >= 16 ? 16 : 8;
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    // layout: per warp 2 stages of (offsets, coefficients) | A tile
-    constexpr int kStageInts = kVjpChunk * kRowInts;
-    int32_t* offs_all = reinterpret_cast<int32_t*>(smem_raw);
-    T* coef_all = reinterpret_cast<T*>(offs_all + kWarps * 2 * kStageInts);
-    T* At = coef_all + kWarps * 2 * kVjpChunk;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // layout: per warp 2 stages of records | A tile
+    T* At = reinterpret_cast<T*>(smem_raw + kWarps * 2 * kStageBytes);
+    const int tid = threadIdx.x, lane = tid & 31;
+    // the shuffle tells the compiler that the warp number (and the incidence range and loop
+    // counts derived from it) is the same in all lanes
+    const int warp = __shfl_sync(kFullMask, tid >> 5, 0);
     const int64_t i0 = static_cast<int64_t>(blockIdx.x) * kRows;
-    int32_t* offs_w = offs_all + warp * 2 * kStageInts;
-    T* coef_w = coef_all + warp * 2 * kVjpChunk;
-    const T* coef_table = static_cast<const T*>(plan.vjp_coef);
+    unsigned char* recs_w = smem_raw + warp * 2 * kStageBytes;
 
     load_tile_transposed(At, A, i0, I, N, tid, kWarps * 32);
     cp_async_commit();
@@ -302,15 +307,9 @@ hpe_vjp_rows(T* __restrict__ gA, const T* __restrict__ gO, const T* __restrict__
 
     auto issue = [&](int stage, int x0) {
         const int xc = x_hi - x0 < kVjpChunk ? x_hi - x0 : kVjpChunk;
-        if constexpr (KQ > 0) {
-            constexpr int unit = KQ >= 4 ? 16 : kRowInts * 4;
-            constexpr int per_row = kRowInts * 4 / unit;
-            const char* src = reinterpret_cast<const char*>(plan.vjp_offs + static_cast<int64_t>(x0) * KQ);
-            char* dst = reinterpret_cast<char*>(offs_w + stage * kStageInts);
-            for (int y = lane; y < xc * per_row; y += 32) cp_async<unit>(dst + y * unit, src + y * unit);
-        }
-        for (int y = lane; y < xc; y += 32)
-            cp_async<sizeof(T)>(coef_w + stage * kVjpChunk + y, coef_table + x0 + y);
+        const unsigned char* src = plan.vjp_rec + static_cast<int64_t>(x0) * RB;
+        unsigned char* dst = recs_w + stage * kStageBytes;
+        for (int y = lane * unit; y < xc * RB; y += 32 * unit) cp_async<unit>(dst + y, src + y);
         cp_async_commit();
     };
     if (x_lo < x_hi) issue(0, x_lo);
@@ -339,24 +338,34 @@ hpe_vjp_rows(T* __restrict__ gA, const T* __restrict__ gO, const T* __restrict__
             cp_async_wait<0>();
         }
         __syncwarp();
-        const int32_t* offs = offs_w + stage * kStageInts;
-        const T* coef = coef_w + stage * kVjpChunk;
-        for (int y = 0; y < xc; y++) {
-            const int x = x0 + y;
-            while (x == end_n) { // group n is complete (possibly empty)
+        const unsigned char* recs = recs_w + stage * kStageBytes;
+        // One term: C_j times the other K-1 factors of incidence y of this stage.
+        auto term = [&](int y) -> T {
+            int o[NF > 0 ? NF : 1];
+            T prod = read_record<T, NF>(recs + y * RB, o);
+#pragma unroll
+            for (int k = 0; k < NF; k++) prod *= col[o[k]];
+            return prod;
+        };
+        int y = 0;
+        while (y < xc) {
+            while (x0 + y == end_n) { // group n is complete (possibly empty)
                 if (live) out[n] = go * acc;
                 acc = T(0);
                 n++;
                 end_n = __ldg(plan.n_start + n + 1);
             }
-            T prod = coef[y];
-            if constexpr (KQ > 0) {
-                int o[kRowInts];
-                read_offsets<KQ>(offs + y * KQ, o);
-#pragma unroll
-                for (int k = 0; k < K - 1; k++) prod *= col[o[k]];
+            // the rest of group n that lies in this stage: no group test inside
+            const int run_end = min(xc, end_n - x0);
+            T acc1 = T(0), acc2 = T(0), acc3 = T(0);
+            for (; y + 4 <= run_end; y += 4) {
+                acc += term(y);
+                acc1 += term(y + 1);
+                acc2 += term(y + 2);
+                acc3 += term(y + 3);
             }
-            acc += prod;
+            for (; y < run_end; y++) acc += term(y);
+            acc += (acc1 + acc2) + acc3;
         }
         __syncwarp(); // the stage is overwritten by the copy issued next round
     }
@@ -418,15 +427,13 @@ __global__ void hpe_vjp_wide(T* __restrict__ gA, const T* __restrict__ gO,
 }
 
 template <typename T, int K> size_t fwd_smem(int N) {
-    constexpr int KP = padded(K);
-    return 2 * kFwdChunk * (KP > 0 ? KP : 1) * sizeof(int32_t) + 2 * kFwdChunk * sizeof(T) +
+    return 2 * kFwdChunk * record_bytes(sizeof(T), K) +
            (static_cast<size_t>(N) * kPad + kWarps * 32) * sizeof(T);
 }
 
 template <typename T, int K> size_t vjp_smem(int N) {
-    constexpr int KQ = padded(K - 1);
-    return kWarps * 2 * kVjpChunk * (KQ > 0 ? KQ : 1) * sizeof(int32_t) +
-           kWarps * 2 * kVjpChunk * sizeof(T) + static_cast<size_t>(N) * kPad * sizeof(T);
+    return kWarps * 2 * kVjpChunk * record_bytes(sizeof(T), K - 1) +
+           static_cast<size_t>(N) * kPad * sizeof(T);
 }
 
 // Allocates the call-scoped tables and runs the plan kernel.
@@ -434,22 +441,18 @@ template <typename T>
 HpePlan make_plan(const Call& call, void** scratch, const T* C, const int32_t* P, int64_t J,
                   int K, int N, bool want_fwd, bool want_vjp) {
     auto up = [](size_t n) { return (n + 255) / 256 * 256; };
-    const int KP = padded(K), KQ = padded(K - 1);
     const size_t M = static_cast<size_t>(J) * K;
-    const size_t b_fwd = want_fwd ? up(static_cast<size_t>(J) * (KP > 0 ? KP : 1) * sizeof(int32_t)) : 0;
-    const size_t b_voffs = want_vjp ? up(M * (KQ > 0 ? KQ : 1) * sizeof(int32_t)) : 0;
-    const size_t b_vcoef = want_vjp ? up(M * sizeof(T)) : 0;
+    const size_t b_fwd = want_fwd ? up(static_cast<size_t>(J) * record_bytes(sizeof(T), K)) : 0;
+    const size_t b_vjp = want_vjp ? up(M * record_bytes(sizeof(T), K - 1)) : 0;
     const size_t b_n = up((static_cast<size_t>(N) + 1) * sizeof(int32_t));
-    unsigned char* p = static_cast<unsigned char*>(
-        scratch_alloc(call, b_fwd + b_voffs + b_vcoef + 2 * b_n + 256));
+    unsigned char* p =
+        static_cast<unsigned char*>(scratch_alloc(call, b_fwd + b_vjp + 2 * b_n + 256));
     *scratch = p;
     HpePlan plan;
-    plan.fwd_offs = reinterpret_cast<int32_t*>(p);
+    plan.fwd_rec = p;
     p += b_fwd;
-    plan.vjp_offs = reinterpret_cast<int32_t*>(p);
-    p += b_voffs;
-    plan.vjp_coef = p;
-    p += b_vcoef;
+    plan.vjp_rec = p;
+    p += b_vjp;
     plan.n_start = reinterpret_cast<int32_t*>(p);
     p += b_n;
     plan.cursor = reinterpret_cast<int32_t*>(p);
@@ -472,7 +475,7 @@ void launch_fwd(const Call& call, T* O, const T* A, const T* C, const int32_t* P
         MOPS_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           static_cast<int>(smem)));
     kernel<<<static_cast<unsigned>(ceil_div(I, kRows)), kWarps * 32, smem, call.stream>>>(
-        O, A, C, plan.fwd_offs, I, N, static_cast<int>(J));
+        O, A, plan.fwd_rec, I, N, static_cast<int>(J));
     MOPS_CUDA_OK(cudaGetLastError());
     scratch_free(call, scratch);
 }
@@ -553,7 +556,7 @@ void mops::cuda::homogeneous_polynomial_evaluation(Tensor<scalar_t, 1> output,
     }
     fits_int32(C.shape[0] * std::max<size_t>(indices_A.shape[1], 1) * 16, "the monomial table", op);
     const size_t smem = fwd_smem<scalar_t, kMaxOrder>(N); // the largest any order needs
-    if (smem <= static_cast<size_t>(max_optin_smem(call.device))) {
+    if (smem <= static_cast<size_t>(max_optin_smem(call.device)) && N <= kMaxTileColumns) {
 #define CALL(KK) launch_fwd<scalar_t, KK>(call, output.data, A.data, C.data, indices_A.data, I, N, J)
         MOPS_B200_ORDER_SWITCH(K, CALL)
 #undef CALL
@@ -583,7 +586,7 @@ void mops::cuda::homogeneous_polynomial_evaluation_vjp(Tensor<scalar_t, 2> grad_
     Call call = begin_call();
     fits_int32(C.shape[0] * std::max<size_t>(indices_A.shape[1], 1) * 16, "the monomial table", op);
     const size_t smem = vjp_smem<scalar_t, kMaxOrder>(N);
-    if (smem <= static_cast<size_t>(max_optin_smem(call.device))) {
+    if (smem <= static_cast<size_t>(max_optin_smem(call.device)) && N <= kMaxTileColumns) {
 #define CALL(KK)                                                                                   \
     launch_vjp<scalar_t, KK>(call, grad_A.data, grad_output.data, A.data, C.data, indices_A.data,  \
                              I, N, J)
