@@ -109,7 +109,14 @@ template <typename T> __device__ __forceinline__ T warp_sum(T v) {
 }
 
 // Fire-and-forget global accumulation (compiles to RED: no value comes back).
-template <typename T> __device__ __forceinline__ void red_add(T* addr, T v) { atomicAdd(addr, v); }
+// Reductions without a return value (atomicAdd with an unused result can still be compiled
+// to the returning form, which holds a register and a scoreboard until the L2 answers).
+__device__ __forceinline__ void red_add(double* addr, double v) {
+    asm volatile("red.global.add.f64 [%0], %1;\n" ::"l"(addr), "d"(v) : "memory");
+}
+__device__ __forceinline__ void red_add(float* addr, float v) {
+    asm volatile("red.global.add.f32 [%0], %1;\n" ::"l"(addr), "f"(v) : "memory");
+}
 
 // Unsorted index: runs only when the segmented kernel of the same call reported it.
 template <typename T>
@@ -120,6 +127,21 @@ __global__ void zero_if_unsorted(T* __restrict__ out, int64_t n, Status st) {
         out[i] = T(0);
 }
 
+
+// ---------------------------------------------------------------- FP64 tensor-core MMA
+// mma.sync m8n8k4, f64. Fragment layout (lane = 4*qr + qc): A[qr][qc], B[k = qc][n = qr],
+// C[qr][2*qc + {0,1}].
+__device__ __forceinline__ void dmma(double (&c)[2], double a, double b) {
+    asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};\n"
+                 : "+d"(c[0]), "+d"(c[1])
+                 : "d"(a), "d"(b));
+}
+// c = a b (no accumulator input)
+__device__ __forceinline__ void dmma0(double (&c)[2], double a, double b) {
+    asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%4,%4};\n"
+                 : "=d"(c[0]), "=d"(c[1])
+                 : "d"(a), "d"(b), "d"(0.0));
+}
 
 // ---------------------------------------------------------------- asynchronous staging
 // Element-wise global -> shared copies that do not pass through registers (LDGSTS): a lane

@@ -448,6 +448,7 @@ struct VjpPlan {
     int nkc;    // number of KP-wide chunks of K
     int threads;
     size_t smem;
+    bool only_if_unsorted; // run only when the segmented kernel of the same call stood down
 };
 
 template <typename T, int KP, int VL, bool WEIGHTED>
@@ -458,6 +459,7 @@ opsa_vjp_entries(T* __restrict__ gA, T* __restrict__ gB, T* __restrict__ gW,
                  const int32_t* __restrict__ P, int64_t J, int K, int L, int64_t nO,
                  VjpPlan plan, Status st) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
+    if (plan.only_if_unsorted && !saw_unsorted(st)) return;
     const int tid = threadIdx.x, EPB = blockDim.x;
     const int Kp = plan.Kp, Lp = plan.Lp, nkc = plan.nkc;
     T* As = reinterpret_cast<T*>(smem_raw);              // [EPB][Kp]  A rows, then gA rows
@@ -645,7 +647,8 @@ __global__ void opsa_vjp_wide(T* __restrict__ gA, T* __restrict__ gB, T* __restr
                               const T* __restrict__ gO, const T* __restrict__ A,
                               const T* __restrict__ B, const T* __restrict__ W,
                               const int32_t* __restrict__ PW, const int32_t* __restrict__ P,
-                              int64_t J, int K, int L, int64_t nO, Status st) {
+                              int64_t J, int K, int L, int64_t nO, bool only_if_unsorted, Status st) {
+    if (only_if_unsorted && !saw_unsorted(st)) return;
     const int64_t per = static_cast<int64_t>(K) + L;
     const int64_t total = J * per;
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
@@ -678,6 +681,176 @@ __global__ void opsa_vjp_wide(T* __restrict__ gA, T* __restrict__ gB, T* __restr
             if (WEIGHTED && gW != nullptr)
                 red_add(gW + static_cast<int64_t>(pw) * L + l, s * B[j * L + l]);
         }
+    }
+}
+
+// ----------------------------------------------------------------------- VJP, tensor cores
+// K <= 16, L <= 32, entries sorted by output row (f32 operands are widened to f64 in
+// registers: the products are then exact and the sums far inside the f32 tolerance). For the entries of one output row the
+// two gradients are small matrix products with the row's grad_output as the common factor,
+//     grad_A[seg, :] = B[seg, :] gO[p]^T      grad_B[seg, :] = A[seg, :] gO[p]
+// so a warp takes one output row, keeps gO[p] in registers as MMA fragments and walks the
+// row's entries eight at a time (the eight entries are the MMA's m dimension). The A and B
+// fragments come straight from global memory (a fragment row is one 32-byte sector) and the
+// results go straight back; nothing is staged. With weights, grad_A uses B*W[PW[e]], and
+// X = A gO gives grad_B = X*W[PW[e]] and grad_W[PW[e]] += X*B.
+// KT = ceil(K / 4), LT8 = ceil(L / 8).
+template <typename S, int KT, int LT8, bool WEIGHTED>
+__global__ void __launch_bounds__(128, 3)
+opsa_vjp_mma(S* __restrict__ gA, S* __restrict__ gB, S* __restrict__ gW,
+             const S* __restrict__ gO, const S* __restrict__ A, const S* __restrict__ B,
+             const S* __restrict__ W, const int32_t* __restrict__ PW,
+             const int64_t* __restrict__ offsets, int K, int L, int64_t nO, int64_t nW, Status st) {
+    using T = double;
+    using S2 = typename VecOf<S, 2>::type;
+    constexpr int NTK = (KT + 1) / 2; // 8-wide tiles over K
+    constexpr int KSL = 2 * LT8;      // k-steps over L
+    constexpr int NTL = LT8;          // 8-wide tiles over L
+    constexpr int KSK = KT;           // k-steps over K
+    if (saw_unsorted(st)) return;     // the entry-per-lane kernel of the same call does the work
+    const int warps = blockDim.x >> 5, lane = threadIdx.x & 31;
+    const int warp = __shfl_sync(kFullMask, threadIdx.x >> 5, 0); // uniform for the compiler
+    const int qr = lane >> 2, qc = lane & 3;
+    const int64_t nwarps = static_cast<int64_t>(gridDim.x) * warps;
+    const int64_t rowsize = static_cast<int64_t>(K) * L;
+    const bool want_a = gA != nullptr, want_b = gB != nullptr || (WEIGHTED && gW != nullptr);
+    const bool pair_ok = L % 2 == 0; // two-scalar accesses to rows of B, W, grad_B
+
+    for (int64_t r = static_cast<int64_t>(blockIdx.x) * warps + warp; r < nO; r += nwarps) {
+        const int64_t lo = offsets[r], hi = offsets[r + 1];
+        if (lo >= hi) continue;
+        const S* g = gO + r * rowsize;
+        // gO[p] as the B operand of both products
+        T ga_k[NTK][KSL]; // [k-step over l][n = k]: gO[k = 8 nt + qr][l = 4 ks + qc]
+        T gb_k[NTL][KSK]; // [k-step over k][n = l]: gO[k = 4 ks + qc][l = 8 nt + qr]
+#pragma unroll
+        for (int nt = 0; nt < NTK; nt++)
+#pragma unroll
+            for (int ks = 0; ks < KSL; ks++) {
+                const int k = 8 * nt + qr, l = 4 * ks + qc;
+                ga_k[nt][ks] = (want_a && k < K && l < L) ? static_cast<T>(__ldg(g + k * L + l)) : T(0);
+            }
+#pragma unroll
+        for (int nt = 0; nt < NTL; nt++)
+#pragma unroll
+            for (int ks = 0; ks < KSK; ks++) {
+                const int k = 4 * ks + qc, l = 8 * nt + qr;
+                gb_k[nt][ks] = (want_b && k < K && l < L) ? static_cast<T>(__ldg(g + k * L + l)) : T(0);
+            }
+
+        // A-operand fragments of the tile that starts at e0: entry e0 + qr, column 4 ks + qc
+        auto load_tile = [&](int64_t e0, T (&af)[KSK], T (&bf)[KSL], int32_t& wrow) {
+            const int64_t e = e0 + qr;
+            const bool valid = e < hi;
+            wrow = 0;
+            if (WEIGHTED && valid) {
+                wrow = __ldg(PW + e);
+                if (clamp_index(wrow, static_cast<int32_t>(nW))) report_bad_index(st, 1);
+            }
+#pragma unroll
+            for (int ks = 0; ks < KSK; ks++) {
+                const int k = 4 * ks + qc;
+                af[ks] = (want_b && valid && k < K) ? static_cast<T>(__ldg(A + e * K + k)) : T(0);
+            }
+#pragma unroll
+            for (int ks = 0; ks < KSL; ks++) {
+                const int l = 4 * ks + qc;
+                T v = (want_a && valid && l < L) ? static_cast<T>(__ldg(B + e * L + l)) : T(0);
+                if (WEIGHTED && want_a && valid && l < L)
+                    v *= static_cast<T>(__ldg(W + static_cast<int64_t>(wrow) * L + l));
+                bf[ks] = v;
+            }
+        };
+
+        T af[KSK], bf[KSL], af_n[KSK], bf_n[KSL];
+        int32_t wrow, wrow_n = 0;
+        load_tile(lo, af, bf, wrow);
+        for (int64_t e0 = lo; e0 < hi; e0 += 8) {
+            if (e0 + 8 < hi) load_tile(e0 + 8, af_n, bf_n, wrow_n);
+            const int64_t e = e0 + qr;
+            const bool valid = e < hi;
+            if (want_a) {
+#pragma unroll
+                for (int nt = 0; nt < NTK; nt++) {
+                    T c[2];
+                    dmma0(c, bf[0], ga_k[nt][0]);
+#pragma unroll
+                    for (int ks = 1; ks < KSL; ks++) dmma(c, bf[ks], ga_k[nt][ks]);
+                    const int k = 8 * nt + 2 * qc;
+                    S* dst = gA + e * K + k;
+                    if (valid && k < K) dst[0] = static_cast<S>(c[0]);
+                    if (valid && k + 1 < K) dst[1] = static_cast<S>(c[1]);
+                }
+            }
+            if (want_b) {
+#pragma unroll
+                for (int nt = 0; nt < NTL; nt++) {
+                    T c[2];
+                    dmma0(c, af[0], gb_k[nt][0]);
+#pragma unroll
+                    for (int ks = 1; ks < KSK; ks++) dmma(c, af[ks], gb_k[nt][ks]);
+                    const int l = 8 * nt + 2 * qc;
+                    if (!valid || l >= L) continue;
+                    const bool two = l + 1 < L;
+                    if (WEIGHTED) {
+                        const S* wp = W + static_cast<int64_t>(wrow) * L + l;
+                        const S* bp = B + e * L + l;
+                        T w0, w1 = T(0), b0, b1 = T(0);
+                        if (pair_ok) {
+                            const S2 w2 = *reinterpret_cast<const S2*>(wp);
+                            const S2 b2 = *reinterpret_cast<const S2*>(bp);
+                            w0 = w2.x, w1 = w2.y, b0 = b2.x, b1 = b2.y;
+                        } else {
+                            w0 = wp[0], b0 = bp[0];
+                            if (two) w1 = wp[1], b1 = bp[1];
+                        }
+                        if (gW != nullptr) {
+                            S* gw = gW + static_cast<int64_t>(wrow) * L + l;
+                            red_add(gw, static_cast<S>(c[0] * b0));
+                            if (two) red_add(gw + 1, static_cast<S>(c[1] * b1));
+                        }
+                        c[0] *= w0;
+                        c[1] *= w1;
+                    }
+                    if (gB != nullptr) {
+                        S* dst = gB + e * L + l;
+                        if (pair_ok) {
+                            S2 v2;
+                            v2.x = static_cast<S>(c[0]), v2.y = static_cast<S>(c[1]);
+                            *reinterpret_cast<S2*>(dst) = v2;
+                        } else {
+                            dst[0] = static_cast<S>(c[0]);
+                            if (two) dst[1] = static_cast<S>(c[1]);
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int ks = 0; ks < KSK; ks++) af[ks] = af_n[ks];
+#pragma unroll
+            for (int ks = 0; ks < KSL; ks++) bf[ks] = bf_n[ks];
+            wrow = wrow_n;
+        }
+    }
+}
+
+template <typename S, int KT, bool WEIGHTED, typename... Args>
+void launch_vjp_mma_l(int L, unsigned blocks, cudaStream_t stream, Args... args) {
+    switch ((L + 7) / 8) {
+    case 1: opsa_vjp_mma<S, KT, 1, WEIGHTED><<<blocks, 128, 0, stream>>>(args...); break;
+    case 2: opsa_vjp_mma<S, KT, 2, WEIGHTED><<<blocks, 128, 0, stream>>>(args...); break;
+    case 3: opsa_vjp_mma<S, KT, 3, WEIGHTED><<<blocks, 128, 0, stream>>>(args...); break;
+    default: opsa_vjp_mma<S, KT, 4, WEIGHTED><<<blocks, 128, 0, stream>>>(args...); break;
+    }
+}
+
+template <typename S, bool WEIGHTED, typename... Args>
+void launch_vjp_mma(int K, int L, unsigned blocks, cudaStream_t stream, Args... args) {
+    switch ((K + 3) / 4) {
+    case 1: launch_vjp_mma_l<S, 1, WEIGHTED>(L, blocks, stream, args...); break;
+    case 2: launch_vjp_mma_l<S, 2, WEIGHTED>(L, blocks, stream, args...); break;
+    case 3: launch_vjp_mma_l<S, 3, WEIGHTED>(L, blocks, stream, args...); break;
+    default: launch_vjp_mma_l<S, 4, WEIGHTED>(L, blocks, stream, args...); break;
     }
 }
 
@@ -732,6 +905,30 @@ void backward(const Call& call, T* gA, T* gB, T* gW, const T* gO, const T* A, co
     }
 
     VjpPlan plan;
+    plan.only_if_unsorted = false;
+    if constexpr (sizeof(T) == 8) { // (measured slower than the kernels below for f32)
+        if (K <= 16 && L <= 32) {
+            // Sorted scatter index (checked on the device): one warp per output row on the
+            // tensor-core path; otherwise the entry-per-lane kernels below do the work.
+            const int sms = sm_count(call.device);
+            int64_t* offsets =
+                static_cast<int64_t*>(scratch_alloc(call, (nO + 1) * sizeof(int64_t)));
+            const int64_t pre_blocks = std::min<int64_t>(ceil_div(J + 1, 256), sms * 32);
+            segment_offsets<<<static_cast<unsigned>(pre_blocks), 256, 0, call.stream>>>(
+                P, J, nO, offsets, call.status);
+            const unsigned blocks =
+                static_cast<unsigned>(std::min<int64_t>(ceil_div(nO, 4), sms * 3));
+            launch_vjp_mma<T, WEIGHTED>(K, L, blocks, call.stream, gA, gB, gW, gO, A, B, W, PW,
+                                        offsets, K, L, nO, nO, call.status);
+            MOPS_CUDA_OK(cudaGetLastError());
+            scratch_free(call, offsets);
+            if (call.wait) {
+                wait_stream(call);
+                if (!host_saw_unsorted(call)) return;
+            }
+            plan.only_if_unsorted = true; // asynchronous calls cannot look: always enqueue
+        }
+    }
     const int KP = vjp_tile_k(K);
     plan.nkc = static_cast<int>(ceil_div(K, KP));
     plan.Kp = K | 1;
@@ -772,7 +969,7 @@ void backward(const Call& call, T* gA, T* gB, T* gW, const T* gO, const T* A, co
         }
     } else {
         opsa_vjp_wide<T, WEIGHTED><<<sm_count(call.device) * 8, 256, 0, call.stream>>>(
-            gA, gB, gW, gO, A, B, W, PW, P, J, K, L, nO, call.status);
+            gA, gB, gW, gO, A, B, W, PW, P, J, K, L, nO, plan.only_if_unsorted, call.status);
     }
     MOPS_CUDA_OK(cudaGetLastError());
 }

@@ -627,11 +627,6 @@ __global__ void sasaw_vjp_fast(T* __restrict__ gA, T* __restrict__ gB, T* __rest
 // Fragment layout of m8n8k4 (lane = 4*qr + qc): A[qr][qc], B[k = qc][n = qr],
 // C[qr][2*qc + {0,1}].
 
-__device__ __forceinline__ void dmma(double (&c)[2], double a, double b) {
-    asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};\n"
-                 : "+d"(c[0]), "+d"(c[1])
-                 : "d"(a), "d"(b));
-}
 
 // Row stride for an A-operand matrix read as 8 rows x 4 columns per fragment: a multiple of
 // four that is 4 or 12 modulo 16, so that the eight rows fall on distinct banks.
@@ -672,12 +667,6 @@ template <int TP> struct VjpMma {
     }
 };
 
-// c = a b (no accumulator input)
-__device__ __forceinline__ void dmma0(double (&c)[2], double a, double b) {
-    asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%4,%4};\n"
-                 : "=d"(c[0]), "=d"(c[1])
-                 : "d"(a), "d"(b), "d"(0.0));
-}
 
 // KS3 = number of four-row k-steps that cover output_size.
 // Predicated forms (one instruction each, no branch around them).
