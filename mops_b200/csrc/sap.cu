@@ -521,6 +521,329 @@ Plan<T> make_plan(const Call& call, void** scratch, const T* C, const int32_t* P
     return plan;
 }
 
+// ------------------------------------------------------------ small-operand kernels
+// When one of A, B has at most 16 columns (angular channels up to l = 7) its row fits in
+// registers. Call it S and the other operand T. Sorting the triplets by (output column, S
+// column) turns the forward sum into
+//     O[i, o] = sum_s S[i, s] * ( sum_{k in (o, s)} C_k T[i, PT_k] ),
+// with s a compile-time index in the unrolled loop, so only T is read from shared memory: one
+// operand read per triplet instead of two. Sorted by (T column, S column) the VJP becomes
+//     inner = sum_{k in (t, s)} C_k gO[i, PO_k]
+//     gT[i, t] = sum_s S[i, s] inner,      gS[i, s] = sum_t T[i, t] inner,
+// one operand read per triplet instead of four, and gS accumulates in registers.
+constexpr int kSmallPad = 2; // zero entries after the last triplet (the row loops read ahead)
+
+template <typename T> struct SmallPlan {
+    Entry<T>* table; // sorted triplets: (c, tile offset of the streamed operand, unused)
+    int32_t* start;  // [groups * NS + 1] first triplet of every (group, s)
+    int32_t* cursor; // scratch of the same size
+};
+
+// mode 0 (forward): groups = output columns, streamed operand = T.
+// mode 1 (VJP):     groups = T columns,      streamed operand = gO.
+template <typename T>
+__global__ void __launch_bounds__(kPlanThreads)
+sap_plan_small(SmallPlan<T> plan, const T* __restrict__ C, const int32_t* __restrict__ PS,
+               const int32_t* __restrict__ PT, const int32_t* __restrict__ PO, int K, int nS,
+               int nT, int nO, int NS, int stride, int mode, int bit_s, int bit_t, Status st) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid < kSmallPad) plan.table[K + tid] = Entry<T>{T(0), 0, 0}; // read ahead by the row loops
+    for (int k = tid; k < K; k += kPlanThreads) {
+        int32_t ps = PS[k], pt = PT[k], po = PO[k];
+        if (clamp_index(ps, nS)) report_bad_index(st, bit_s);
+        if (clamp_index(pt, nT)) report_bad_index(st, bit_t);
+        if (clamp_index(po, nO)) report_bad_index(st, 2);
+    }
+    if (warp != 0) return;
+    const int groups = mode == 0 ? nO : nT, nbins = groups * NS;
+    auto key_of = [&](int k) {
+        int32_t ps = PS[k], g = mode == 0 ? PO[k] : PT[k];
+        clamp_index(ps, nS);
+        clamp_index(g, groups);
+        return g * NS + ps;
+    };
+    int32_t* cursor = plan.cursor;
+    for (int b = lane; b <= nbins; b += 32) cursor[b] = 0;
+    __syncwarp();
+    for (int k = lane; k < K; k += 32) atomicAdd(&cursor[key_of(k)], 1);
+    __syncwarp();
+    int run = 0;
+    for (int b0 = 0; b0 <= nbins; b0 += 32) {
+        const int b = b0 + lane;
+        const int v = b < nbins ? cursor[b] : 0;
+        int incl = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(kFullMask, incl, o);
+            if (lane >= o) incl += t;
+        }
+        if (b <= nbins) {
+            plan.start[b] = run + incl - v;
+            cursor[b] = run + incl - v;
+        }
+        run += __shfl_sync(kFullMask, incl, 31);
+    }
+    __syncwarp();
+    for (int k0 = 0; k0 < K; k0 += 32) { // stable: equal keys keep ascending k
+        const int k = k0 + lane;
+        const bool live = k < K;
+        const int32_t v = live ? key_of(k) : -1 - lane;
+        const unsigned same = __match_any_sync(kFullMask, v);
+        const int rank = __popc(same & ((1u << lane) - 1));
+        const int leader = __ffs(same) - 1;
+        int base = 0;
+        if (live && lane == leader) {
+            base = cursor[v];
+            cursor[v] = base + __popc(same);
+        }
+        base = __shfl_sync(kFullMask, base, leader);
+        if (live) {
+            int32_t x = mode == 0 ? PT[k] : PO[k];
+            clamp_index(x, mode == 0 ? nT : nO);
+            plan.table[base + rank] = Entry<T>{C[k], x * stride, 0};
+        }
+        __syncwarp();
+    }
+}
+
+// Row i of the small operand into registers (zero beyond its width).
+template <typename T, int NS>
+__device__ __forceinline__ void load_small_row(T (&s)[NS], const T* __restrict__ S, int64_t i,
+                                               int nS) {
+#pragma unroll
+    for (int q = 0; q < NS; q++) s[q] = q < nS ? __ldg(S + i * nS + q) : T(0);
+}
+
+// Copies the plan's tables into shared memory behind the tiles.
+template <typename T>
+__device__ __forceinline__ void stage_small(const SmallPlan<T>& plan, int K, int nbins,
+                                            unsigned char* slot, const Entry<T>*& table,
+                                            const int32_t*& start) {
+    Entry<T>* t = reinterpret_cast<Entry<T>*>(slot);
+    int32_t* st =
+        reinterpret_cast<int32_t*>(slot + static_cast<size_t>(K + kSmallPad) * sizeof(Entry<T>));
+    for (int k = threadIdx.x; k < K + kSmallPad; k += blockDim.x)
+        cp_async<16>(t + k, plan.table + k);
+    for (int b = threadIdx.x; b <= nbins; b += blockDim.x) cp_async<4>(st + b, plan.start + b);
+    table = t;
+    start = st;
+}
+
+template <typename T, int NS>
+__global__ void sap_fwd_small(T* __restrict__ O, const T* __restrict__ S, const T* __restrict__ Tm,
+                              SmallPlan<T> plan, int64_t I, int nS, int nT, int nO, int K) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int R = blockDim.x, stride = R + 1, tid = threadIdx.x;
+    T* Tt = reinterpret_cast<T*>(smem_raw);
+    unsigned char* tables = smem_raw + up16(static_cast<size_t>(nT) * stride * sizeof(T));
+    const int64_t i0 = static_cast<int64_t>(blockIdx.x) * R;
+    tile_load(Tt, nT, Tm, i0, I, R, stride);
+    const Entry<T>* table;
+    const int32_t* start;
+    stage_small(plan, K, nO * NS, tables, table, start);
+    cp_async_commit();
+    const int64_t i = i0 + tid;
+    T sreg[NS];
+    load_small_row<T, NS>(sreg, S, i < I ? i : I - 1, nS);
+    cp_async_wait<0>();
+    __syncthreads();
+    if (i >= I) return;
+    const T* t = Tt + tid;
+    T* o = O + i * nO;
+    // The triplets are one stream across all groups, read two ahead: (c0, v0) is triplet k with
+    // its operand already loaded, e1 is triplet k + 1.
+    int k = 0;
+    Entry<T> e1 = fetch_shared(table);
+    T c0 = e1.c, v0 = t[e1.o1];
+    e1 = fetch_shared(table + 1);
+    for (int col = 0; col < nO; col++) {
+        const int32_t* bounds = start + col * NS + 1;
+        T acc = T(0);
+#pragma unroll
+        for (int q = 0; q < NS; q++) {
+            const int end = bounds[q];
+            T inner = T(0);
+            for (; k < end; k++) {
+                const Entry<T> e2 = fetch_shared(table + k + 2);
+                const T v1 = t[e1.o1];
+                inner += c0 * v0;
+                c0 = e1.c, v0 = v1, e1 = e2;
+            }
+            acc += sreg[q] * inner;
+        }
+        o[col] = acc;
+    }
+}
+
+template <typename T, int NS>
+__global__ void sap_vjp_small(T* __restrict__ gS, T* __restrict__ gT, const T* __restrict__ gO,
+                              const T* __restrict__ S, const T* __restrict__ Tm,
+                              SmallPlan<T> plan, int64_t I, int nS, int nT, int nO, int K) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int R = blockDim.x, stride = R + 1, tid = threadIdx.x;
+    T* Tt = reinterpret_cast<T*>(smem_raw);
+    T* Gt = Tt + static_cast<size_t>(nT) * stride;
+    unsigned char* tables = smem_raw + up16(static_cast<size_t>(nT + nO) * stride * sizeof(T));
+    const int64_t i0 = static_cast<int64_t>(blockIdx.x) * R;
+    if (gS != nullptr) tile_load(Tt, nT, Tm, i0, I, R, stride);
+    tile_load(Gt, nO, gO, i0, I, R, stride);
+    const Entry<T>* table;
+    const int32_t* start;
+    stage_small(plan, K, nT * NS, tables, table, start);
+    cp_async_commit();
+    const int64_t i = i0 + tid;
+    T sreg[NS], gs[NS];
+    load_small_row<T, NS>(sreg, S, i < I ? i : I - 1, nS);
+#pragma unroll
+    for (int q = 0; q < NS; q++) gs[q] = T(0);
+    cp_async_wait<0>();
+    __syncthreads();
+    if (i >= I) return;
+    const T* g = Gt + tid;
+    const T* t = Tt + tid;
+    int k = 0; // one stream of triplets read two ahead, as in the forward kernel
+    Entry<T> e1 = fetch_shared(table);
+    T c0 = e1.c, v0 = g[e1.o1];
+    e1 = fetch_shared(table + 1);
+    for (int col = 0; col < nT; col++) {
+        const int32_t* bounds = start + col * NS + 1;
+        const T tv = gS != nullptr ? t[col * stride] : T(0);
+        T acc = T(0);
+#pragma unroll
+        for (int q = 0; q < NS; q++) {
+            const int end = bounds[q];
+            T inner = T(0);
+            for (; k < end; k++) {
+                const Entry<T> e2 = fetch_shared(table + k + 2);
+                const T v1 = g[e1.o1];
+                inner += c0 * v0;
+                c0 = e1.c, v0 = v1, e1 = e2;
+            }
+            acc += sreg[q] * inner;
+            gs[q] += tv * inner;
+        }
+        if (gT != nullptr) gT[i * nT + col] = acc;
+    }
+    if (gS != nullptr) {
+#pragma unroll
+        for (int q = 0; q < NS; q++)
+            if (q < nS) gS[i * nS + q] = gs[q];
+    }
+}
+
+// Width of the register-resident operand (4, 8 or 16), or 0 when neither operand is small.
+inline int small_width(int nA, int nB) {
+    const int n = std::min(nA, nB);
+    return n <= 4 ? 4 : n <= 8 ? 8 : n <= 16 ? 16 : 0;
+}
+
+// Rows per block for tiles of `cols` columns plus the small plan's tables: the block size that
+// puts the most warps on an SM (the tables are per block, the tiles per row); 0 if 32 rows do
+// not fit.
+template <typename T>
+int rows_small(const Call& call, int cols, int64_t K, int nbins, size_t* smem) {
+    const size_t limit = static_cast<size_t>(max_optin_smem(call.device));
+    const size_t per_sm = 228 * 1024, reserved = 1024;
+    const size_t tables = up16(static_cast<size_t>(K + kSmallPad) * sizeof(Entry<T>) +
+                               (static_cast<size_t>(nbins) + 1) * 4);
+    int best_r = 0, best_warps = 0;
+    for (int R : {32, 64, 96, 128, 160, 192, 256, 320, 384, 512}) {
+        const size_t total = up16(static_cast<size_t>(cols) * (R + 1) * sizeof(T)) + tables;
+        if (total > limit) break;
+        const int blocks = static_cast<int>(std::min<size_t>(per_sm / (total + reserved), 32));
+        const int warps = std::min(blocks * (R / 32), 64);
+        if (warps > best_warps) {
+            best_warps = warps;
+            best_r = R;
+            *smem = total;
+        }
+    }
+    return best_r;
+}
+
+template <typename T>
+SmallPlan<T> make_small_plan(const Call& call, void** scratch, const T* C, const int32_t* PS,
+                             const int32_t* PT, const int32_t* PO, int64_t K, int nS, int nT,
+                             int nO, int NS, int stride, int mode, int bit_s, int bit_t) {
+    const size_t nbins = static_cast<size_t>(mode == 0 ? nO : nT) * NS;
+    const size_t table = up16(static_cast<size_t>(K + kSmallPad) * sizeof(Entry<T>));
+    const size_t ints = up16((nbins + 1) * sizeof(int32_t));
+    unsigned char* p = static_cast<unsigned char*>(scratch_alloc(call, table + 2 * ints));
+    *scratch = p;
+    SmallPlan<T> plan;
+    plan.table = reinterpret_cast<Entry<T>*>(p);
+    plan.start = reinterpret_cast<int32_t*>(p + table);
+    plan.cursor = reinterpret_cast<int32_t*>(p + table + ints);
+    sap_plan_small<T><<<1, kPlanThreads, 0, call.stream>>>(plan, C, PS, PT, PO,
+                                                           static_cast<int>(K), nS, nT, nO, NS,
+                                                           stride, mode, bit_s, bit_t, call.status);
+    MOPS_CUDA_OK(cudaGetLastError());
+    return plan;
+}
+
+// Forward with the narrower of A, B in registers. Returns false if it does not apply.
+template <typename T>
+bool forward_small(const Call& call, T* O, const T* A, const T* B, const T* C, const int32_t* PA,
+                   const int32_t* PB, const int32_t* PO, int64_t I, int64_t K, int nA, int nB,
+                   int nO) {
+    const int NS = small_width(nA, nB);
+    if (NS == 0 || static_cast<int64_t>(nO) * NS > (1 << 20)) return false;
+    const bool b_small = nB <= nA;
+    const T *S = b_small ? B : A, *Tm = b_small ? A : B;
+    const int32_t *PS = b_small ? PB : PA, *PT = b_small ? PA : PB;
+    const int nS = b_small ? nB : nA, nT = b_small ? nA : nB;
+    size_t smem = 0;
+    const int R = rows_small<T>(call, nT, K, nO * NS, &smem);
+    if (R == 0) return false;
+    void* scratch = nullptr;
+    SmallPlan<T> plan = make_small_plan<T>(call, &scratch, C, PS, PT, PO, K, nS, nT, nO, NS, R + 1,
+                                           0, b_small ? 1 : 0, b_small ? 0 : 1);
+    const unsigned blocks = static_cast<unsigned>(ceil_div(I, R));
+#define MOPS_B200_LAUNCH(NS_)                                                                      \
+    {                                                                                              \
+        allow_smem(sap_fwd_small<T, NS_>, smem);                                                   \
+        sap_fwd_small<T, NS_><<<blocks, R, smem, call.stream>>>(O, S, Tm, plan, I, nS, nT, nO,     \
+                                                                static_cast<int>(K));              \
+    }
+    if (NS == 4) MOPS_B200_LAUNCH(4) else if (NS == 8) MOPS_B200_LAUNCH(8) else MOPS_B200_LAUNCH(16)
+#undef MOPS_B200_LAUNCH
+    MOPS_CUDA_OK(cudaGetLastError());
+    scratch_free(call, scratch);
+    return true;
+}
+
+template <typename T>
+bool backward_small(const Call& call, T* gA, T* gB, const T* gO, const T* A, const T* B,
+                    const T* C, const int32_t* PA, const int32_t* PB, const int32_t* PO, int64_t I,
+                    int64_t K, int nA, int nB, int nO) {
+    const int NS = small_width(nA, nB);
+    if (NS == 0) return false;
+    const bool b_small = nB <= nA;
+    const T *S = b_small ? B : A, *Tm = b_small ? A : B;
+    T *gS = b_small ? gB : gA, *gT = b_small ? gA : gB;
+    const int32_t *PS = b_small ? PB : PA, *PT = b_small ? PA : PB;
+    const int nS = b_small ? nB : nA, nT = b_small ? nA : nB;
+    if (static_cast<int64_t>(nT) * NS > (1 << 20)) return false;
+    size_t smem = 0;
+    const int R = rows_small<T>(call, nT + nO, K, nT * NS, &smem);
+    if (R == 0) return false;
+    void* scratch = nullptr;
+    SmallPlan<T> plan = make_small_plan<T>(call, &scratch, C, PS, PT, PO, K, nS, nT, nO, NS, R + 1,
+                                           1, b_small ? 1 : 0, b_small ? 0 : 1);
+    const unsigned blocks = static_cast<unsigned>(ceil_div(I, R));
+#define MOPS_B200_LAUNCH(NS_)                                                                      \
+    {                                                                                              \
+        allow_smem(sap_vjp_small<T, NS_>, smem);                                                   \
+        sap_vjp_small<T, NS_><<<blocks, R, smem, call.stream>>>(gS, gT, gO, S, Tm, plan, I, nS,    \
+                                                                nT, nO, static_cast<int>(K));      \
+    }
+    if (NS == 4) MOPS_B200_LAUNCH(4) else if (NS == 8) MOPS_B200_LAUNCH(8) else MOPS_B200_LAUNCH(16)
+#undef MOPS_B200_LAUNCH
+    MOPS_CUDA_OK(cudaGetLastError());
+    scratch_free(call, scratch);
+    return true;
+}
+
 const char* const kIndexNames[] = {"indices_A", "indices_B", "indices_output"};
 
 template <typename scalar_t>
@@ -563,6 +886,11 @@ void mops::cuda::sparse_accumulation_of_products(Tensor<scalar_t, 2> output, Ten
             throw std::runtime_error("Index arrays in operation " + op +
                                      " refer to columns of an operand that has none");
         MOPS_CUDA_OK(cudaMemsetAsync(output.data, 0, I * nO * sizeof(scalar_t), call.stream));
+        end_call(call, op.c_str(), kIndexNames, 3);
+        return;
+    }
+    if (forward_small<scalar_t>(call, output.data, A.data, B.data, C.data, indices_A.data,
+                                indices_B.data, indices_output.data, I, K, nA, nB, nO)) {
         end_call(call, op.c_str(), kIndexNames, 3);
         return;
     }
@@ -612,6 +940,12 @@ void mops::cuda::sparse_accumulation_of_products_vjp(
             MOPS_CUDA_OK(cudaMemsetAsync(grad_A.data, 0, I * nA * sizeof(scalar_t), call.stream));
         if (grad_B.data != nullptr && nB > 0)
             MOPS_CUDA_OK(cudaMemsetAsync(grad_B.data, 0, I * nB * sizeof(scalar_t), call.stream));
+        end_call(call, op.c_str(), kIndexNames, 3);
+        return;
+    }
+    if (backward_small<scalar_t>(call, grad_A.data, grad_B.data, grad_output.data, A.data, B.data,
+                                 C.data, indices_A.data, indices_B.data, indices_output.data, I, K,
+                                 nA, nB, nO)) {
         end_call(call, op.c_str(), kIndexNames, 3);
         return;
     }
