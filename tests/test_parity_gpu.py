@@ -127,6 +127,38 @@ def test_outer_product_shapes(oracle, K, L, dtype):
     compare("opsaw", workloads.opsaw(E=700, K=K, L=L, n=23), dtype, oracle, what=f"opsaw {K}x{L}")
 
 
+@pytest.mark.parametrize("kw", [
+    dict(I=100, nA=3, nB=20, nO=7, K=300),      # A is the register-resident operand
+    dict(I=257, nA=20, nB=16, nO=50, K=1000),   # widest register-resident row
+    dict(I=33, nA=9, nB=9, nO=9, K=400),
+    dict(I=64, nA=1, nB=1, nO=1, K=5),
+    dict(I=90, nA=17, nB=40, nO=30, K=700),     # neither operand is narrow: general kernels
+    dict(I=70, nA=5, nB=8, nO=300, K=40),       # most output columns receive nothing
+], ids=lambda kw: "-".join(f"{k}{v}" for k, v in kw.items()))
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_sap_operand_widths(oracle, kw, dtype):
+    """SAP with either operand narrow enough to sit in registers, and with neither; the output
+    index in random order (the plan kernels sort the triplets themselves)."""
+    d = workloads.sap(**kw)
+    r = np.random.default_rng(11)
+    d["indices_output"] = r.permutation(d["indices_output"])
+    d["grad_grad_A"] = r.standard_normal(d["A"].shape)
+    d["grad_grad_B"] = r.standard_normal(d["B"].shape)
+    compare("sap", d, dtype, oracle, second_order=True, what=f"sap {kw}")
+    t = to_dev(d, dtype)
+    import mops_b200 as M
+    want = run_checker(oracle, "sap", d, dtype)
+    for need_a, need_b in ((True, False), (False, True)):
+        gA, gB = M.sparse_accumulation_of_products_vjp(
+            t["grad_output"], t["A"], t["B"], t["C"], t["indices_A"], t["indices_B"],
+            t["indices_output"], compute_grad_A=need_a, compute_grad_B=need_b)
+        assert (gA is not None) == need_a and (gB is not None) == need_b
+        if need_a:
+            assert_parity(gA.cpu().numpy(), want["grad_A"], f"grad_A only {kw}")
+        if need_b:
+            assert_parity(gB.cpu().numpy(), want["grad_B"], f"grad_B only {kw}")
+
+
 def test_single_giant_segment_and_many_empty_rows(oracle):
     d = workloads.opsa(J=5000, K=5, L=6, nO=40)
     d["indices_output"][:] = 17
