@@ -87,7 +87,7 @@ struct HpePlan {
     unsigned char* vjp_rec; // [J*K]  grouped by differentiated factor: C[j], the other K-1 offsets
     int32_t* n_start;       // [N + 1]       first incidence of every factor
     int32_t* split;         // [kWarps + 1]  factor ranges of the block's warps
-    int32_t* cursor;        // [N + 1] scratch
+    int32_t* cursor;        // [plan warps][N + 1] scratch
 };
 
 // Loads rows [i0, i0+32) of a row-major [I][N] matrix into tile[n*kPad + row].
@@ -114,8 +114,8 @@ __device__ __forceinline__ void load_tile_transposed(T* tile, const T* __restric
     }
 }
 
-// Builds the packed tables. One block; the grouping is a stable counting sort done by warp 0
-// (equal factors keep ascending (j,k), so the sums are reproducible).
+// Builds the packed tables. One block; the grouping is a stable counting sort (equal factors
+// keep ascending (j,k), so the sums are reproducible).
 template <typename T>
 __global__ void __launch_bounds__(kPlanThreads)
 hpe_plan(HpePlan plan, const T* __restrict__ C, const int32_t* __restrict__ P, int J, int K,
@@ -139,83 +139,103 @@ hpe_plan(HpePlan plan, const T* __restrict__ C, const int32_t* __restrict__ P, i
         }
     }
     if (!want_vjp || M == 0) return;
-    if (warp == 0) {
-        for (int b = lane; b <= N; b += 32) plan.cursor[b] = 0;
-        __syncwarp();
-        for (int x = lane; x < M; x += 32) {
-            int32_t p = P[x];
-            clamp_index(p, N);
-            atomicAdd(&plan.cursor[p], 1);
+    // Stable counting sort of the J*K incidences by factor. Every warp takes a contiguous
+    // chunk of the incidences; per-(warp, factor) counts turn into each warp's own write
+    // cursors, so equal factors keep ascending (j, k) across and within the chunks.
+    constexpr int kPlanWarps = kPlanThreads / 32;
+    const int stride = N + 1;
+    int32_t* cnt = plan.cursor; // [kPlanWarps][N + 1]
+    const int chunk = ((M + kPlanWarps - 1) / kPlanWarps + 31) / 32 * 32;
+    const int x_lo = min(warp * chunk, M), x_hi = min(x_lo + chunk, M);
+    for (int i = tid; i < kPlanWarps * stride; i += kPlanThreads) cnt[i] = 0;
+    __syncthreads();
+    for (int x = x_lo + lane; x < x_hi; x += 32) {
+        int32_t p = P[x];
+        clamp_index(p, N);
+        atomicAdd(&cnt[warp * stride + p], 1);
+    }
+    __syncthreads();
+    for (int b = tid; b < N; b += kPlanThreads) { // counts -> offsets of each warp inside factor b
+        int run = 0;
+        for (int w = 0; w < kPlanWarps; w++) {
+            const int v = cnt[w * stride + b];
+            cnt[w * stride + b] = run;
+            run += v;
         }
-        __syncwarp();
+        plan.n_start[b] = run; // total, scanned below
+    }
+    __syncthreads();
+    if (warp == 0) {
         int run = 0;
         for (int b0 = 0; b0 <= N; b0 += 32) {
             const int b = b0 + lane;
-            const int v = b < N ? plan.cursor[b] : 0;
+            const int v = b < N ? plan.n_start[b] : 0;
             int incl = v;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
                 const int t = __shfl_up_sync(kFullMask, incl, o);
                 if (lane >= o) incl += t;
             }
-            if (b <= N) {
-                plan.n_start[b] = run + incl - v;
-                plan.cursor[b] = run + incl - v;
-            }
+            if (b <= N) plan.n_start[b] = run + incl - v;
             run += __shfl_sync(kFullMask, incl, 31);
         }
-        __syncwarp();
-        for (int x0 = 0; x0 < M; x0 += 32) {
-            const int x = x0 + lane;
-            const bool live = x < M;
-            int32_t key = -1 - lane;
-            if (live) {
-                key = P[x];
-                clamp_index(key, N);
-            }
-            const unsigned same = __match_any_sync(kFullMask, key);
-            const int rank = __popc(same & ((1u << lane) - 1));
-            const int leader = __ffs(same) - 1;
-            int base = 0;
-            if (live && lane == leader) {
-                base = plan.cursor[key];
-                plan.cursor[key] = base + __popc(same);
-            }
-            base = __shfl_sync(kFullMask, base, leader);
-            if (live) {
-                const int pos = base + rank, j = x / K, k = x - j * K;
-                unsigned char* rec = plan.vjp_rec + static_cast<size_t>(pos) * vjp_bytes;
-                write_record<T>(rec, vjp_bytes, C[j]);
-                int q = 0;
-                for (int l = 0; l < K; l++) {
-                    if (l == k) continue;
-                    int32_t p = P[j * K + l];
-                    clamp_index(p, N);
-                    write_offset<T>(rec, q++, p * kPad);
-                }
-            }
-            __syncwarp();
+    }
+    __syncthreads();
+    for (int i = tid; i < kPlanWarps * N; i += kPlanThreads) {
+        const int w = i / N, b = i - w * N;
+        cnt[w * stride + b] += plan.n_start[b];
+    }
+    __syncthreads();
+    int32_t* cursor = cnt + warp * stride;
+    for (int x0 = x_lo; x0 < x_hi; x0 += 32) {
+        const int x = x0 + lane;
+        const bool live = x < x_hi;
+        int32_t key = -1 - lane;
+        if (live) {
+            key = P[x];
+            clamp_index(key, N);
         }
-        // Factor ranges of the four warps, balanced by incidence count.
-        __syncwarp();
-        if (lane <= kWarps) {
-            int n = 0;
-            if (lane == kWarps) {
-                n = N;
-            } else if (lane > 0) {
-                const int target = static_cast<int>(static_cast<int64_t>(M) * lane / kWarps);
-                int lo = 0, hi = N; // first n with n_start[n] >= target
-                while (lo < hi) {
-                    const int mid = (lo + hi) / 2;
-                    if (plan.n_start[mid] < target)
-                        lo = mid + 1;
-                    else
-                        hi = mid;
-                }
-                n = lo;
-            }
-            plan.split[lane] = n;
+        const unsigned same = __match_any_sync(kFullMask, key);
+        const int rank = __popc(same & ((1u << lane) - 1));
+        const int leader = __ffs(same) - 1;
+        int base = 0;
+        if (live && lane == leader) {
+            base = cursor[key];
+            cursor[key] = base + __popc(same);
         }
+        base = __shfl_sync(kFullMask, base, leader);
+        if (live) {
+            const int pos = base + rank, j = x / K, k = x - j * K;
+            unsigned char* rec = plan.vjp_rec + static_cast<size_t>(pos) * vjp_bytes;
+            write_record<T>(rec, vjp_bytes, C[j]);
+            int q = 0;
+            for (int l = 0; l < K; l++) {
+                if (l == k) continue;
+                int32_t p = P[j * K + l];
+                clamp_index(p, N);
+                write_offset<T>(rec, q++, p * kPad);
+            }
+        }
+        __syncwarp();
+    }
+    // Factor ranges of the row kernel's four warps, balanced by incidence count.
+    if (warp == 0 && lane <= kWarps) {
+        int n = 0;
+        if (lane == kWarps) {
+            n = N;
+        } else if (lane > 0) {
+            const int target = static_cast<int>(static_cast<int64_t>(M) * lane / kWarps);
+            int lo = 0, hi = N; // first n with n_start[n] >= target
+            while (lo < hi) {
+                const int mid = (lo + hi) / 2;
+                if (plan.n_start[mid] < target)
+                    lo = mid + 1;
+                else
+                    hi = mid;
+            }
+            n = lo;
+        }
+        plan.split[lane] = n;
     }
 }
 
@@ -445,8 +465,9 @@ HpePlan make_plan(const Call& call, void** scratch, const T* C, const int32_t* P
     const size_t b_fwd = want_fwd ? up(static_cast<size_t>(J) * record_bytes(sizeof(T), K)) : 0;
     const size_t b_vjp = want_vjp ? up(M * record_bytes(sizeof(T), K - 1)) : 0;
     const size_t b_n = up((static_cast<size_t>(N) + 1) * sizeof(int32_t));
+    const size_t b_cur = up((kPlanThreads / 32) * (static_cast<size_t>(N) + 1) * sizeof(int32_t));
     unsigned char* p =
-        static_cast<unsigned char*>(scratch_alloc(call, b_fwd + b_vjp + 2 * b_n + 256));
+        static_cast<unsigned char*>(scratch_alloc(call, b_fwd + b_vjp + b_n + b_cur + 256));
     *scratch = p;
     HpePlan plan;
     plan.fwd_rec = p;
@@ -456,7 +477,7 @@ HpePlan make_plan(const Call& call, void** scratch, const T* C, const int32_t* P
     plan.n_start = reinterpret_cast<int32_t*>(p);
     p += b_n;
     plan.cursor = reinterpret_cast<int32_t*>(p);
-    p += b_n;
+    p += b_cur;
     plan.split = reinterpret_cast<int32_t*>(p);
     hpe_plan<T><<<1, kPlanThreads, 0, call.stream>>>(plan, C, P, static_cast<int>(J), K, N,
                                                      want_fwd, want_vjp, call.status);
