@@ -826,6 +826,13 @@ opsa_vjp_mma(S* __restrict__ gA, S* __restrict__ gB, S* __restrict__ gW,
     constexpr int KSL = 2 * LT8;      // k-steps over L
     constexpr int NTL = LT8;          // 8-wide tiles over L
     constexpr int KSK = KT;           // k-steps over K
+    // Eight-entry tiles loaded per iteration (and again one iteration ahead): narrower scalars
+    // need more tiles for the same number of bytes in flight.
+    constexpr int TILES = sizeof(S) == 8 ? 1 : (WEIGHTED ? 2 : 4);
+    struct RawTile {
+        S a[KSK], b[KSL]; // b already multiplied by W[PW[e]] when there are weights
+        int32_t wrow;
+    };
     if (saw_unsorted(st)) return;     // the entry-per-lane kernel of the same call does the work
     const int warps = blockDim.x >> 5, lane = threadIdx.x & 31;
     const int warp = __shfl_sync(kFullMask, threadIdx.x >> 5, 0); // uniform for the compiler
@@ -857,98 +864,111 @@ opsa_vjp_mma(S* __restrict__ gA, S* __restrict__ gB, S* __restrict__ gW,
                 gb_k[nt][ks] = (want_b && k < K && l < L) ? static_cast<T>(__ldg(g + k * L + l)) : T(0);
             }
 
-        // A-operand fragments of the tile that starts at e0: entry e0 + qr, column 4 ks + qc
-        auto load_tile = [&](int64_t e0, T (&af)[KSK], T (&bf)[KSL], int32_t& wrow) {
+        // A-operand fragments of the tile that starts at e0, as loaded: entry e0 + qr, column
+        // 4 ks + qc of A and B (times W[PW[e]]).
+        auto load_tile = [&](int64_t e0, RawTile& t) {
             const int64_t e = e0 + qr;
             const bool valid = e < hi;
-            wrow = 0;
+            t.wrow = 0;
             if (WEIGHTED && valid) {
-                wrow = __ldg(PW + e);
-                if (clamp_index(wrow, static_cast<int32_t>(nW))) report_bad_index(st, 1);
+                t.wrow = __ldg(PW + e);
+                if (clamp_index(t.wrow, static_cast<int32_t>(nW))) report_bad_index(st, 1);
             }
 #pragma unroll
             for (int ks = 0; ks < KSK; ks++) {
                 const int k = 4 * ks + qc;
-                af[ks] = (want_b && valid && k < K) ? static_cast<T>(__ldg(A + e * K + k)) : T(0);
+                t.a[ks] = (want_b && valid && k < K) ? __ldg(A + e * K + k) : S(0);
             }
 #pragma unroll
             for (int ks = 0; ks < KSL; ks++) {
                 const int l = 4 * ks + qc;
-                T v = (want_a && valid && l < L) ? static_cast<T>(__ldg(B + e * L + l)) : T(0);
-                if (WEIGHTED && want_a && valid && l < L)
-                    v *= static_cast<T>(__ldg(W + static_cast<int64_t>(wrow) * L + l));
-                bf[ks] = v;
+                const bool in = want_a && valid && l < L;
+                S v = in ? __ldg(B + e * L + l) : S(0);
+                if (WEIGHTED && in) v *= __ldg(W + static_cast<int64_t>(t.wrow) * L + l);
+                t.b[ks] = v;
             }
         };
 
-        T af[KSK], bf[KSL], af_n[KSK], bf_n[KSL];
-        int32_t wrow, wrow_n = 0;
-        load_tile(lo, af, bf, wrow);
-        for (int64_t e0 = lo; e0 < hi; e0 += 8) {
-            if (e0 + 8 < hi) load_tile(e0 + 8, af_n, bf_n, wrow_n);
-            const int64_t e = e0 + qr;
-            const bool valid = e < hi;
-            if (want_a) {
+        RawTile cur[TILES], nxt[TILES];
 #pragma unroll
-                for (int nt = 0; nt < NTK; nt++) {
-                    T c[2];
-                    dmma0(c, bf[0], ga_k[nt][0]);
+        for (int t = 0; t < TILES; t++) load_tile(lo + 8 * t, cur[t]);
+        for (int64_t e_it = lo; e_it < hi; e_it += 8 * TILES) {
+            if (e_it + 8 * TILES < hi) {
 #pragma unroll
-                    for (int ks = 1; ks < KSL; ks++) dmma(c, bf[ks], ga_k[nt][ks]);
-                    const int k = 8 * nt + 2 * qc;
-                    S* dst = gA + e * K + k;
-                    if (valid && k < K) dst[0] = static_cast<S>(c[0]);
-                    if (valid && k + 1 < K) dst[1] = static_cast<S>(c[1]);
-                }
-            }
-            if (want_b) {
-#pragma unroll
-                for (int nt = 0; nt < NTL; nt++) {
-                    T c[2];
-                    dmma0(c, af[0], gb_k[nt][0]);
-#pragma unroll
-                    for (int ks = 1; ks < KSK; ks++) dmma(c, af[ks], gb_k[nt][ks]);
-                    const int l = 8 * nt + 2 * qc;
-                    if (!valid || l >= L) continue;
-                    const bool two = l + 1 < L;
-                    if (WEIGHTED) {
-                        const S* wp = W + static_cast<int64_t>(wrow) * L + l;
-                        const S* bp = B + e * L + l;
-                        T w0, w1 = T(0), b0, b1 = T(0);
-                        if (pair_ok) {
-                            const S2 w2 = *reinterpret_cast<const S2*>(wp);
-                            const S2 b2 = *reinterpret_cast<const S2*>(bp);
-                            w0 = w2.x, w1 = w2.y, b0 = b2.x, b1 = b2.y;
-                        } else {
-                            w0 = wp[0], b0 = bp[0];
-                            if (two) w1 = wp[1], b1 = bp[1];
-                        }
-                        if (gW != nullptr) {
-                            S* gw = gW + static_cast<int64_t>(wrow) * L + l;
-                            red_add(gw, static_cast<S>(c[0] * b0));
-                            if (two) red_add(gw + 1, static_cast<S>(c[1] * b1));
-                        }
-                        c[0] *= w0;
-                        c[1] *= w1;
-                    }
-                    if (gB != nullptr) {
-                        S* dst = gB + e * L + l;
-                        if (pair_ok) {
-                            S2 v2;
-                            v2.x = static_cast<S>(c[0]), v2.y = static_cast<S>(c[1]);
-                            *reinterpret_cast<S2*>(dst) = v2;
-                        } else {
-                            dst[0] = static_cast<S>(c[0]);
-                            if (two) dst[1] = static_cast<S>(c[1]);
-                        }
-                    }
-                }
+                for (int t = 0; t < TILES; t++) load_tile(e_it + 8 * TILES + 8 * t, nxt[t]);
             }
 #pragma unroll
-            for (int ks = 0; ks < KSK; ks++) af[ks] = af_n[ks];
+            for (int t = 0; t < TILES; t++) {
+                const int64_t e0 = e_it + 8 * t;
+                if (e0 >= hi) break;
+                const int64_t e = e0 + qr;
+                const bool valid = e < hi;
+                const int32_t wrow = cur[t].wrow;
+                if (want_a) {
+                    T bf[KSL];
 #pragma unroll
-            for (int ks = 0; ks < KSL; ks++) bf[ks] = bf_n[ks];
-            wrow = wrow_n;
+                    for (int ks = 0; ks < KSL; ks++) bf[ks] = static_cast<T>(cur[t].b[ks]);
+#pragma unroll
+                    for (int nt = 0; nt < NTK; nt++) {
+                        T c[2];
+                        dmma0(c, bf[0], ga_k[nt][0]);
+#pragma unroll
+                        for (int ks = 1; ks < KSL; ks++) dmma(c, bf[ks], ga_k[nt][ks]);
+                        const int k = 8 * nt + 2 * qc;
+                        S* dst = gA + e * K + k;
+                        if (valid && k < K) dst[0] = static_cast<S>(c[0]);
+                        if (valid && k + 1 < K) dst[1] = static_cast<S>(c[1]);
+                    }
+                }
+                if (want_b) {
+                    T af[KSK];
+#pragma unroll
+                    for (int ks = 0; ks < KSK; ks++) af[ks] = static_cast<T>(cur[t].a[ks]);
+#pragma unroll
+                    for (int nt = 0; nt < NTL; nt++) {
+                        T c[2];
+                        dmma0(c, af[0], gb_k[nt][0]);
+#pragma unroll
+                        for (int ks = 1; ks < KSK; ks++) dmma(c, af[ks], gb_k[nt][ks]);
+                        const int l = 8 * nt + 2 * qc;
+                        if (!valid || l >= L) continue;
+                        const bool two = l + 1 < L;
+                        if (WEIGHTED) {
+                            const S* wp = W + static_cast<int64_t>(wrow) * L + l;
+                            const S* bp = B + e * L + l;
+                            T w0, w1 = T(0), b0, b1 = T(0);
+                            if (pair_ok) {
+                                const S2 w2 = *reinterpret_cast<const S2*>(wp);
+                                const S2 b2 = *reinterpret_cast<const S2*>(bp);
+                                w0 = w2.x, w1 = w2.y, b0 = b2.x, b1 = b2.y;
+                            } else {
+                                w0 = wp[0], b0 = bp[0];
+                                if (two) w1 = wp[1], b1 = bp[1];
+                            }
+                            if (gW != nullptr) {
+                                S* gw = gW + static_cast<int64_t>(wrow) * L + l;
+                                red_add(gw, static_cast<S>(c[0] * b0));
+                                if (two) red_add(gw + 1, static_cast<S>(c[1] * b1));
+                            }
+                            c[0] *= w0;
+                            c[1] *= w1;
+                        }
+                        if (gB != nullptr) {
+                            S* dst = gB + e * L + l;
+                            if (pair_ok) {
+                                S2 v2;
+                                v2.x = static_cast<S>(c[0]), v2.y = static_cast<S>(c[1]);
+                                *reinterpret_cast<S2*>(dst) = v2;
+                            } else {
+                                dst[0] = static_cast<S>(c[0]);
+                                if (two) dst[1] = static_cast<S>(c[1]);
+                            }
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int t = 0; t < TILES; t++) cur[t] = nxt[t];
         }
     }
 }
@@ -1025,7 +1045,7 @@ void backward(const Call& call, T* gA, T* gB, T* gW, const T* gO, const T* A, co
 
     VjpPlan plan;
     plan.only_if_unsorted = false;
-    if constexpr (sizeof(T) == 8) { // (measured slower than the kernels below for f32)
+    if constexpr (sizeof(T) == 8) { // (f32 widened to f64 here measured slower: 2.4 against 2.06 ms)
         if (K <= 16 && L <= 32) {
             // Sorted scatter index (checked on the device): one warp per output row on the
             // tensor-core path; otherwise the entry-per-lane kernels below do the work.

@@ -738,10 +738,14 @@ inline int small_width(int nA, int nB) {
 }
 
 // Rows per block for tiles of `cols` columns plus the small plan's tables: the block size that
-// puts the most warps on an SM (the tables are per block, the tiles per row); 0 if 32 rows do
-// not fit.
+// puts the most warps on an SM within its shared memory and registers (the tables are per
+// block, the tiles per row); 0 if 32 rows do not fit.
 template <typename T>
-int rows_small(const Call& call, int cols, int64_t K, int nbins, size_t* smem) {
+int rows_small(const Call& call, const void* kernel, int cols, int64_t K, int nbins,
+               size_t* smem) {
+    cudaFuncAttributes attr{};
+    MOPS_CUDA_OK(cudaFuncGetAttributes(&attr, kernel));
+    const int regs = std::max(attr.numRegs, 1);
     const size_t limit = static_cast<size_t>(max_optin_smem(call.device));
     const size_t per_sm = 228 * 1024, reserved = 1024;
     const size_t tables = up16(static_cast<size_t>(K + kSmallPad) * sizeof(Entry<T>) +
@@ -749,8 +753,9 @@ int rows_small(const Call& call, int cols, int64_t K, int nbins, size_t* smem) {
     int best_r = 0, best_warps = 0;
     for (int R : {32, 64, 96, 128, 160, 192, 256, 320, 384, 512}) {
         const size_t total = up16(static_cast<size_t>(cols) * (R + 1) * sizeof(T)) + tables;
-        if (total > limit) break;
-        const int blocks = static_cast<int>(std::min<size_t>(per_sm / (total + reserved), 32));
+        if (total > limit || R * regs > 65536) break;
+        const int by_smem = static_cast<int>(std::min<size_t>(per_sm / (total + reserved), 32));
+        const int blocks = std::min(by_smem, 65536 / (regs * R));
         const int warps = std::min(blocks * (R / 32), 64);
         if (warps > best_warps) {
             best_warps = warps;
@@ -793,7 +798,10 @@ bool forward_small(const Call& call, T* O, const T* A, const T* B, const T* C, c
     const int32_t *PS = b_small ? PB : PA, *PT = b_small ? PA : PB;
     const int nS = b_small ? nB : nA, nT = b_small ? nA : nB;
     size_t smem = 0;
-    const int R = rows_small<T>(call, nT, K, nO * NS, &smem);
+    const void* kernel = NS == 4   ? reinterpret_cast<const void*>(sap_fwd_small<T, 4>)
+                         : NS == 8 ? reinterpret_cast<const void*>(sap_fwd_small<T, 8>)
+                                   : reinterpret_cast<const void*>(sap_fwd_small<T, 16>);
+    const int R = rows_small<T>(call, kernel, nT, K, nO * NS, &smem);
     if (R == 0) return false;
     void* scratch = nullptr;
     SmallPlan<T> plan = make_small_plan<T>(call, &scratch, C, PS, PT, PO, K, nS, nT, nO, NS, R + 1,
@@ -825,7 +833,10 @@ bool backward_small(const Call& call, T* gA, T* gB, const T* gO, const T* A, con
     const int nS = b_small ? nB : nA, nT = b_small ? nA : nB;
     if (static_cast<int64_t>(nT) * NS > (1 << 20)) return false;
     size_t smem = 0;
-    const int R = rows_small<T>(call, nT + nO, K, nT * NS, &smem);
+    const void* kernel = NS == 4   ? reinterpret_cast<const void*>(sap_vjp_small<T, 4>)
+                         : NS == 8 ? reinterpret_cast<const void*>(sap_vjp_small<T, 8>)
+                                   : reinterpret_cast<const void*>(sap_vjp_small<T, 16>);
+    const int R = rows_small<T>(call, kernel, nT + nO, K, nT * NS, &smem);
     if (R == 0) return false;
     void* scratch = nullptr;
     SmallPlan<T> plan = make_small_plan<T>(call, &scratch, C, PS, PT, PO, K, nS, nT, nO, NS, R + 1,
