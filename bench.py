@@ -65,12 +65,12 @@ LAUNCHES = {"hpe": (2, 2), "sap": (2, 2), "opsa": (2, 1), "opsaw": (2, 1), "sasa
 # operands and results of these kernels scale with the batch. The summaries under profiles/
 # hold the captured figures.
 MEASURED_TRAFFIC = {
-    ("hpe", "fwd"): 8 * 108.4e6, ("hpe", "vjp"): 8 * 181.0e6,
-    ("sap", "fwd"): 8 * 346.0e6, ("sap", "vjp"): 8 * 405.0e6,
-    ("opsa", "fwd"): 8 * 614.4e6, ("opsa", "vjp"): 8 * 1138.0e6,
-    ("opsa_f32", "fwd"): 8 * 304.6e6, ("opsa_f32", "vjp"): 8 * 554.9e6,
-    ("opsaw", "fwd"): 8 * 211.3e6, ("opsaw", "vjp"): 8 * 376.8e6,
-    ("sasaw", "fwd"): 8 * 207.4e6, ("sasaw", "vjp"): 8 * 403.2e6,
+    ("hpe", "fwd"): 8 * 108.6e6, ("hpe", "vjp"): 8 * 195.3e6,
+    ("sap", "fwd"): 8 * 432.9e6, ("sap", "vjp"): 8 * 403.3e6,
+    ("opsa", "fwd"): 8 * 614.0e6, ("opsa", "vjp"): 8 * 1138.3e6,
+    ("opsa_f32", "fwd"): 8 * 304.7e6, ("opsa_f32", "vjp"): 8 * 554.5e6,
+    ("opsaw", "fwd"): 8 * 212.0e6, ("opsaw", "vjp"): 8 * 372.9e6,
+    ("sasaw", "fwd"): 8 * 209.2e6, ("sasaw", "vjp"): 8 * 409.8e6,
 }
 
 
