@@ -272,6 +272,16 @@ def main():
     ap.add_argument("--scale", type=int, default=1,
                     help="divide every batch dimension by this (small cases for profiling)")
     args = ap.parse_args()
+    # stdout carries exactly one JSON line: everything libraries print there (NCCL's version
+    # banner, for one) is sent to stderr, and the line is written to the original descriptor.
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
+
+    def emit(line):
+        sys.stdout.flush()
+        os.write(json_fd, (json.dumps(line) + "\n").encode())
+
     global SCALE
     SCALE = max(1, args.scale)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -299,7 +309,7 @@ def main():
                 "e2e": {"value": r["value"], "unit": "GB/s", "h2d_bytes_per_step": 0,
                         "d2h_bytes_per_step": 0},
                 "per_op": r["per_op"], "gpu_launches": 0}
-        print(json.dumps(line))
+        emit(line)
         return 0
 
     import torch
@@ -478,7 +488,7 @@ def main():
         r = cpu_run(names, 1, 1)
         line["cpu_baseline"] = {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")}
         line["cpu_baseline"]["per_op"] = r["per_op"]
-    print(json.dumps(line))
+    emit(line)
     if world > 1:
         dist.destroy_process_group()
     return 0
