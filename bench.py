@@ -269,6 +269,9 @@ def main():
     ap.add_argument("--workload", default="all", choices=["all"] + list(CASES))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-spread", action="store_true",
+                    help="skip the per-call median / p10 / p90 measurement (also skipped with "
+                         "--no-e2e)")
     ap.add_argument("--scale", type=int, default=1,
                     help="divide every batch dimension by this (small cases for profiling)")
     args = ap.parse_args()
@@ -388,6 +391,23 @@ def main():
     step_bytes = sum(sum(nbytes[n]) for n in names)
     value = step_bytes * world * args.steps / (t_ms / 1e3) / 1e9
 
+    # ---- spread of every call: the same calls again, each one between its own pair of events
+    # (outside the timed step; rank 0's view)
+    spread = {}
+    if not (args.no_spread or args.no_e2e):  # quick / profiling runs skip it with the e2e leg
+        reps = 20
+        for n in names:
+            ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(reps)]
+            for r in range(reps):
+                run_case(n, devd[n], ev[r])
+            torch.cuda.synchronize()
+            f = sorted(e[0].elapsed_time(e[1]) for e in ev)
+            v = sorted(e[1].elapsed_time(e[2]) for e in ev)
+            q = lambda xs, p: xs[min(len(xs) - 1, int(p * len(xs)))]
+            spread[n] = {"reps": reps, "fwd_ms_median": q(f, 0.5), "fwd_ms_p10": q(f, 0.1),
+                         "fwd_ms_p90": q(f, 0.9), "vjp_ms_median": q(v, 0.5),
+                         "vjp_ms_p10": q(v, 0.1), "vjp_ms_p90": q(v, 0.9)}
+
     # ---- end to end: every step copies each case's inputs from pinned host memory to the
     # device, calls forward and VJP through the public API and copies all results back into
     # pinned host buffers. Three CUDA streams (copy in, compute, copy out) chained by events:
@@ -466,7 +486,7 @@ def main():
                      "vjp_GBps": bv / v_ms / 1e6, "fwd_frac_of_hbm": bf / f_ms / 1e6 / peak,
                      "vjp_frac_of_hbm": bv / v_ms / 1e6 / peak,
                      "fwd_items_per_s": items / f_ms * 1e3, "vjp_items_per_s": items / v_ms * 1e3,
-                     "fwd_bytes": bf, "vjp_bytes": bv,
+                     "fwd_bytes": bf, "vjp_bytes": bv, **spread.get(n, {}),
                      "fwd_traffic": traffic(n, "fwd"), "vjp_traffic": traffic(n, "vjp")}
         for lvl, ms, b in (("fwd", f_ms, bf), ("vjp", v_ms, bv)):
             if dominant is None or ms > dominant[2]:
