@@ -1167,13 +1167,79 @@ void mops::cuda::outer_product_scatter_add_vjp(Tensor<scalar_t, 2> grad_A,
     end_call(call, op.c_str(), kOpsaIndexNames, 1);
 }
 
+// Second order, by composition of the first-order kernels (mops/src/opsa/cpu.tpp:114-246; the
+// reference CUDA build throws "Not implemented", mops/src/opsa/opsa.cu:305-318):
+//   ggO  = opsa(ggA, B) + opsa(A, ggB)
+//   gA2  = grad_A of opsa_vjp(gO; ., B := ggB),   gB2 = grad_B of opsa_vjp(gO; A := ggA, .)
+// A missing grad_grad input makes its terms vanish; a missing output is skipped.
+template <typename T>
+static __global__ void add_into(T* __restrict__ dst, const T* __restrict__ src, int64_t n) {
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+        dst[i] += src[i];
+}
+
 template <typename scalar_t>
 void mops::cuda::outer_product_scatter_add_vjp_vjp(
-    Tensor<scalar_t, 3>, Tensor<scalar_t, 2>, Tensor<scalar_t, 2>, Tensor<scalar_t, 2>,
-    Tensor<scalar_t, 2>, Tensor<scalar_t, 3>, Tensor<scalar_t, 2>, Tensor<scalar_t, 2>,
-    Tensor<int32_t, 1>) {
-    // Same behaviour as the reference CUDA build (mops/src/opsa/opsa.cu:305-318).
-    throw std::runtime_error("Not implemented");
+    Tensor<scalar_t, 3> grad_grad_output, Tensor<scalar_t, 2> grad_A_2,
+    Tensor<scalar_t, 2> grad_B_2, Tensor<scalar_t, 2> grad_grad_A,
+    Tensor<scalar_t, 2> grad_grad_B, Tensor<scalar_t, 3> grad_output, Tensor<scalar_t, 2> A,
+    Tensor<scalar_t, 2> B, Tensor<int32_t, 1> indices_output) {
+    const std::string op = "cuda_outer_product_scatter_add_vjp_vjp";
+    grad_like(grad_grad_output, "grad_grad_output", grad_output, "grad_output", op);
+    grad_like(grad_A_2, "grad_A_2", A, "A", op);
+    grad_like(grad_B_2, "grad_B_2", B, "B", op);
+    grad_like(grad_grad_A, "grad_grad_A", A, "A", op);
+    grad_like(grad_grad_B, "grad_grad_B", B, "B", op);
+    same_size(A, "A", 0, B, "B", 0, op);
+    same_size(A, "A", 1, grad_output, "grad_output", 1, op);
+    same_size(B, "B", 1, grad_output, "grad_output", 2, op);
+    same_size(A, "A", 0, indices_output, "indices_output", 0, op);
+    fits_int32(grad_output.shape[0], "grad_output.shape[0]", op);
+    fits_int32(A.shape[1], "A.shape[1]", op);
+    fits_int32(B.shape[1], "B.shape[1]", op);
+    if (grad_grad_output.data == nullptr && grad_A_2.data == nullptr && grad_B_2.data == nullptr)
+        return;
+    const int64_t J = static_cast<int64_t>(A.shape[0]);
+    const int K = static_cast<int>(A.shape[1]), L = static_cast<int>(B.shape[1]);
+    const int64_t nO = static_cast<int64_t>(grad_output.shape[0]);
+    const int64_t out_size = nO * K * L;
+    const scalar_t *ggA = grad_grad_A.data, *ggB = grad_grad_B.data;
+    const int32_t* P = indices_output.data;
+    Call call = begin_call();
+    if (grad_grad_output.data != nullptr && out_size > 0) {
+        scalar_t* ggO = grad_grad_output.data;
+        if (ggA != nullptr && ggB != nullptr) {
+            forward<scalar_t, false>(call, ggO, ggA, B.data, nullptr, nullptr, P, J, K, L, nO);
+            scalar_t* tmp =
+                static_cast<scalar_t*>(scratch_alloc(call, out_size * sizeof(scalar_t)));
+            forward<scalar_t, false>(call, tmp, A.data, ggB, nullptr, nullptr, P, J, K, L, nO);
+            add_into<scalar_t><<<sm_count(call.device) * 8, 256, 0, call.stream>>>(ggO, tmp, out_size);
+            MOPS_CUDA_OK(cudaGetLastError());
+            scratch_free(call, tmp);
+        } else if (ggA != nullptr) {
+            forward<scalar_t, false>(call, ggO, ggA, B.data, nullptr, nullptr, P, J, K, L, nO);
+        } else if (ggB != nullptr) {
+            forward<scalar_t, false>(call, ggO, A.data, ggB, nullptr, nullptr, P, J, K, L, nO);
+        } else {
+            MOPS_CUDA_OK(cudaMemsetAsync(ggO, 0, out_size * sizeof(scalar_t), call.stream));
+        }
+    }
+    if (grad_A_2.data != nullptr && J * K > 0) {
+        if (ggB != nullptr)
+            backward<scalar_t, false>(call, grad_A_2.data, nullptr, nullptr, grad_output.data,
+                                      A.data, ggB, nullptr, nullptr, P, J, K, L, nO);
+        else
+            MOPS_CUDA_OK(cudaMemsetAsync(grad_A_2.data, 0, J * K * sizeof(scalar_t), call.stream));
+    }
+    if (grad_B_2.data != nullptr && J * L > 0) {
+        if (ggA != nullptr)
+            backward<scalar_t, false>(call, nullptr, grad_B_2.data, nullptr, grad_output.data, ggA,
+                                      B.data, nullptr, nullptr, P, J, K, L, nO);
+        else
+            MOPS_CUDA_OK(cudaMemsetAsync(grad_B_2.data, 0, J * L * sizeof(scalar_t), call.stream));
+    }
+    end_call(call, op.c_str(), kOpsaIndexNames, 1);
 }
 
 template <typename scalar_t>

@@ -266,7 +266,7 @@ struct Sap : torch::autograd::Function<Sap> {
 
 // =============================================================================== OPSA
 struct OpsaBackward : torch::autograd::Function<OpsaBackward> {
-    static tensor_list forward(AutogradContext*, Tensor grad_output, Tensor A, Tensor B,
+    static tensor_list forward(AutogradContext* ctx, Tensor grad_output, Tensor A, Tensor B,
                                Tensor indices_output) {
         Tensor grad_A = maybe_empty_like(A), grad_B = maybe_empty_like(B);
         on_stream_of(A, [&] {
@@ -277,10 +277,31 @@ struct OpsaBackward : torch::autograd::Function<OpsaBackward> {
                     view<int32_t, 1>(indices_output));
             });
         });
+        if (grad_output.requires_grad() || A.requires_grad() || B.requires_grad()) {
+            ctx->save_for_backward({grad_output, A, B, indices_output});
+        }
         return {defined(grad_A, A), defined(grad_B, A)};
     }
-    static tensor_list backward(AutogradContext*, tensor_list) {
-        no_second_derivative("outer_product_scatter_add");
+    static tensor_list backward(AutogradContext* ctx, tensor_list grads) {
+        auto saved = ctx->get_saved_variables();
+        Tensor grad_output = saved[0], A = saved[1], B = saved[2], indices_output = saved[3];
+        // a placeholder output (gradient not requested in the first backward) has no gradient
+        Tensor gg_A = grads[0].defined() && grads[0].sizes() == A.sizes() ? grads[0].contiguous()
+                                                                           : Tensor();
+        Tensor gg_B = grads[1].defined() && grads[1].sizes() == B.sizes() ? grads[1].contiguous()
+                                                                           : Tensor();
+        Tensor gg_output = maybe_empty_like(grad_output);
+        Tensor grad_A_2 = maybe_empty_like(A), grad_B_2 = maybe_empty_like(B);
+        on_stream_of(A, [&] {
+            AT_DISPATCH_FLOATING_TYPES(A.scalar_type(), "outer_product_scatter_add_vjp_vjp", [&] {
+                mops::cuda::outer_product_scatter_add_vjp_vjp<scalar_t>(
+                    view<scalar_t, 3>(gg_output), view<scalar_t, 2>(grad_A_2),
+                    view<scalar_t, 2>(grad_B_2), view<scalar_t, 2>(gg_A), view<scalar_t, 2>(gg_B),
+                    view<scalar_t, 3>(grad_output), view<scalar_t, 2>(A), view<scalar_t, 2>(B),
+                    view<int32_t, 1>(indices_output));
+            });
+        });
+        return {gg_output, grad_A_2, grad_B_2, Tensor()};
     }
 };
 

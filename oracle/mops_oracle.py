@@ -109,6 +109,17 @@ class Oracle:
                    [A.shape[0], A.shape[1], B.shape[1], gO.shape[0]])
         return gA, gB
 
+    def opsa_vjp_vjp(self, ggA, ggB, gO, A, B, P, need=(True, True, True)):
+        gO, A, B, P = _c(gO), _c(A), _c(B), _i32(P)
+        ggA = None if ggA is None else _c(ggA)
+        ggB = None if ggB is None else _c(ggB)
+        ggO = np.empty_like(gO) if need[0] else None
+        gA2 = np.empty_like(A) if need[1] else None
+        gB2 = np.empty_like(B) if need[2] else None
+        self._call("opsa_vjp_vjp", A.dtype, [ggO, gA2, gB2, ggA, ggB, gO, A, B, P],
+                   [A.shape[0], A.shape[1], B.shape[1], gO.shape[0]])
+        return ggO, gA2, gB2
+
     # ---- OPSAW
     def opsaw(self, A, B, W, PW, PO):
         A, B, W, PW, PO = _c(A), _c(B), _c(W), _i32(PW), _i32(PO)
@@ -264,6 +275,17 @@ class Reference:
         n2 = Null(2, A.dtype)
         self.raw("opsa", "_vjp", A.dtype, gA if need[0] else n2, gB if need[1] else n2, gO, A, B, P)
         return gA, gB
+
+    def opsa_vjp_vjp(self, ggA, ggB, gO, A, B, P, need=(True, True, True)):
+        gO, A, B, P = _c(gO), _c(A), _c(B), _i32(P)
+        ggO = np.empty_like(gO) if need[0] else None
+        gA2 = np.empty_like(A) if need[1] else None
+        gB2 = np.empty_like(B) if need[2] else None
+        n2, n3 = Null(2, A.dtype), Null(3, A.dtype)
+        self.raw("opsa", "_vjp_vjp", A.dtype, ggO if need[0] else n3, gA2 if need[1] else n2,
+                 gB2 if need[2] else n2, n2 if ggA is None else _c(ggA),
+                 n2 if ggB is None else _c(ggB), gO, A, B, P)
+        return ggO, gA2, gB2
 
     def opsaw(self, A, B, W, PW, PO):
         A, B, W, PW, PO = _c(A), _c(B), _c(W), _i32(PW), _i32(PO)

@@ -140,6 +140,34 @@ void FN(oracle_opsa_vjp)(T *gA, T *gB, const T *gO, const T *A, const T *B, cons
     }
 }
 
+/* Second-order terms of OPSA.  mops/src/opsa/cpu.tpp:114-246
+ *   ggO[P_j,k,l] += ggA[j,k] B[j,l] + A[j,k] ggB[j,l]
+ *   gA2[j,k] = sum_l gO[P_j,k,l] ggB[j,l];   gB2[j,l] = sum_k gO[P_j,k,l] ggA[j,k]
+ * ggA / ggB may be NULL (their terms vanish); each output may be NULL (skipped). */
+void FN(oracle_opsa_vjp_vjp)(T *ggO, T *gA2, T *gB2, const T *ggA, const T *ggB, const T *gO,
+                             const T *A, const T *B, const int32_t *P, int64_t J, int64_t K,
+                             int64_t L, int64_t nO) {
+    if (ggO) for (int64_t x = 0; x < nO * K * L; x++) ggO[x] = 0;
+    for (int64_t j = 0; j < J; j++) {
+        const T *g = gO + (int64_t)P[j] * K * L;
+        T *o = ggO ? ggO + (int64_t)P[j] * K * L : 0;
+        if (gA2) for (int64_t k = 0; k < K; k++) gA2[j * K + k] = 0;
+        if (gB2) for (int64_t l = 0; l < L; l++) gB2[j * L + l] = 0;
+        if (ggA)
+            for (int64_t k = 0; k < K; k++)
+                for (int64_t l = 0; l < L; l++) {
+                    if (o) o[k * L + l] += ggA[j * K + k] * B[j * L + l];
+                    if (gB2) gB2[j * L + l] += ggA[j * K + k] * g[k * L + l];
+                }
+        if (ggB)
+            for (int64_t k = 0; k < K; k++)
+                for (int64_t l = 0; l < L; l++) {
+                    if (o) o[k * L + l] += ggB[j * L + l] * A[j * K + k];
+                    if (gA2) gA2[j * K + k] += ggB[j * L + l] * g[k * L + l];
+                }
+    }
+}
+
 /* O[PO[e],k,l] += A[e,k]*B[e,l]*W[PW[e],l]       mops/src/opsaw/cpu.tpp:35-53 */
 void FN(oracle_opsaw)(T *O, const T *A, const T *B, const T *W, const int32_t *PW,
                       const int32_t *PO, int64_t E, int64_t K, int64_t L, int64_t nO) {

@@ -39,6 +39,8 @@ def opsa(empty_row=False):
     d = dict(A=r.rand(100, 10), B=r.rand(100, 5),
              indices_output=r.randint(10, size=100).astype(np.int32), output_size=10)
     d["grad_output"] = r.rand(10, 10, 5)
+    d["grad_grad_A"] = r.rand(100, 10)
+    d["grad_grad_B"] = r.rand(100, 5)
     if empty_row:
         d["indices_output"][d["indices_output"] == 1] = 2
     return d

@@ -44,6 +44,11 @@ def run_library(op, d, second_order=False):
                                                    d["output_size"])
         out["grad_A"], out["grad_B"] = M.outer_product_scatter_add_vjp(
             d["grad_output"], d["A"], d["B"], d["indices_output"])
+        if second_order:
+            out["grad_grad_output"], out["grad_A_2"], out["grad_B_2"] = \
+                M.outer_product_scatter_add_vjp_vjp(
+                    d["grad_grad_A"], d["grad_grad_B"], d["grad_output"], d["A"], d["B"],
+                    d["indices_output"])
     elif op == "opsaw":
         idx = (d["indices_W"], d["indices_output"])
         out["output"] = M.outer_product_scatter_add_with_weights(d["A"], d["B"], d["W"], *idx)
@@ -83,6 +88,10 @@ def run_checker(impl, op, d, dtype, second_order=False):
         out["output"] = impl.opsa(c(d["A"]), c(d["B"]), d["indices_output"], d["output_size"])
         out["grad_A"], out["grad_B"] = impl.opsa_vjp(c(d["grad_output"]), c(d["A"]), c(d["B"]),
                                                      d["indices_output"])
+        if second_order:
+            out["grad_grad_output"], out["grad_A_2"], out["grad_B_2"] = impl.opsa_vjp_vjp(
+                c(d["grad_grad_A"]), c(d["grad_grad_B"]), c(d["grad_output"]), c(d["A"]),
+                c(d["B"]), d["indices_output"])
     elif op == "opsaw":
         idx = (d["indices_W"], d["indices_output"])
         out["output"] = impl.opsaw(c(d["A"]), c(d["B"]), c(d["W"]), *idx)

@@ -49,8 +49,11 @@ def test_host_entry_points_report_that_this_build_is_cuda_only():
 def test_second_order_entry_points_without_a_kernel_say_so():
     z2, z3, i1 = _lib.null_struct(2), _lib.null_struct(3), _lib.null_struct(1)
     with pytest.raises(_lib.MopsError, match="Not implemented"):
-        _lib.call("mops_cuda_outer_product_scatter_add_vjp_vjp_f64",
-                  [z3, z2, z2, z2, z2, z3, z2, z2, i1])
+        _lib.call("mops_cuda_outer_product_scatter_add_with_weights_vjp_vjp_f64",
+                  [z3, z2, z2, z2, z2, z2, z2, z3, z2, z2, z2, i1, i1])
+    # OPSA's second order exists (all outputs skipped: returns without touching the device)
+    _lib.call("mops_cuda_outer_product_scatter_add_vjp_vjp_f64",
+              [z3, z2, z2, z2, z2, z3, z2, z2, i1])
     z1, i2 = _lib.null_struct(1), _lib.null_struct(2)
     with pytest.raises(_lib.MopsError, match="Not implemented"):
         _lib.call("mops_cuda_homogeneous_polynomial_evaluation_vjp_vjp_f32",

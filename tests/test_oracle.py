@@ -35,6 +35,10 @@ def run_all(impl, name, d, dtype=np.float64, second_order=True):
         out["output"] = impl.opsa(c(d["A"]), c(d["B"]), d["indices_output"], d["output_size"])
         out["grad_A"], out["grad_B"] = impl.opsa_vjp(
             c(d["grad_output"]), c(d["A"]), c(d["B"]), d["indices_output"])
+        if second_order and "grad_grad_A" in d:
+            out["grad_grad_output"], out["grad_A_2"], out["grad_B_2"] = impl.opsa_vjp_vjp(
+                c(d["grad_grad_A"]), c(d["grad_grad_B"]), c(d["grad_output"]), c(d["A"]),
+                c(d["B"]), d["indices_output"])
     elif op == "opsaw":
         idx = (d["indices_W"], d["indices_output"])
         out["output"] = impl.opsaw(c(d["A"]), c(d["B"]), c(d["W"]), *idx)

@@ -34,7 +34,7 @@ def test_golden_vectors(name):
     Scatter indices of these fixtures are unsorted: exercises the unsorted-index path."""
     d = fixtures.CASES[name]()
     op = name.split("_")[0]
-    got = run_library(op, to_dev(d, np.float64), second_order=(op == "sap"))
+    got = run_library(op, to_dev(d, np.float64), second_order=(op in ("sap", "opsa")))
     keys = [k for k in GOLD.files if k.startswith(name + "/")]
     assert len(keys) == len(got)
     for k in keys:
@@ -45,7 +45,8 @@ def test_golden_vectors(name):
 @pytest.mark.parametrize("name", sorted(fixtures.CASES))
 def test_fixtures_against_oracle(oracle, name, dtype):
     op = name.split("_")[0]
-    compare(op, fixtures.CASES[name](), dtype, oracle, second_order=(op == "sap"), what=name)
+    compare(op, fixtures.CASES[name](), dtype, oracle, second_order=(op in ("sap", "opsa")),
+            what=name)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -56,9 +57,10 @@ def test_fixtures_sorted_indices(oracle, name, dtype):
     d = fixtures.CASES[name]()
     key = "indices_output_1" if name == "sasaw" else "indices_output"
     order = np.argsort(d[key], kind="stable")
-    per_entry = {"A", "B", key, "indices_W", "indices_W_1"}
+    per_entry = {"A", "B", key, "indices_W", "indices_W_1", "grad_grad_A", "grad_grad_B"}
     d = {k: (v[order] if k in per_entry and isinstance(v, np.ndarray) else v) for k, v in d.items()}
-    compare(name.split("_")[0], d, dtype, oracle, what=name + "/sorted")
+    op = name.split("_")[0]
+    compare(op, d, dtype, oracle, second_order=(op == "opsa"), what=name + "/sorted")
 
 
 # ---------------------------------------------------------------- benchmark shapes

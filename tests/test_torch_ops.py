@@ -1,7 +1,7 @@
 """The torch operators (torch.ops.mops.*): registration and argument checks on CPU; on the
 GPU, forward parity with the CPU oracle, finite-difference gradient checks in f64 (the VJP
 checked against the forward, independent of any reference VJP; the reference does the same
-in python/mops-torch/tests/*.py), second derivatives for SAP, and a TorchScript round trip."""
+in python/mops-torch/tests/*.py), second derivatives for SAP and OPSA, and a TorchScript round trip."""
 import io
 
 import numpy as np
@@ -104,6 +104,8 @@ def test_gradcheck_all_operations():
     idx = torch.sort(ri(10, 60)).values
     idx[idx == 1] = 2  # an empty output row, as in python/mops-torch/tests/opsa.py:28-32
     assert torch.autograd.gradcheck(mt.outer_product_scatter_add, (A, B, idx, 10), fast_mode=True)
+    assert torch.autograd.gradgradcheck(mt.outer_product_scatter_add, (A, B, idx, 10),
+                                        fast_mode=True)
 
     A, B, W = rand(60, 6), rand(60, 5), rand(10, 5)
     # unsorted indices, as in python/mops-torch/tests/opsaw.py:45-47
@@ -123,9 +125,9 @@ def test_gradcheck_all_operations():
 @pytest.mark.gpu
 def test_second_derivatives_without_a_kernel_raise():
     A = torch.rand(20, 6, dtype=torch.float64, device="cuda", requires_grad=True)
-    B = torch.rand(20, 5, dtype=torch.float64, device="cuda", requires_grad=True)
-    idx = torch.sort(torch.randint(4, (20,), dtype=torch.int32, device="cuda")).values
-    out = mt.outer_product_scatter_add(A, B, idx, 4)
+    C = torch.rand(9, dtype=torch.float64, device="cuda")
+    P = torch.randint(6, (9, 3), dtype=torch.int32, device="cuda")
+    out = mt.homogeneous_polynomial_evaluation(A, C, P)
     (gA,) = torch.autograd.grad(out.sum(), A, create_graph=True)
     with pytest.raises(NotImplementedError, match="second derivatives are not supported"):
         gA.sum().backward()
