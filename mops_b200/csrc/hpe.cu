@@ -538,6 +538,84 @@ void launch_vjp(const Call& call, T* gA, const T* gO, const T* A, const T* C, co
 
 const char* const kIndexNames[] = {"indices_A"};
 
+// Forward / VJP of an already checked problem on the call's stream (tile kernels when a
+// 32-row tile of A fits in shared memory, the global-memory kernels otherwise).
+template <typename T>
+void run_forward(const Call& call, T* O, const T* A, const T* C, const int32_t* P, int64_t I,
+                 int N, int64_t J, int K) {
+    const size_t smem = fwd_smem<T, kMaxOrder>(N); // the largest any order needs
+    if (smem <= static_cast<size_t>(max_optin_smem(call.device)) && N <= kMaxTileColumns) {
+#define CALL(KK) launch_fwd<T, KK>(call, O, A, C, P, I, N, J)
+        MOPS_B200_ORDER_SWITCH(K, CALL)
+#undef CALL
+    } else {
+        hpe_fwd_wide<T><<<static_cast<unsigned>(ceil_div(I, 128)), 128, 0, call.stream>>>(
+            O, A, C, P, I, N, J, K, call.status);
+    }
+    MOPS_CUDA_OK(cudaGetLastError());
+}
+
+template <typename T>
+void run_backward(const Call& call, T* gA, const T* gO, const T* A, const T* C, const int32_t* P,
+                  int64_t I, int N, int64_t J, int K) {
+    const size_t smem = vjp_smem<T, kMaxOrder>(N);
+    if (smem <= static_cast<size_t>(max_optin_smem(call.device)) && N <= kMaxTileColumns) {
+#define CALL(KK) launch_vjp<T, KK>(call, gA, gO, A, C, P, I, N, J)
+        MOPS_B200_ORDER_SWITCH(K, CALL)
+#undef CALL
+    } else {
+        hpe_vjp_wide<T><<<static_cast<unsigned>(ceil_div(I, 128)), 128, 0, call.stream>>>(
+            gA, gO, A, C, P, I, N, J, K, call.status);
+    }
+    MOPS_CUDA_OK(cudaGetLastError());
+}
+
+// ---- second order, as a first-order problem on augmented operands
+// With A2 = [A | ggA] (2N columns) and, for every monomial j and position k, the monomial
+// (j, k) whose k-th factor is taken from the ggA half,
+//     Q(A2) = sum_{j,k} C_j ggA[i, P_jk] prod_{l != k} A[i, P_jl],
+// the second-order terms of mops/src/hpe/cpu.tpp:275-539 are
+//     ggO[i] = Q(A2)[i],      gA2[i, n] = gO[i] dQ/dA[i, n]   (the first N columns of Q's VJP).
+template <typename T>
+__global__ void hpe_augment_rows(T* __restrict__ A2, const T* __restrict__ A,
+                                 const T* __restrict__ ggA, int64_t I, int N) {
+    const int64_t total = I * 2 * N;
+    for (int64_t x = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; x < total;
+         x += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t i = x / (2 * N);
+        const int n = static_cast<int>(x - i * 2 * N);
+        A2[x] = n < N ? A[i * N + n] : ggA[i * N + n - N];
+    }
+}
+
+template <typename T>
+__global__ void hpe_augment_table(T* __restrict__ C2, int32_t* __restrict__ P2,
+                                  const T* __restrict__ C, const int32_t* __restrict__ P, int J,
+                                  int K, int N, Status st) {
+    const int total = J * K;
+    for (int x = blockIdx.x * blockDim.x + threadIdx.x; x < total; x += gridDim.x * blockDim.x) {
+        const int j = x / K, k = x - j * K;
+        C2[x] = C[j];
+        for (int l = 0; l < K; l++) {
+            int32_t p = P[j * K + l];
+            if (clamp_index(p, N)) report_bad_index(st, 0);
+            P2[static_cast<int64_t>(x) * K + l] = l == k ? N + p : p;
+        }
+    }
+}
+
+template <typename T>
+__global__ void hpe_take_left_half(T* __restrict__ out, const T* __restrict__ in2, int64_t I,
+                                   int N) {
+    const int64_t total = I * N;
+    for (int64_t x = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; x < total;
+         x += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t i = x / N;
+        out[x] = in2[i * 2 * N + (x - i * N)];
+    }
+}
+
+
 void check_order(size_t K) {
     // Same limit and text as the reference CPU code (mops/src/hpe/cpu.tpp:129); the reference
     // CUDA launcher silently does nothing for larger orders (mops/src/hpe/hpe.cu:183-185).
@@ -576,15 +654,7 @@ void mops::cuda::homogeneous_polynomial_evaluation(Tensor<scalar_t, 1> output,
         return;
     }
     fits_int32(C.shape[0] * std::max<size_t>(indices_A.shape[1], 1) * 16, "the monomial table", op);
-    const size_t smem = fwd_smem<scalar_t, kMaxOrder>(N); // the largest any order needs
-    if (smem <= static_cast<size_t>(max_optin_smem(call.device)) && N <= kMaxTileColumns) {
-#define CALL(KK) launch_fwd<scalar_t, KK>(call, output.data, A.data, C.data, indices_A.data, I, N, J)
-        MOPS_B200_ORDER_SWITCH(K, CALL)
-#undef CALL
-    } else {
-        hpe_fwd_wide<scalar_t><<<static_cast<unsigned>(ceil_div(I, 128)), 128, 0, call.stream>>>(
-            output.data, A.data, C.data, indices_A.data, I, N, J, K, call.status);
-    }
+    run_forward<scalar_t>(call, output.data, A.data, C.data, indices_A.data, I, N, J, K);
     end_call(call, op.c_str(), kIndexNames, 1);
 }
 
@@ -606,27 +676,69 @@ void mops::cuda::homogeneous_polynomial_evaluation_vjp(Tensor<scalar_t, 2> grad_
     if (I == 0 || N == 0) return;
     Call call = begin_call();
     fits_int32(C.shape[0] * std::max<size_t>(indices_A.shape[1], 1) * 16, "the monomial table", op);
-    const size_t smem = vjp_smem<scalar_t, kMaxOrder>(N);
-    if (smem <= static_cast<size_t>(max_optin_smem(call.device)) && N <= kMaxTileColumns) {
-#define CALL(KK)                                                                                   \
-    launch_vjp<scalar_t, KK>(call, grad_A.data, grad_output.data, A.data, C.data, indices_A.data,  \
-                             I, N, J)
-        MOPS_B200_ORDER_SWITCH(K, CALL)
-#undef CALL
-    } else {
-        hpe_vjp_wide<scalar_t><<<static_cast<unsigned>(ceil_div(I, 128)), 128, 0, call.stream>>>(
-            grad_A.data, grad_output.data, A.data, C.data, indices_A.data, I, N, J, K,
-            call.status);
-    }
+    run_backward<scalar_t>(call, grad_A.data, grad_output.data, A.data, C.data, indices_A.data, I,
+                           N, J, K);
     end_call(call, op.c_str(), kIndexNames, 1);
 }
 
 template <typename scalar_t>
 void mops::cuda::homogeneous_polynomial_evaluation_vjp_vjp(
-    Tensor<scalar_t, 1>, Tensor<scalar_t, 2>, Tensor<scalar_t, 2>, Tensor<scalar_t, 1>,
-    Tensor<scalar_t, 2>, Tensor<scalar_t, 1>, Tensor<int32_t, 2>) {
-    // Same behaviour as the reference CUDA build (mops/src/hpe/hpe.cu:402-413).
-    throw std::runtime_error("Not implemented");
+    Tensor<scalar_t, 1> grad_grad_output, Tensor<scalar_t, 2> grad_A_2,
+    Tensor<scalar_t, 2> grad_grad_A, Tensor<scalar_t, 1> grad_output, Tensor<scalar_t, 2> A,
+    Tensor<scalar_t, 1> C, Tensor<int32_t, 2> indices_A) {
+    // The reference CUDA build throws "Not implemented" (mops/src/hpe/hpe.cu:402-413); the
+    // semantics are those of its CPU code (mops/src/hpe/cpu.tpp:275-539).
+    const std::string op = "cuda_homogeneous_polynomial_evaluation_vjp_vjp";
+    grad_like(grad_grad_output, "grad_grad_output", grad_output, "grad_output", op);
+    grad_like(grad_A_2, "grad_A_2", A, "A", op);
+    grad_like(grad_grad_A, "grad_grad_A", A, "A", op);
+    same_size(A, "A", 0, grad_output, "grad_output", 0, op);
+    same_size(C, "C", 0, indices_A, "indices_A", 0, op);
+    check_order(indices_A.shape[1]);
+    fits_int32(2 * A.shape[1], "2 * A.shape[1]", op);
+    if (grad_grad_output.data == nullptr && grad_A_2.data == nullptr) return;
+    const int64_t I = static_cast<int64_t>(A.shape[0]), J = static_cast<int64_t>(C.shape[0]);
+    const int N = static_cast<int>(A.shape[1]), K = static_cast<int>(indices_A.shape[1]);
+    if (I == 0) return;
+    Call call = begin_call();
+    const bool trivial = grad_grad_A.data == nullptr || K == 0 || J == 0 || N == 0;
+    if (trivial) { // no dependence on grad_grad_A: both second-order terms vanish
+        if (N == 0 && K > 0 && J > 0)
+            throw std::runtime_error("Index array indices_A in operation " + op +
+                                     " refers to columns of an A that has none");
+        if (grad_grad_output.data != nullptr)
+            MOPS_CUDA_OK(cudaMemsetAsync(grad_grad_output.data, 0, I * sizeof(scalar_t), call.stream));
+        if (grad_A_2.data != nullptr && N > 0)
+            MOPS_CUDA_OK(cudaMemsetAsync(grad_A_2.data, 0, I * N * sizeof(scalar_t), call.stream));
+        end_call(call, op.c_str(), kIndexNames, 1);
+        return;
+    }
+    fits_int32(C.shape[0] * indices_A.shape[1] * indices_A.shape[1] * 16, "the monomial table", op);
+    const int64_t J2 = J * K;
+    const int N2 = 2 * N, grid = sm_count(call.device) * 8;
+    auto up = [](size_t n) { return (n + 255) / 256 * 256; };
+    const size_t b_a2 = up(static_cast<size_t>(I) * N2 * sizeof(scalar_t));
+    const size_t b_c2 = up(static_cast<size_t>(J2) * sizeof(scalar_t));
+    const size_t b_p2 = up(static_cast<size_t>(J2) * K * sizeof(int32_t));
+    const size_t b_g2 = grad_A_2.data != nullptr ? b_a2 : 0;
+    unsigned char* base = static_cast<unsigned char*>(scratch_alloc(call, b_a2 + b_c2 + b_p2 + b_g2));
+    scalar_t* A2 = reinterpret_cast<scalar_t*>(base);
+    scalar_t* C2 = reinterpret_cast<scalar_t*>(base + b_a2);
+    int32_t* P2 = reinterpret_cast<int32_t*>(base + b_a2 + b_c2);
+    scalar_t* G2 = reinterpret_cast<scalar_t*>(base + b_a2 + b_c2 + b_p2);
+    hpe_augment_rows<scalar_t><<<grid, 256, 0, call.stream>>>(A2, A.data, grad_grad_A.data, I, N);
+    hpe_augment_table<scalar_t><<<grid, 256, 0, call.stream>>>(
+        C2, P2, C.data, indices_A.data, static_cast<int>(J), K, N, call.status);
+    MOPS_CUDA_OK(cudaGetLastError());
+    if (grad_grad_output.data != nullptr)
+        run_forward<scalar_t>(call, grad_grad_output.data, A2, C2, P2, I, N2, J2, K);
+    if (grad_A_2.data != nullptr) {
+        run_backward<scalar_t>(call, G2, grad_output.data, A2, C2, P2, I, N2, J2, K);
+        hpe_take_left_half<scalar_t><<<grid, 256, 0, call.stream>>>(grad_A_2.data, G2, I, N);
+        MOPS_CUDA_OK(cudaGetLastError());
+    }
+    scratch_free(call, base);
+    end_call(call, op.c_str(), kIndexNames, 1);
 }
 
 #define INSTANTIATE(T)                                                                             \

@@ -681,11 +681,11 @@ __global__ void sap_vjp_small(T* __restrict__ gS, T* __restrict__ gT, const T* _
                               SmallPlan<T> plan, int64_t I, int nS, int nT, int nO, int K) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int R = blockDim.x, stride = R + 1, tid = threadIdx.x;
-    T* Tt = reinterpret_cast<T*>(smem_raw);
-    T* Gt = Tt + static_cast<size_t>(nT) * stride;
-    unsigned char* tables = smem_raw + up16(static_cast<size_t>(nT + nO) * stride * sizeof(T));
+    // only gO is gathered by runtime column: T[i, t] is read once per t, straight from global
+    // memory (the row's few sectors stay in L1), which leaves the shared memory to more rows
+    T* Gt = reinterpret_cast<T*>(smem_raw);
+    unsigned char* tables = smem_raw + up16(static_cast<size_t>(nO) * stride * sizeof(T));
     const int64_t i0 = static_cast<int64_t>(blockIdx.x) * R;
-    if (gS != nullptr) tile_load(Tt, nT, Tm, i0, I, R, stride);
     tile_load(Gt, nO, gO, i0, I, R, stride);
     const Entry<T>* table;
     const int32_t* start;
@@ -700,14 +700,14 @@ __global__ void sap_vjp_small(T* __restrict__ gS, T* __restrict__ gT, const T* _
     __syncthreads();
     if (i >= I) return;
     const T* g = Gt + tid;
-    const T* t = Tt + tid;
+    const T* t = Tm + i * nT;
     int k = 0; // one stream of triplets read two ahead, as in the forward kernel
     Entry<T> e1 = fetch_shared(table);
     T c0 = e1.c, v0 = g[e1.o1];
     e1 = fetch_shared(table + 1);
     for (int col = 0; col < nT; col++) {
         const int32_t* bounds = start + col * NS + 1;
-        const T tv = gS != nullptr ? t[col * stride] : T(0);
+        const T tv = gS != nullptr ? __ldg(t + col) : T(0);
         T acc = T(0);
 #pragma unroll
         for (int q = 0; q < NS; q++) {
@@ -836,7 +836,7 @@ bool backward_small(const Call& call, T* gA, T* gB, const T* gO, const T* A, con
     const void* kernel = NS == 4   ? reinterpret_cast<const void*>(sap_vjp_small<T, 4>)
                          : NS == 8 ? reinterpret_cast<const void*>(sap_vjp_small<T, 8>)
                                    : reinterpret_cast<const void*>(sap_vjp_small<T, 16>);
-    const int R = rows_small<T>(call, kernel, nT + nO, K, nT * NS, &smem);
+    const int R = rows_small<T>(call, kernel, nO, K, nT * NS, &smem);
     if (R == 0) return false;
     void* scratch = nullptr;
     SmallPlan<T> plan = make_small_plan<T>(call, &scratch, C, PS, PT, PO, K, nS, nT, nO, NS, R + 1,

@@ -135,11 +135,27 @@ struct HpeBackward : torch::autograd::Function<HpeBackward> {
                     view<scalar_t, 1>(C), view<int32_t, 2>(indices_A));
             });
         });
-        (void)ctx;
+        if (grad_output.requires_grad() || A.requires_grad()) {
+            ctx->save_for_backward({grad_output, A, C, indices_A});
+        }
         return {defined(grad_A, A)};
     }
-    static tensor_list backward(AutogradContext*, tensor_list) {
-        no_second_derivative("homogeneous_polynomial_evaluation");
+    static tensor_list backward(AutogradContext* ctx, tensor_list grads) {
+        auto saved = ctx->get_saved_variables();
+        Tensor grad_output = saved[0], A = saved[1], C = saved[2], indices_A = saved[3];
+        // a placeholder output (gradient not requested in the first backward) has no gradient
+        Tensor gg_A = grads[0].defined() && grads[0].sizes() == A.sizes() ? grads[0].contiguous()
+                                                                           : Tensor();
+        Tensor gg_output = maybe_empty_like(grad_output), grad_A_2 = maybe_empty_like(A);
+        on_stream_of(A, [&] {
+            AT_DISPATCH_FLOATING_TYPES(A.scalar_type(), "homogeneous_polynomial_evaluation_vjp_vjp", [&] {
+                mops::cuda::homogeneous_polynomial_evaluation_vjp_vjp<scalar_t>(
+                    view<scalar_t, 1>(gg_output), view<scalar_t, 2>(grad_A_2),
+                    view<scalar_t, 2>(gg_A), view<scalar_t, 1>(grad_output), view<scalar_t, 2>(A),
+                    view<scalar_t, 1>(C), view<int32_t, 2>(indices_A));
+            });
+        });
+        return {gg_output, grad_A_2, Tensor(), Tensor()};
     }
 };
 

@@ -64,6 +64,15 @@ class Oracle:
                    [A.shape[0], A.shape[1], P.shape[0], P.shape[1]])
         return gA
 
+    def hpe_vjp_vjp(self, ggA, gO, A, C, P, need=(True, True)):
+        gO, A, C, P = _c(gO), _c(A), _c(C), _i32(P)
+        ggA = None if ggA is None else _c(ggA)
+        ggO = np.empty_like(gO) if need[0] else None
+        gA2 = np.empty_like(A) if need[1] else None
+        self._call("hpe_vjp_vjp", A.dtype, [ggO, gA2, ggA, gO, A, C, P],
+                   [A.shape[0], A.shape[1], P.shape[0], P.shape[1]])
+        return ggO, gA2
+
     # ---- SAP
     def sap(self, A, B, C, PA, PB, PO, n_out):
         A, B, C = _c(A), _c(B), _c(C)
@@ -236,6 +245,16 @@ class Reference:
         gA = np.empty_like(A)
         self.raw("hpe", "_vjp", A.dtype, gA, gO, A, C, P)
         return gA
+
+    def hpe_vjp_vjp(self, ggA, gO, A, C, P, need=(True, True)):
+        gO, A, C, P = _c(gO), _c(A), _c(C), _i32(P)
+        ggO = np.empty_like(gO) if need[0] else None
+        gA2 = np.empty_like(A) if need[1] else None
+        # C prototype order (mops/include/mops/hpe.h:46-54)
+        self.raw("hpe", "_vjp_vjp", A.dtype, ggO if need[0] else Null(1, A.dtype),
+                 gA2 if need[1] else Null(2, A.dtype),
+                 Null(2, A.dtype) if ggA is None else _c(ggA), gO, A, C, P)
+        return ggO, gA2
 
     def sap(self, A, B, C, PA, PB, PO, n_out):
         A, B, C, PA, PB, PO = _c(A), _c(B), _c(C), _i32(PA), _i32(PB), _i32(PO)

@@ -46,6 +46,42 @@ void FN(oracle_hpe_vjp)(T *gA, const T *gO, const T *A, const T *C, const int32_
     }
 }
 
+/* Second-order terms of HPE.  mops/src/hpe/cpu.tpp:275-539,
+ * python/mops/src/mops/reference_implementations.py:322-376
+ *   ggO[i]          += C[j] ggA[i,P[j,k]] prod_{l != k} A[i,P[j,l]]                  (all j, k)
+ *   gA2[i, P[j,l]]  += gO[i] C[j] ggA[i,P[j,k]] prod_{m != k, m != l} A[i,P[j,m]]    (all j, l, k != l)
+ * ggA may be NULL (both terms vanish); each output may be NULL (skipped). */
+void FN(oracle_hpe_vjp_vjp)(T *ggO, T *gA2, const T *ggA, const T *gO, const T *A, const T *C,
+                            const int32_t *P, int64_t I, int64_t N, int64_t J, int64_t K) {
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < I; i++) {
+        const T *a = A + i * N;
+        if (ggO) ggO[i] = 0;
+        if (gA2) for (int64_t n = 0; n < N; n++) gA2[i * N + n] = 0;
+        if (!ggA) continue;
+        const T *h = ggA + i * N;
+        for (int64_t j = 0; j < J; j++) {
+            const int32_t *p = P + j * K;
+            if (ggO)
+                for (int64_t k = 0; k < K; k++) {
+                    T t = C[j] * h[p[k]];
+                    for (int64_t l = 0; l < K; l++)
+                        if (l != k) t *= a[p[l]];
+                    ggO[i] += t;
+                }
+            if (gA2)
+                for (int64_t l = 0; l < K; l++)
+                    for (int64_t k = 0; k < K; k++) {
+                        if (k == l) continue;
+                        T t = C[j] * gO[i] * h[p[k]];
+                        for (int64_t m = 0; m < K; m++)
+                            if (m != k && m != l) t *= a[p[m]];
+                        gA2[i * N + p[l]] += t;
+                    }
+        }
+    }
+}
+
 /* O[i, PO[k]] += C[k]*A[i,PA[k]]*B[i,PB[k]]      mops/src/sap/cpu.tpp:65-78 */
 void FN(oracle_sap)(T *O, const T *A, const T *B, const T *C, const int32_t *PA,
                     const int32_t *PB, const int32_t *PO, int64_t I, int64_t nA, int64_t nB,

@@ -18,8 +18,10 @@ def _rs():
 
 def hpe():
     r = _rs()
-    return dict(A=r.rand(99, 20), C=r.rand(200), indices_A=r.randint(20, size=(200, 4)).astype(np.int32),
-                grad_output=r.rand(99))
+    d = dict(A=r.rand(99, 20), C=r.rand(200),
+             indices_A=r.randint(20, size=(200, 4)).astype(np.int32), grad_output=r.rand(99))
+    d["grad_grad_A"] = r.rand(99, 20)
+    return d
 
 
 def sap():

@@ -28,6 +28,9 @@ def run_library(op, d, second_order=False):
         out["output"] = M.homogeneous_polynomial_evaluation(d["A"], d["C"], d["indices_A"])
         out["grad_A"] = M.homogeneous_polynomial_evaluation_vjp(
             d["grad_output"], d["A"], d["C"], d["indices_A"])
+        if second_order:
+            out["grad_grad_output"], out["grad_A_2"] = M.homogeneous_polynomial_evaluation_vjp_vjp(
+                d["grad_grad_A"], d["grad_output"], d["A"], d["C"], d["indices_A"])
     elif op == "sap":
         idx = (d["indices_A"], d["indices_B"], d["indices_output"])
         out["output"] = M.sparse_accumulation_of_products(d["A"], d["B"], d["C"], *idx,
@@ -75,6 +78,9 @@ def run_checker(impl, op, d, dtype, second_order=False):
     if op == "hpe":
         out["output"] = impl.hpe(c(d["A"]), c(d["C"]), d["indices_A"])
         out["grad_A"] = impl.hpe_vjp(c(d["grad_output"]), c(d["A"]), c(d["C"]), d["indices_A"])
+        if second_order:
+            out["grad_grad_output"], out["grad_A_2"] = impl.hpe_vjp_vjp(
+                c(d["grad_grad_A"]), c(d["grad_output"]), c(d["A"]), c(d["C"]), d["indices_A"])
     elif op == "sap":
         idx = (d["indices_A"], d["indices_B"], d["indices_output"])
         out["output"] = impl.sap(c(d["A"]), c(d["B"]), c(d["C"]), *idx, d["output_size"])

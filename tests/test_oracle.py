@@ -22,6 +22,9 @@ def run_all(impl, name, d, dtype=np.float64, second_order=True):
     if op == "hpe":
         out["output"] = impl.hpe(c(d["A"]), c(d["C"]), d["indices_A"])
         out["grad_A"] = impl.hpe_vjp(c(d["grad_output"]), c(d["A"]), c(d["C"]), d["indices_A"])
+        if second_order and "grad_grad_A" in d:
+            out["grad_grad_output"], out["grad_A_2"] = impl.hpe_vjp_vjp(
+                c(d["grad_grad_A"]), c(d["grad_output"]), c(d["A"]), c(d["C"]), d["indices_A"])
     elif op == "sap":
         idx = (d["indices_A"], d["indices_B"], d["indices_output"])
         out["output"] = impl.sap(c(d["A"]), c(d["B"]), c(d["C"]), *idx, d["output_size"])

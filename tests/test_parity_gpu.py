@@ -34,7 +34,7 @@ def test_golden_vectors(name):
     Scatter indices of these fixtures are unsorted: exercises the unsorted-index path."""
     d = fixtures.CASES[name]()
     op = name.split("_")[0]
-    got = run_library(op, to_dev(d, np.float64), second_order=(op in ("sap", "opsa")))
+    got = run_library(op, to_dev(d, np.float64), second_order=(op in ("hpe", "sap", "opsa")))
     keys = [k for k in GOLD.files if k.startswith(name + "/")]
     assert len(keys) == len(got)
     for k in keys:
@@ -45,7 +45,7 @@ def test_golden_vectors(name):
 @pytest.mark.parametrize("name", sorted(fixtures.CASES))
 def test_fixtures_against_oracle(oracle, name, dtype):
     op = name.split("_")[0]
-    compare(op, fixtures.CASES[name](), dtype, oracle, second_order=(op in ("sap", "opsa")),
+    compare(op, fixtures.CASES[name](), dtype, oracle, second_order=(op in ("hpe", "sap", "opsa")),
             what=name)
 
 
@@ -89,8 +89,9 @@ def test_sasaw_full_small_config(oracle):
 def test_hpe_every_order(oracle, K, dtype):
     r = np.random.default_rng(100 + K)
     d = dict(A=r.uniform(-1, 1, (77, 13)), C=r.standard_normal(41),
-             indices_A=r.integers(0, 13, (41, K), dtype=np.int32), grad_output=r.standard_normal(77))
-    compare("hpe", d, dtype, oracle, what=f"hpe K={K}")
+             indices_A=r.integers(0, 13, (41, K), dtype=np.int32), grad_output=r.standard_normal(77),
+             grad_grad_A=r.standard_normal((77, 13)))
+    compare("hpe", d, dtype, oracle, second_order=True, what=f"hpe K={K}")
 
 
 def test_hpe_order_above_10_is_an_error():

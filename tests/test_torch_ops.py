@@ -1,7 +1,7 @@
 """The torch operators (torch.ops.mops.*): registration and argument checks on CPU; on the
 GPU, forward parity with the CPU oracle, finite-difference gradient checks in f64 (the VJP
 checked against the forward, independent of any reference VJP; the reference does the same
-in python/mops-torch/tests/*.py), second derivatives for SAP and OPSA, and a TorchScript round trip."""
+in python/mops-torch/tests/*.py), second derivatives for HPE, SAP and OPSA, and a TorchScript round trip."""
 import io
 
 import numpy as np
@@ -93,6 +93,8 @@ def test_gradcheck_all_operations():
 
     A, C, P = rand(30, 8), torch.rand(40, dtype=torch.float64, generator=g).cuda(), ri(8, 40, 3)
     assert torch.autograd.gradcheck(mt.homogeneous_polynomial_evaluation, (A, C, P), fast_mode=True)
+    assert torch.autograd.gradgradcheck(mt.homogeneous_polynomial_evaluation, (A, C, P),
+                                        fast_mode=True)
 
     A, B = rand(20, 7), rand(20, 5)
     Csap = torch.rand(30, dtype=torch.float64, generator=g).cuda()
@@ -125,9 +127,10 @@ def test_gradcheck_all_operations():
 @pytest.mark.gpu
 def test_second_derivatives_without_a_kernel_raise():
     A = torch.rand(20, 6, dtype=torch.float64, device="cuda", requires_grad=True)
-    C = torch.rand(9, dtype=torch.float64, device="cuda")
-    P = torch.randint(6, (9, 3), dtype=torch.int32, device="cuda")
-    out = mt.homogeneous_polynomial_evaluation(A, C, P)
+    B = torch.rand(20, 5, dtype=torch.float64, device="cuda", requires_grad=True)
+    W = torch.rand(4, 5, dtype=torch.float64, device="cuda", requires_grad=True)
+    idx = torch.sort(torch.randint(4, (20,), dtype=torch.int32, device="cuda")).values
+    out = mt.outer_product_scatter_add_with_weights(A, B, W, idx, idx)
     (gA,) = torch.autograd.grad(out.sum(), A, create_graph=True)
     with pytest.raises(NotImplementedError, match="second derivatives are not supported"):
         gA.sum().backward()
