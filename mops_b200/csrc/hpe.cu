@@ -90,21 +90,23 @@ struct HpePlan {
     int32_t* cursor;        // [plan warps][N + 1] scratch
 };
 
-// Loads rows [i0, i0+32) of a row-major [I][N] matrix into tile[n*kPad + row].
+// Loads rows [i0, i0+rows) of a row-major [I][N] matrix into tile[n*(rows+1) + row].
 template <typename T>
 __device__ __forceinline__ void load_tile_transposed(T* tile, const T* __restrict__ M, int64_t i0,
-                                                     int64_t I, int N, int tid, int nthreads) {
-    const int64_t rows = I - i0 < kRows ? I - i0 : kRows;
-    const int total = kRows * N;
-    const int valid = static_cast<int>(rows) * N;
+                                                     int64_t I, int N, int tid, int nthreads,
+                                                     int rows = kRows) {
+    const int pad = rows + 1;
+    const int64_t have = I - i0 < rows ? I - i0 : rows;
+    const int total = rows * N;
+    const int valid = static_cast<int>(have) * N;
     const T* src = M + i0 * N;
     const int dr = nthreads / N, dn = nthreads - dr * N;
     int row = tid / N, n = tid - row * N;
     for (int idx = tid; idx < total; idx += nthreads) {
         if (idx < valid)
-            cp_async<sizeof(T)>(tile + n * kPad + row, src + idx);
+            cp_async<sizeof(T)>(tile + n * pad + row, src + idx);
         else
-            tile[n * kPad + row] = T(0);
+            tile[n * pad + row] = T(0);
         row += dr;
         n += dn;
         if (n >= N) {
@@ -119,7 +121,7 @@ __device__ __forceinline__ void load_tile_transposed(T* tile, const T* __restric
 template <typename T>
 __global__ void __launch_bounds__(kPlanThreads)
 hpe_plan(HpePlan plan, const T* __restrict__ C, const int32_t* __restrict__ P, int J, int K,
-         int N, bool want_fwd, bool want_vjp, Status st) {
+         int N, bool want_fwd, bool want_vjp, int vjp_pad, Status st) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int fwd_bytes = record_bytes(sizeof(T), K), vjp_bytes = record_bytes(sizeof(T), K - 1);
     const int M = J * K;
@@ -213,7 +215,7 @@ hpe_plan(HpePlan plan, const T* __restrict__ C, const int32_t* __restrict__ P, i
                 if (l == k) continue;
                 int32_t p = P[j * K + l];
                 clamp_index(p, N);
-                write_offset<T>(rec, q++, p * kPad);
+                write_offset<T>(rec, q++, p * vjp_pad);
             }
         }
         __syncwarp();
@@ -301,7 +303,9 @@ hpe_fwd_rows(T* __restrict__ O, const T* __restrict__ A, const unsigned char* __
     }
 }
 
-template <typename T, int K>
+// R rows per lane (lane works on rows lane + 32 r of the block's 32 R-row tile): one record read
+// serves R rows.
+template <typename T, int K, int R>
 __global__ void __launch_bounds__(kWarps * 32)
 hpe_vjp_rows(T* __restrict__ gA, const T* __restrict__ gO, const T* __restrict__ A, HpePlan plan,
              int64_t I, int N) {
@@ -309,6 +313,7 @@ hpe_vjp_rows(T* __restrict__ gA, const T* __restrict__ gO, const T* __restrict__
     constexpr int RB = record_bytes(sizeof(T), NF);
     constexpr int kStageBytes = kVjpChunk * RB;
     constexpr int unit = RB >= 16 ? 16 : 8;
+    constexpr int kTileRows = 32 * R;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     // layout: per warp 2 stages of records | A tile
     T* At = reinterpret_cast<T*>(smem_raw + kWarps * 2 * kStageBytes);
@@ -316,10 +321,10 @@ hpe_vjp_rows(T* __restrict__ gA, const T* __restrict__ gO, const T* __restrict__
     // the shuffle tells the compiler that the warp number (and the incidence range and loop
     // counts derived from it) is the same in all lanes
     const int warp = __shfl_sync(kFullMask, tid >> 5, 0);
-    const int64_t i0 = static_cast<int64_t>(blockIdx.x) * kRows;
+    const int64_t i0 = static_cast<int64_t>(blockIdx.x) * kTileRows;
     unsigned char* recs_w = smem_raw + warp * 2 * kStageBytes;
 
-    load_tile_transposed(At, A, i0, I, N, tid, kWarps * 32);
+    load_tile_transposed(At, A, i0, I, N, tid, kWarps * 32, kTileRows);
     cp_async_commit();
 
     const int n_lo = __ldg(plan.split + warp), n_hi = __ldg(plan.split + warp + 1);
@@ -340,14 +345,29 @@ hpe_vjp_rows(T* __restrict__ gA, const T* __restrict__ gO, const T* __restrict__
         cp_async_wait<0>();
     __syncthreads();
 
-    const bool live = i0 + lane < I;
-    const T go = live ? gO[i0 + lane] : T(0);
+    T go[R];
+    bool live[R];
+#pragma unroll
+    for (int r = 0; r < R; r++) {
+        live[r] = i0 + lane + 32 * r < I;
+        go[r] = live[r] ? gO[i0 + lane + 32 * r] : T(0);
+    }
     const T* col = At + lane;
     T* out = gA + (i0 + lane) * N;
+    constexpr int U = R == 1 ? 4 : 2; // independent partial sums per row
 
     int n = n_lo;
     int end_n = n < n_hi ? __ldg(plan.n_start + n + 1) : x_hi;
-    T acc = T(0);
+    T acc[R];
+#pragma unroll
+    for (int r = 0; r < R; r++) acc[r] = T(0);
+    auto close_group = [&] {
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+            if (live[r]) out[static_cast<int64_t>(32 * r) * N + n] = go[r] * acc[r];
+            acc[r] = T(0);
+        }
+    };
     int stage = 0;
     for (int x0 = x_lo; x0 < x_hi; x0 += kVjpChunk, stage ^= 1) {
         const int xc = x_hi - x0 < kVjpChunk ? x_hi - x0 : kVjpChunk;
@@ -359,41 +379,47 @@ hpe_vjp_rows(T* __restrict__ gA, const T* __restrict__ gO, const T* __restrict__
         }
         __syncwarp();
         const unsigned char* recs = recs_w + stage * kStageBytes;
-        // One term: C_j times the other K-1 factors of incidence y of this stage.
-        auto term = [&](int y) -> T {
+        // One term per row: C_j times the other K-1 factors of incidence y of this stage.
+        auto add_term = [&](int y, T (&sum)[R]) {
             int o[NF > 0 ? NF : 1];
-            T prod = read_record<T, NF>(recs + y * RB, o);
+            const T c = read_record<T, NF>(recs + y * RB, o);
 #pragma unroll
-            for (int k = 0; k < NF; k++) prod *= col[o[k]];
-            return prod;
+            for (int r = 0; r < R; r++) {
+                T prod = c;
+#pragma unroll
+                for (int k = 0; k < NF; k++) prod *= col[o[k] + 32 * r];
+                sum[r] += prod;
+            }
         };
         int y = 0;
         while (y < xc) {
             while (x0 + y == end_n) { // group n is complete (possibly empty)
-                if (live) out[n] = go * acc;
-                acc = T(0);
+                close_group();
                 n++;
                 end_n = __ldg(plan.n_start + n + 1);
             }
             // the rest of group n that lies in this stage: no group test inside
             const int run_end = min(xc, end_n - x0);
-            T acc1 = T(0), acc2 = T(0), acc3 = T(0);
-            for (; y + 4 <= run_end; y += 4) {
-                acc += term(y);
-                acc1 += term(y + 1);
-                acc2 += term(y + 2);
-                acc3 += term(y + 3);
+            T part[U - 1][R];
+#pragma unroll
+            for (int u = 0; u < U - 1; u++)
+#pragma unroll
+                for (int r = 0; r < R; r++) part[u][r] = T(0);
+            for (; y + U <= run_end; y += U) {
+                add_term(y, acc);
+#pragma unroll
+                for (int u = 1; u < U; u++) add_term(y + u, part[u - 1]);
             }
-            for (; y < run_end; y++) acc += term(y);
-            acc += (acc1 + acc2) + acc3;
+            for (; y < run_end; y++) add_term(y, acc);
+#pragma unroll
+            for (int u = 0; u < U - 1; u++)
+#pragma unroll
+                for (int r = 0; r < R; r++) acc[r] += part[u][r];
         }
         __syncwarp(); // the stage is overwritten by the copy issued next round
     }
     // Close the last group and any empty groups after it.
-    for (; n < n_hi; n++) {
-        if (live) out[n] = go * acc;
-        acc = T(0);
-    }
+    for (; n < n_hi; n++) close_group();
 }
 
 // Any N: one thread per row, factors straight from global memory. Used when a 32-row tile of
@@ -451,15 +477,15 @@ template <typename T, int K> size_t fwd_smem(int N) {
            (static_cast<size_t>(N) * kPad + kWarps * 32) * sizeof(T);
 }
 
-template <typename T, int K> size_t vjp_smem(int N) {
+template <typename T, int K> size_t vjp_smem(int N, int rows_per_lane = 1) {
     return kWarps * 2 * kVjpChunk * record_bytes(sizeof(T), K - 1) +
-           static_cast<size_t>(N) * kPad * sizeof(T);
+           static_cast<size_t>(N) * (32 * rows_per_lane + 1) * sizeof(T);
 }
 
 // Allocates the call-scoped tables and runs the plan kernel.
 template <typename T>
 HpePlan make_plan(const Call& call, void** scratch, const T* C, const int32_t* P, int64_t J,
-                  int K, int N, bool want_fwd, bool want_vjp) {
+                  int K, int N, bool want_fwd, bool want_vjp, int vjp_pad = kPad) {
     auto up = [](size_t n) { return (n + 255) / 256 * 256; };
     const size_t M = static_cast<size_t>(J) * K;
     const size_t b_fwd = want_fwd ? up(static_cast<size_t>(J) * record_bytes(sizeof(T), K)) : 0;
@@ -480,7 +506,7 @@ HpePlan make_plan(const Call& call, void** scratch, const T* C, const int32_t* P
     p += b_cur;
     plan.split = reinterpret_cast<int32_t*>(p);
     hpe_plan<T><<<1, kPlanThreads, 0, call.stream>>>(plan, C, P, static_cast<int>(J), K, N,
-                                                     want_fwd, want_vjp, call.status);
+                                                     want_fwd, want_vjp, vjp_pad, call.status);
     MOPS_CUDA_OK(cudaGetLastError());
     return plan;
 }
@@ -508,15 +534,28 @@ void launch_vjp(const Call& call, T* gA, const T* gO, const T* A, const T* C, co
         MOPS_CUDA_OK(cudaMemsetAsync(gA, 0, I * N * sizeof(T), call.stream));
         return;
     }
-    const size_t smem = vjp_smem<T, K>(N);
+    // Two rows per lane when the batch still fills the GPU that way and the wider tile fits.
+    const size_t smem2 = vjp_smem<T, K>(N, 2);
+    const bool two = I >= static_cast<int64_t>(sm_count(call.device)) * 64 * 8 &&
+                     smem2 <= 75 * 1024 && static_cast<int64_t>(N) * 65 <= 65535;
+    const size_t smem = two ? smem2 : vjp_smem<T, K>(N);
     void* scratch = nullptr;
-    HpePlan plan = make_plan<T>(call, &scratch, C, P, J, K, N, false, true);
-    auto kernel = hpe_vjp_rows<T, K>;
-    if (smem > 48 * 1024)
-        MOPS_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          static_cast<int>(smem)));
-    kernel<<<static_cast<unsigned>(ceil_div(I, kRows)), kWarps * 32, smem, call.stream>>>(
-        gA, gO, A, plan, I, N);
+    HpePlan plan = make_plan<T>(call, &scratch, C, P, J, K, N, false, true, two ? 65 : kPad);
+    if (two) {
+        auto kernel = hpe_vjp_rows<T, K, 2>;
+        if (smem > 48 * 1024)
+            MOPS_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                              static_cast<int>(smem)));
+        kernel<<<static_cast<unsigned>(ceil_div(I, 64)), kWarps * 32, smem, call.stream>>>(
+            gA, gO, A, plan, I, N);
+    } else {
+        auto kernel = hpe_vjp_rows<T, K, 1>;
+        if (smem > 48 * 1024)
+            MOPS_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                              static_cast<int>(smem)));
+        kernel<<<static_cast<unsigned>(ceil_div(I, kRows)), kWarps * 32, smem, call.stream>>>(
+            gA, gO, A, plan, I, N);
+    }
     MOPS_CUDA_OK(cudaGetLastError());
     scratch_free(call, scratch);
 }

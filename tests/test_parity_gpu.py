@@ -112,6 +112,16 @@ def test_ragged_batch_sizes(oracle, I):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+def test_hpe_large_batch(oracle, dtype):
+    """A batch large enough for the two-rows-per-lane HPE VJP (chosen when the batch still
+    fills the GPU that way), with a ragged last block."""
+    compare("hpe", workloads.hpe(I=148 * 64 * 8 + 37, N=17, J=60, K=3), dtype, oracle,
+            what="hpe large batch")
+    compare("hpe", workloads.hpe(I=148 * 64 * 8 + 1, N=9, J=25, K=1), dtype, oracle,
+            what="hpe large batch, K=1")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_wide_operands_take_the_global_memory_kernels(oracle, dtype):
     """Operand widths whose tiles do not fit in shared memory."""
     compare("hpe", workloads.hpe(I=70, N=1500, J=64, K=3), dtype, oracle, what="hpe wide")
