@@ -121,7 +121,7 @@ __device__ __forceinline__ void load_tile_transposed(T* tile, const T* __restric
 template <typename T>
 __global__ void __launch_bounds__(kPlanThreads)
 hpe_plan(HpePlan plan, const T* __restrict__ C, const int32_t* __restrict__ P, int J, int K,
-         int N, bool want_fwd, bool want_vjp, int vjp_pad, Status st) {
+         int N, bool want_fwd, bool want_vjp, int pad, Status st) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int fwd_bytes = record_bytes(sizeof(T), K), vjp_bytes = record_bytes(sizeof(T), K - 1);
     const int M = J * K;
@@ -136,7 +136,7 @@ hpe_plan(HpePlan plan, const T* __restrict__ C, const int32_t* __restrict__ P, i
             for (int k = 0; k < K; k++) {
                 int32_t p = P[j * K + k];
                 clamp_index(p, N);
-                write_offset<T>(rec, k, p * kPad);
+                write_offset<T>(rec, k, p * pad);
             }
         }
     }
@@ -215,7 +215,7 @@ hpe_plan(HpePlan plan, const T* __restrict__ C, const int32_t* __restrict__ P, i
                 if (l == k) continue;
                 int32_t p = P[j * K + l];
                 clamp_index(p, N);
-                write_offset<T>(rec, q++, p * vjp_pad);
+                write_offset<T>(rec, q++, p * pad);
             }
         }
         __syncwarp();
@@ -241,19 +241,22 @@ hpe_plan(HpePlan plan, const T* __restrict__ C, const int32_t* __restrict__ P, i
     }
 }
 
-template <typename T, int K>
+// R rows per lane (lane works on rows lane + 32 r of the block's 32 R-row tile): one record read
+// serves R rows.
+template <typename T, int K, int R>
 __global__ void __launch_bounds__(kWarps * 32)
 hpe_fwd_rows(T* __restrict__ O, const T* __restrict__ A, const unsigned char* __restrict__ records,
              int64_t I, int N, int J) {
     constexpr int RB = record_bytes(sizeof(T), K);
     constexpr int kStageBytes = kFwdChunk * RB;
     constexpr int unit = RB >= 16 ? 16 : 8;
+    constexpr int kTileRows = 32 * R;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     // layout: stage 0 records | stage 1 records | A tile | partial
     T* At = reinterpret_cast<T*>(smem_raw + 2 * kStageBytes);
-    T* partial = At + static_cast<size_t>(N) * kPad;
+    T* partial = At + static_cast<size_t>(N) * (kTileRows + 1);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int64_t i0 = static_cast<int64_t>(blockIdx.x) * kRows;
+    const int64_t i0 = static_cast<int64_t>(blockIdx.x) * kTileRows;
 
     auto issue = [&](int stage, int m0) {
         const int mc = J - m0 < kFwdChunk ? J - m0 : kFwdChunk;
@@ -263,11 +266,13 @@ hpe_fwd_rows(T* __restrict__ O, const T* __restrict__ A, const unsigned char* __
         cp_async_commit();
     };
 
-    load_tile_transposed(At, A, i0, I, N, tid, kWarps * 32);
+    load_tile_transposed(At, A, i0, I, N, tid, kWarps * 32, kTileRows);
     if (J > 0) issue(0, 0);
 
     const T* col = At + lane;
-    T acc = T(0);
+    T acc[R];
+#pragma unroll
+    for (int r = 0; r < R; r++) acc[r] = T(0);
     int stage = 0;
     for (int m0 = 0; m0 < J; m0 += kFwdChunk, stage ^= 1) {
         const int mc = J - m0 < kFwdChunk ? J - m0 : kFwdChunk;
@@ -282,10 +287,14 @@ hpe_fwd_rows(T* __restrict__ O, const T* __restrict__ A, const unsigned char* __
 #pragma unroll 4
         for (int m = warp; m < mc; m += kWarps) {
             int o[K > 0 ? K : 1];
-            T prod = read_record<T, K>(recs + m * RB, o);
+            const T c = read_record<T, K>(recs + m * RB, o);
 #pragma unroll
-            for (int k = 0; k < K; k++) prod *= col[o[k]];
-            acc += prod;
+            for (int r = 0; r < R; r++) {
+                T prod = c;
+#pragma unroll
+                for (int k = 0; k < K; k++) prod *= col[o[k] + 32 * r];
+                acc[r] += prod;
+            }
         }
         __syncthreads(); // the stage is overwritten by the copy issued next round
     }
@@ -293,13 +302,16 @@ hpe_fwd_rows(T* __restrict__ O, const T* __restrict__ A, const unsigned char* __
         cp_async_wait<0>();
         __syncthreads();
     }
-    partial[warp * 32 + lane] = acc;
-    __syncthreads();
-    if (warp == 0 && i0 + lane < I) {
-        T sum = partial[lane];
 #pragma unroll
-        for (int w = 1; w < kWarps; w++) sum += partial[w * 32 + lane];
-        O[i0 + lane] = sum;
+    for (int r = 0; r < R; r++) partial[warp * kTileRows + 32 * r + lane] = acc[r];
+    __syncthreads();
+    for (int row = tid; row < kTileRows; row += kWarps * 32) {
+        if (i0 + row < I) {
+            T sum = partial[row];
+#pragma unroll
+            for (int w = 1; w < kWarps; w++) sum += partial[w * kTileRows + row];
+            O[i0 + row] = sum;
+        }
     }
 }
 
@@ -472,9 +484,10 @@ __global__ void hpe_vjp_wide(T* __restrict__ gA, const T* __restrict__ gO,
     }
 }
 
-template <typename T, int K> size_t fwd_smem(int N) {
+template <typename T, int K> size_t fwd_smem(int N, int rows_per_lane = 1) {
+    const int rows = 32 * rows_per_lane;
     return 2 * kFwdChunk * record_bytes(sizeof(T), K) +
-           (static_cast<size_t>(N) * kPad + kWarps * 32) * sizeof(T);
+           (static_cast<size_t>(N) * (rows + 1) + kWarps * rows) * sizeof(T);
 }
 
 template <typename T, int K> size_t vjp_smem(int N, int rows_per_lane = 1) {
@@ -485,7 +498,7 @@ template <typename T, int K> size_t vjp_smem(int N, int rows_per_lane = 1) {
 // Allocates the call-scoped tables and runs the plan kernel.
 template <typename T>
 HpePlan make_plan(const Call& call, void** scratch, const T* C, const int32_t* P, int64_t J,
-                  int K, int N, bool want_fwd, bool want_vjp, int vjp_pad = kPad) {
+                  int K, int N, bool want_fwd, bool want_vjp, int pad = kPad) {
     auto up = [](size_t n) { return (n + 255) / 256 * 256; };
     const size_t M = static_cast<size_t>(J) * K;
     const size_t b_fwd = want_fwd ? up(static_cast<size_t>(J) * record_bytes(sizeof(T), K)) : 0;
@@ -506,7 +519,7 @@ HpePlan make_plan(const Call& call, void** scratch, const T* C, const int32_t* P
     p += b_cur;
     plan.split = reinterpret_cast<int32_t*>(p);
     hpe_plan<T><<<1, kPlanThreads, 0, call.stream>>>(plan, C, P, static_cast<int>(J), K, N,
-                                                     want_fwd, want_vjp, vjp_pad, call.status);
+                                                     want_fwd, want_vjp, pad, call.status);
     MOPS_CUDA_OK(cudaGetLastError());
     return plan;
 }
@@ -514,15 +527,28 @@ HpePlan make_plan(const Call& call, void** scratch, const T* C, const int32_t* P
 template <typename T, int K>
 void launch_fwd(const Call& call, T* O, const T* A, const T* C, const int32_t* P, int64_t I,
                 int N, int64_t J) {
-    const size_t smem = fwd_smem<T, K>(N);
+    // Two rows per lane when the batch still fills the GPU that way and the wider tile fits.
+    const size_t smem2 = fwd_smem<T, K>(N, 2);
+    const bool two = I >= static_cast<int64_t>(sm_count(call.device)) * 64 * 8 &&
+                     smem2 <= 75 * 1024 && static_cast<int64_t>(N) * 65 <= 65535;
+    const size_t smem = two ? smem2 : fwd_smem<T, K>(N);
     void* scratch = nullptr;
-    HpePlan plan = make_plan<T>(call, &scratch, C, P, J, K, N, true, false);
-    auto kernel = hpe_fwd_rows<T, K>;
-    if (smem > 48 * 1024)
-        MOPS_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          static_cast<int>(smem)));
-    kernel<<<static_cast<unsigned>(ceil_div(I, kRows)), kWarps * 32, smem, call.stream>>>(
-        O, A, plan.fwd_rec, I, N, static_cast<int>(J));
+    HpePlan plan = make_plan<T>(call, &scratch, C, P, J, K, N, true, false, two ? 65 : kPad);
+    if (two) {
+        auto kernel = hpe_fwd_rows<T, K, 2>;
+        if (smem > 48 * 1024)
+            MOPS_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                              static_cast<int>(smem)));
+        kernel<<<static_cast<unsigned>(ceil_div(I, 64)), kWarps * 32, smem, call.stream>>>(
+            O, A, plan.fwd_rec, I, N, static_cast<int>(J));
+    } else {
+        auto kernel = hpe_fwd_rows<T, K, 1>;
+        if (smem > 48 * 1024)
+            MOPS_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                              static_cast<int>(smem)));
+        kernel<<<static_cast<unsigned>(ceil_div(I, kRows)), kWarps * 32, smem, call.stream>>>(
+            O, A, plan.fwd_rec, I, N, static_cast<int>(J));
+    }
     MOPS_CUDA_OK(cudaGetLastError());
     scratch_free(call, scratch);
 }
