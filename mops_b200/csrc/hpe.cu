@@ -366,7 +366,7 @@ hpe_vjp_rows(T* __restrict__ gA, const T* __restrict__ gO, const T* __restrict__
     }
     const T* col = At + lane;
     T* out = gA + (i0 + lane) * N;
-    constexpr int U = R == 1 ? 4 : 2; // independent partial sums per row
+    constexpr int U = R == 1 ? 4 : R == 2 ? 2 : 1; // independent partial sums per row
 
     int n = n_lo;
     int end_n = n < n_hi ? __ldg(plan.n_start + n + 1) : x_hi;
@@ -412,7 +412,7 @@ hpe_vjp_rows(T* __restrict__ gA, const T* __restrict__ gO, const T* __restrict__
             }
             // the rest of group n that lies in this stage: no group test inside
             const int run_end = min(xc, end_n - x0);
-            T part[U - 1][R];
+            T part[U > 1 ? U - 1 : 1][R];
 #pragma unroll
             for (int u = 0; u < U - 1; u++)
 #pragma unroll
@@ -560,28 +560,32 @@ void launch_vjp(const Call& call, T* gA, const T* gO, const T* A, const T* C, co
         MOPS_CUDA_OK(cudaMemsetAsync(gA, 0, I * N * sizeof(T), call.stream));
         return;
     }
-    // Two rows per lane when the batch still fills the GPU that way and the wider tile fits.
-    const size_t smem2 = vjp_smem<T, K>(N, 2);
-    const bool two = I >= static_cast<int64_t>(sm_count(call.device)) * 64 * 8 &&
-                     smem2 <= 75 * 1024 && static_cast<int64_t>(N) * 65 <= 65535;
-    const size_t smem = two ? smem2 : vjp_smem<T, K>(N);
-    void* scratch = nullptr;
-    HpePlan plan = make_plan<T>(call, &scratch, C, P, J, K, N, false, true, two ? 65 : kPad);
-    if (two) {
-        auto kernel = hpe_vjp_rows<T, K, 2>;
-        if (smem > 48 * 1024)
-            MOPS_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                              static_cast<int>(smem)));
-        kernel<<<static_cast<unsigned>(ceil_div(I, 64)), kWarps * 32, smem, call.stream>>>(
-            gA, gO, A, plan, I, N);
-    } else {
-        auto kernel = hpe_vjp_rows<T, K, 1>;
-        if (smem > 48 * 1024)
-            MOPS_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                              static_cast<int>(smem)));
-        kernel<<<static_cast<unsigned>(ceil_div(I, kRows)), kWarps * 32, smem, call.stream>>>(
-            gA, gO, A, plan, I, N);
+    // Several rows per lane when the batch still fills the GPU that way and the wider tile fits.
+    int rpl = 1;
+    for (int r : {4, 2}) {
+        if (I >= static_cast<int64_t>(sm_count(call.device)) * 32 * r * 8 &&
+            vjp_smem<T, K>(N, r) <= 112 * 1024 &&
+            static_cast<int64_t>(N) * (32 * r + 1) <= 65535) {
+            rpl = r;
+            break;
+        }
     }
+    const size_t smem = vjp_smem<T, K>(N, rpl);
+    void* scratch = nullptr;
+    HpePlan plan = make_plan<T>(call, &scratch, C, P, J, K, N, false, true, 32 * rpl + 1);
+    auto launch = [&](auto kernel) {
+        if (smem > 48 * 1024)
+            MOPS_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                              static_cast<int>(smem)));
+        kernel<<<static_cast<unsigned>(ceil_div(I, 32 * rpl)), kWarps * 32, smem, call.stream>>>(
+            gA, gO, A, plan, I, N);
+    };
+    if (rpl == 4)
+        launch(hpe_vjp_rows<T, K, 4>);
+    else if (rpl == 2)
+        launch(hpe_vjp_rows<T, K, 2>);
+    else
+        launch(hpe_vjp_rows<T, K, 1>);
     MOPS_CUDA_OK(cudaGetLastError());
     scratch_free(call, scratch);
 }

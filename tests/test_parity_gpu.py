@@ -113,10 +113,12 @@ def test_ragged_batch_sizes(oracle, I):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_hpe_large_batch(oracle, dtype):
-    """A batch large enough for the two-rows-per-lane HPE VJP (chosen when the batch still
-    fills the GPU that way), with a ragged last block."""
+    """Batches large enough for the two- and four-rows-per-lane HPE kernels (chosen when the
+    batch still fills the GPU that way), with ragged last blocks."""
     compare("hpe", workloads.hpe(I=148 * 64 * 8 + 37, N=17, J=60, K=3), dtype, oracle,
             what="hpe large batch")
+    compare("hpe", workloads.hpe(I=148 * 128 * 8 + 69, N=11, J=40, K=4), dtype, oracle,
+            what="hpe larger batch")
     compare("hpe", workloads.hpe(I=148 * 64 * 8 + 1, N=9, J=25, K=1), dtype, oracle,
             what="hpe large batch, K=1")
 
