@@ -2,7 +2,9 @@
 """Benchmark of the mops hot path on B200: forward + VJP of the five sparse operations.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload all|hpe|sap|opsa|opsa_f32|opsaw|sasaw] [--no-cpu-baseline]
+                    [--workload all|hpe|sap|opsa|opsa_f32|opsaw|sasaw]
+                    [--no-cpu-baseline] [--no-e2e] [--no-verify] [--no-small] [--no-strong]
+                    [--scale D [--keep-rows]]
 
 A step is one pass of the hot path over one batch of synthetic input: forward and VJP of
 every selected operation at its large configuration (per GPU):
@@ -14,21 +16,34 @@ every selected operation at its large configuration (per GPU):
     opsaw    f64  E=2^22 edges, 13x32, 2^16 nodes   (the reference's OPSAW shape, scaled up)
     sasaw    f64  E=2^22 edges, 9x32, 2^16 nodes, 500 coupling entries
 
-Metric: algorithmic GB/s (bytes each call must move, every input read once and every output
-written once, divided by device time), summed over all calls of a step and all GPUs. The
-per-operation numbers are in ``per_op``. ``e2e`` is the same pass starting and ending in
-HOST memory: every step copies each case's inputs from pinned host buffers to the device,
-calls forward and VJP through the public API (``mops_b200``) and copies every result back
-to pinned host buffers, all inside the timed region (copy-in, compute and copy-out streams
-chained by events, so copies in both directions and kernels overlap). With N > 1 every rank works on its own shard of the same size (weak scaling; rows
-and output-segment ranges are independent, so there is no collective on the data path
-except the all-reduce of grad_W for OPSAW/SASAW, whose W is replicated).
+``value``: algorithmic GB/s (bytes each call must move, every input read once and every
+output written once, divided by device time), summed over all calls of a step and all GPUs;
+inputs resident in HBM, CUDA events on the launching stream. ``per_op``: each operation's
+forward and VJP time, GB/s, fraction of the measured HBM peak, the resource that bounds it
+and the fraction of that resource, measured DRAM traffic (profiles/traffic.json).
+
+``e2e``: the same pass starting and ending in HOST memory through the package's public API:
+inside ``with mops_b200.HostQueue()`` every step calls forward and VJP of every case on
+pinned host arrays; the queue copies the operands in, runs the kernels and copies every
+result back to pinned host memory on three streams, all inside the timed region.
+
+``verified``: after timing, the very buffers that were timed are compared with the CPU
+oracle on sub-ranges (tests/subrange.py), outside the timed region.
+
+``small_configs``: call latency (median / p10 / p90 of >= 100 synchronous calls through the
+C ABI) at the five small configurations of BASELINE.json; no roofline for these.
+
+With N > 1 every rank first runs its own problem of the full per-GPU size (weak scaling, the
+headline), then all ranks split rank 0's problem (``strong``: batch rows / output-segment
+ranges cut by mops_b200.sharding, grad_W all-reduced) and report T(1)/T(N) per operation.
 
 ``--impl reference`` times the reference's own CPU implementation (oracle/_ref/libmops_ref.so,
-built from the unmodified reference sources; the C restatement if that is absent) on all
-host cores, on a bounded sample of the same workload.
+built from the unmodified reference sources; the C restatement if that is absent) with all
+host threads on the same configuration at its full size; because one such step takes many
+seconds it times at most 3 steps after 1 warm-up and says so in the line.
 """
 import argparse
+import ctypes
 import json
 import os
 import statistics
@@ -44,6 +59,7 @@ sys.path.insert(0, ROOT)
 from mops_b200 import workloads  # noqa: E402
 
 FALLBACK_HBM_GBS = 6650.0
+FP64_FLOP_PER_CLK_PER_SM = 128  # 64 DFMA lanes (or the same rate as DMMA) x 2
 
 # name -> (op, dtype, generator kwargs for the full per-GPU size, CPU sample divisor)
 CASES = {
@@ -54,48 +70,77 @@ CASES = {
     "opsaw": ("opsaw", np.float64, dict(E=1 << 22, n=1 << 16), 8),
     "sasaw": ("sasaw", np.float64, dict(E=1 << 22, n=1 << 16), 64),
 }
+# the configurations BASELINE.json lists (the generators' defaults): latency cases
+SMALL_CASES = {
+    "hpe": ("hpe", np.float64), "sap": ("sap", np.float64), "opsa": ("opsa", np.float64),
+    "opsa_f32": ("opsa", np.float32), "opsaw": ("opsaw", np.float64),
+    "sasaw": ("sasaw", np.float64),
+}
 BATCH_KEYS = {"hpe": ("I",), "sap": ("I",), "opsa": ("J", "nO"), "opsaw": ("E", "n"),
               "sasaw": ("E", "n")}
+ROW_KEYS = ("nO", "n")
+# what bounds each case on the SM: HBM bytes, shared-memory
+# wavefronts (every operand is a gather with a run-time index), or FP64 throughput
+BOUND = {"hpe": "smem", "sap": "smem", "opsa": "hbm", "opsa_f32": "hbm", "opsaw": "hbm",
+         "sasaw": "fp64"}
 # kernels of this library launched by one forward / one VJP call of every case (sorted input,
 # waiting calls): a table builder (plan, segment offsets, coupling) + the main kernel; the f32
 # OPSA VJP needs no table, the SASAW forward builds two
 LAUNCHES = {"hpe": (2, 2), "sap": (2, 2), "opsa": (2, 2), "opsa_f32": (2, 1), "opsaw": (2, 2),
             "sasaw": (3, 2)}
-# DRAM traffic per launch of the main kernel (dram__bytes_read.sum + dram__bytes_write.sum of
-# one ncu capture), by case and level. Captured with every batch dimension divided by 8 (the
-# full-size step is too large for a multi-pass capture) and multiplied by 8 here: all
-# operands and results of these kernels scale with the batch. The summaries under profiles/
-# hold the captured figures.
-MEASURED_TRAFFIC = {
-    ("hpe", "fwd"): 8 * 108.6e6, ("hpe", "vjp"): 8 * 193.5e6,
-    ("sap", "fwd"): 8 * 432.9e6, ("sap", "vjp"): 8 * 407.4e6,
-    ("opsa", "fwd"): 8 * 614.0e6, ("opsa", "vjp"): 8 * 1138.3e6,
-    ("opsa_f32", "fwd"): 8 * 304.7e6, ("opsa_f32", "vjp"): 8 * 554.5e6,
-    ("opsaw", "fwd"): 8 * 212.0e6, ("opsaw", "vjp"): 8 * 372.9e6,
-    ("sasaw", "fwd"): 8 * 209.2e6, ("sasaw", "vjp"): 8 * 409.8e6,
+
+OP_NAMES = {"hpe": "homogeneous_polynomial_evaluation", "sap": "sparse_accumulation_of_products",
+            "opsa": "outer_product_scatter_add", "opsaw": "outer_product_scatter_add_with_weights",
+            "sasaw": "sparse_accumulation_scatter_add_with_weights"}
+# C-ABI argument order (include/mops.h): outputs, grad_output, inputs, indices
+ABI = {
+    "hpe": (("output", "A", "C", "indices_A"),
+            ("grad_A", "grad_output", "A", "C", "indices_A")),
+    "sap": (("output", "A", "B", "C", "indices_A", "indices_B", "indices_output"),
+            ("grad_A", "grad_B", "grad_output", "A", "B", "C", "indices_A", "indices_B",
+             "indices_output")),
+    "opsa": (("output", "A", "B", "indices_output"),
+             ("grad_A", "grad_B", "grad_output", "A", "B", "indices_output")),
+    "opsaw": (("output", "A", "B", "W", "indices_W", "indices_output"),
+              ("grad_A", "grad_B", "grad_W", "grad_output", "A", "B", "W", "indices_W",
+               "indices_output")),
+    "sasaw": (("output", "A", "B", "C", "W", "indices_A", "indices_W_1", "indices_W_2",
+               "indices_output_1", "indices_output_2"),
+              ("grad_A", "grad_B", "grad_W", "grad_output", "A", "B", "C", "W", "indices_A",
+               "indices_W_1", "indices_W_2", "indices_output_1", "indices_output_2")),
 }
 
-
-def traffic(name, level):
-    t = MEASURED_TRAFFIC.get((name, level))
-    return None if t is None else t / SCALE
+SCALE = 1          # --scale N divides every batch dimension by N (small cases for ncu captures)
+KEEP_ROWS = False  # --keep-rows: --scale leaves the number of output rows / nodes alone
 
 
 def selected_cases(which):
     return list(CASES) if which == "all" else [which]
 
 
-SCALE = 1  # --scale N divides every batch dimension by N (small cases for ncu captures)
+def case_sizes(name, divisor=1):
+    op, _, kw, _ = CASES[name]
+    div = divisor * SCALE
+    return {k: (v // (1 if (KEEP_ROWS and k in ROW_KEYS) else div) if k in BATCH_KEYS[op] else v)
+            for k, v in kw.items()}
 
 
 def generate(name, rank, divisor=1):
-    op, dtype, kw, _ = CASES[name]
-    divisor *= SCALE
-    kw = {k: (v // divisor if k in BATCH_KEYS[op] else v) for k, v in kw.items()}
+    op, dtype, _, _ = CASES[name]
     seed = workloads.SEEDS[op] + 1000 * rank
-    if name == "opsa_f32":
-        seed = workloads.SEEDS["opsa"] + 1000 * rank
-    return workloads.GENERATORS[op](dtype=dtype, seed=seed, **kw)
+    return workloads.GENERATORS[op](dtype=dtype, seed=seed, **case_sizes(name, divisor))
+
+
+def output_shape(op, d):
+    if op == "hpe":
+        return (d["A"].shape[0],)
+    if op == "sap":
+        return (d["A"].shape[0], d["output_size"])
+    if op == "opsa":
+        return (d["output_size"], d["A"].shape[1], d["B"].shape[1])
+    if op == "opsaw":
+        return (d["W"].shape[0], d["A"].shape[1], d["B"].shape[1])
+    return (d["W"].shape[0], d["output_size"], d["B"].shape[1])
 
 
 # ------------------------------------------------------------------------------ call shapes
@@ -122,15 +167,26 @@ def vjp_args(op, d):
 
 def api(op):
     import mops_b200 as M
-    f = {"hpe": "homogeneous_polynomial_evaluation", "sap": "sparse_accumulation_of_products",
-         "opsa": "outer_product_scatter_add", "opsaw": "outer_product_scatter_add_with_weights",
-         "sasaw": "sparse_accumulation_scatter_add_with_weights"}[op]
-    return getattr(M, f), getattr(M, f + "_vjp")
+    return getattr(M, OP_NAMES[op]), getattr(M, OP_NAMES[op] + "_vjp")
+
+
+def named_results(op, out, grads):
+    grads = grads if isinstance(grads, tuple) else (grads,)
+    names = [n for n in ABI[op][1] if n.startswith("grad_") and n != "grad_output"]
+    res = {"output": out}
+    res.update(dict(zip(names, grads)))
+    return res
 
 
 def tensor_bytes(args):
     import torch
     return sum(a.numel() * a.element_size() for a in args if isinstance(a, torch.Tensor))
+
+
+def quantiles(xs):
+    xs = sorted(xs)
+    q = lambda p: xs[min(len(xs) - 1, int(p * len(xs)))]
+    return q(0.5), q(0.1), q(0.9)
 
 
 # ------------------------------------------------------------------------------ clocks
@@ -185,16 +241,34 @@ def physical_gpu_index(local):
 
 
 # ------------------------------------------------------------------------------ CPU arm
+def host_threads():
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
 def cpu_impl():
+    """The CPU implementation and the number of OpenMP threads it will really use. The thread
+    count is set explicitly (a launcher may have exported OMP_NUM_THREADS=1) both in the
+    environment, before the library loads, and through the OpenMP runtime it is linked to."""
+    want = host_threads()
+    os.environ["OMP_NUM_THREADS"] = str(want)
     from oracle import mops_oracle as mo
-    if mo.have_reference():
-        return mo.Reference(), "reference"
-    return mo.Oracle(), "port"
+    impl, kind = (mo.Reference(), "reference") if mo.have_reference() else (mo.Oracle(), "port")
+    threads = want
+    try:
+        gomp = ctypes.CDLL("libgomp.so.1")
+        gomp.omp_set_num_threads(ctypes.c_int(want))
+        threads = int(gomp.omp_get_max_threads())
+    except OSError:
+        pass
+    return impl, kind, threads
 
 
 def cpu_pass(impl, name, d):
     """Forward + VJP of one case on the CPU implementation; returns seconds (fwd, vjp)."""
-    op = CASES[name][0]
+    op = CASES[name][0] if name in CASES else name
     t0 = time.perf_counter()
     if op == "hpe":
         impl.hpe(d["A"], d["C"], d["indices_A"])
@@ -223,42 +297,143 @@ def cpu_pass(impl, name, d):
     return t1 - t0, t2 - t1
 
 
-def cpu_run(names, steps, warmup):
-    """Times the CPU implementation on a bounded sample (a 1/divisor-size draw of every case)."""
-    impl, kind = cpu_impl()
-    cores = os.cpu_count() or 1
-    os.environ.setdefault("OMP_NUM_THREADS", str(cores))
-    data, nbytes, sample = {}, 0, []
-    for n in names:
-        op, _, _, div = CASES[n]
-        data[n] = generate(n, 0, divisor=div)
-        nbytes += workloads.algorithmic_bytes(op, "fwd", data[n]) + \
-            workloads.algorithmic_bytes(op, "vjp", data[n])
-        sample.append(f"{n}: 1/{div}")
+def cpu_run(impl, kind, threads, names, steps, warmup, full):
+    """Times the CPU implementation on every case: at the full configured size (``full``) or
+    on a bounded sample (a 1/divisor-size draw of every case)."""
+    nbytes, sample = 0, []
     per_op = {n: [0.0, 0.0] for n in names}
     total = 0.0
-    for s in range(warmup + steps):
-        t_step = 0.0
-        for n in names:
-            f, v = cpu_pass(impl, n, data[n])
+    # one case at a time, so that only one case's arrays are alive
+    for n in names:
+        op, _, _, div = CASES[n]
+        div = 1 if full else div
+        d = generate(n, 0, divisor=div)
+        nbytes += workloads.algorithmic_bytes(op, "fwd", d) + workloads.algorithmic_bytes(op, "vjp", d)
+        sample.append(f"{n}: 1/{div}")
+        for s in range(warmup + steps):
+            f, v = cpu_pass(impl, n, d)
             if s >= warmup:
                 per_op[n][0] += f
                 per_op[n][1] += v
-            t_step += f + v
-        if s >= warmup:
-            total += t_step
-    ms = total / steps * 1e3
+                total += f + v
+        per_op[n] += [workloads.algorithmic_bytes(op, "fwd", d), workloads.algorithmic_bytes(op, "vjp", d)]
+        del d
     out_per_op = {}
     for n in names:
-        op = CASES[n][0]
-        bf = workloads.algorithmic_bytes(op, "fwd", data[n])
-        bv = workloads.algorithmic_bytes(op, "vjp", data[n])
-        out_per_op[n] = {"fwd_ms": per_op[n][0] / steps * 1e3, "vjp_ms": per_op[n][1] / steps * 1e3,
-                         "fwd_GBps": bf / (per_op[n][0] / steps) / 1e9,
-                         "vjp_GBps": bv / (per_op[n][1] / steps) / 1e9}
-    return {"value": nbytes / (total / steps) / 1e9, "unit": "GB/s", "cores": cores, "kind": kind,
-            "sample": "same generators at reduced batch: " + ", ".join(sample),
-            "ms_per_step": ms, "per_op": out_per_op}
+        f, v, bf, bv = per_op[n]
+        out_per_op[n] = {"fwd_ms": f / steps * 1e3, "vjp_ms": v / steps * 1e3,
+                         "fwd_GBps": bf / (f / steps) / 1e9, "vjp_GBps": bv / (v / steps) / 1e9}
+    what = "the full configured size of every case" if full else \
+        "same generators at reduced batch: " + ", ".join(sample)
+    return {"value": nbytes / (total / steps) / 1e9, "unit": "GB/s", "cores": threads,
+            "kind": kind, "sample": what + f"; {steps} timed step(s) after {warmup} warm-up",
+            "ms_per_step": total / steps * 1e3, "per_op": out_per_op}
+
+
+def cpu_small_configs(impl, kind, names):
+    """Call latency of the CPU implementation at the small configurations (full config, as
+    listed in BASELINE.json), through the reference's C ABI on preallocated arrays;
+    repetitions sized to about two seconds per call kind."""
+    out = {}
+    for n in names:
+        op, dtype = SMALL_CASES[n]
+        d = workloads.GENERATORS[op](dtype=dtype)
+        arrays = dict(d)
+        arrays["output"] = np.empty(output_shape(op, d), dtype)
+        for k in ("A", "B", "W"):
+            if k in d:
+                arrays["grad_" + k] = np.empty_like(d[k])
+        res = {}
+        for level, tag in ((0, "fwd"), (1, "vjp")):
+            if kind == "reference":
+                call = impl.prepared(op, "_vjp" if level else "", dtype,
+                                     *[arrays[k] for k in ABI[op][level]])
+            else:
+                call = (lambda: cpu_pass(impl, op, d))  # the port: forward and VJP together
+            call()
+            t0 = time.perf_counter()
+            call()
+            once = time.perf_counter() - t0
+            reps = int(max(5, min(100, 2.0 / max(once, 1e-6))))
+            ts = []
+            for _ in range(reps):
+                t0 = time.perf_counter()
+                call()
+                ts.append((time.perf_counter() - t0) * 1e6)
+            m, p10, p90 = quantiles(ts)
+            res.update({f"{tag}_us_median": m, f"{tag}_us_p10": p10, f"{tag}_us_p90": p90,
+                        f"{tag}_reps": reps})
+        out[n] = res
+    return out
+
+
+# ------------------------------------------------------------------------------ GPU, C ABI
+def abi_structs(op, level, tensors):
+    """ctypes structs of one C-ABI call on CUDA tensors (prototype order)."""
+    from mops_b200 import _lib
+    return [_lib.make_struct(tensors[k].data_ptr(), tensors[k].shape) for k in ABI[op][level]]
+
+
+def gpu_small_configs(names, dev):
+    """Call latency through the C ABI (mops_cuda_*: device pointers, complete on return) at
+    the small configurations: wall-clock time of >= 100 synchronous calls each."""
+    import torch
+    from mops_b200 import _lib
+    lib = _lib.library()
+    out = {}
+    for n in names:
+        op, dtype = SMALL_CASES[n]
+        d = workloads.GENERATORS[op](dtype=dtype)
+        t = {k: torch.from_numpy(v).to(dev) for k, v in d.items() if isinstance(v, np.ndarray)}
+        tdt = t["A"].dtype
+        t["output"] = torch.empty(output_shape(op, d), dtype=tdt, device=dev)
+        for k in ("A", "B", "W"):
+            if k in t:
+                t["grad_" + k] = torch.empty_like(t[k])
+        suffix = "f32" if dtype == np.float32 else "f64"
+        res = {}
+        for level, tag in ((0, "fwd"), (1, "vjp")):
+            fn = getattr(lib, f"mops_cuda_{OP_NAMES[op]}{'_vjp' if level else ''}_{suffix}")
+            structs = abi_structs(op, level, t)
+            fn.restype, fn.argtypes = ctypes.c_int, [type(s) for s in structs]
+            for _ in range(10):
+                _lib.check_status(fn(*structs))
+            torch.cuda.synchronize()
+            ts = []
+            for _ in range(200):
+                t0 = time.perf_counter()
+                status = fn(*structs)
+                ts.append((time.perf_counter() - t0) * 1e6)
+                _lib.check_status(status)
+            m, p10, p90 = quantiles(ts)
+            res.update({f"{tag}_us_median": m, f"{tag}_us_p10": p10, f"{tag}_us_p90": p90,
+                        f"{tag}_kernels": _lib.last_kernels()})
+        res["reps"] = 200
+        out[n] = res
+    return out
+
+
+# ------------------------------------------------------------------------------ traffic
+def load_traffic():
+    path = os.path.join(ROOT, "profiles", "traffic.json")
+    return json.load(open(path)) if os.path.exists(path) else {}
+
+
+def measured(traffic, name, level, launched):
+    """(DRAM bytes per launch, shared-memory wavefronts per launch) of the captured kernel,
+    scaled to this run's size, or (None, None, why) when the capture is of another
+    instantiation than the one this run launched."""
+    e = traffic.get(f"{name}/{level}")
+    if e is None:
+        return None, None, "no capture"
+    if not any(e["kernel"] in k for k in launched):
+        return None, None, f"capture is of {e['kernel']}, this run launched {'; '.join(launched)}"
+    if bool(e.get("keep_rows", False)) != KEEP_ROWS and SCALE != 1:
+        return None, None, "capture and run scale their output rows differently"
+    f = e["scale"] / SCALE
+    wf = e.get("smem_wavefronts")
+    return (e["dram_read_bytes"] + e["dram_write_bytes"]) * f, None if wf is None else wf * f, \
+        e.get("note")
 
 
 # ------------------------------------------------------------------------------ main
@@ -271,12 +446,23 @@ def main():
     ap.add_argument("--workload", default="all", choices=["all"] + list(CASES))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-verify", action="store_true",
+                    help="skip the oracle check of the timed buffers")
+    ap.add_argument("--no-small", action="store_true", help="skip the small-config latencies")
+    ap.add_argument("--no-strong", action="store_true",
+                    help="with N > 1: skip the strong-scaling leg")
     ap.add_argument("--no-spread", action="store_true",
-                    help="skip the per-call median / p10 / p90 measurement (also skipped with "
-                         "--no-e2e)")
+                    help="skip the per-call median / p10 / p90 measurement")
+    ap.add_argument("--quick", action="store_true",
+                    help="device-resident timing only (profiling runs)")
     ap.add_argument("--scale", type=int, default=1,
                     help="divide every batch dimension by this (small cases for profiling)")
+    ap.add_argument("--keep-rows", action="store_true",
+                    help="--scale leaves the number of output rows / nodes alone")
     args = ap.parse_args()
+    if args.quick:
+        args.no_cpu_baseline = args.no_e2e = args.no_verify = args.no_small = True
+        args.no_strong = args.no_spread = True
     # stdout carries exactly one JSON line: everything libraries print there (NCCL's version
     # banner, for one) is sent to stderr, and the line is written to the original descriptor.
     sys.stdout.flush()
@@ -287,17 +473,16 @@ def main():
         sys.stdout.flush()
         os.write(json_fd, (json.dumps(line) + "\n").encode())
 
-    global SCALE
-    SCALE = max(1, args.scale)
+    global SCALE, KEEP_ROWS
+    SCALE, KEEP_ROWS = max(1, args.scale), args.keep_rows
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     names = selected_cases(args.workload)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     config = {"workload": "fwd+vjp of " + ",".join(names) + " at the scaled per-GPU sizes" +
-              (f" divided by {SCALE}" if SCALE > 1 else ""),
-              "cases": {n: {**{k: int(v) // (SCALE if k in BATCH_KEYS[CASES[n][0]] else 1)
-                               for k, v in CASES[n][2].items()},
+              (f" divided by {SCALE}" + (" (rows kept)" if KEEP_ROWS else "") if SCALE > 1 else ""),
+              "cases": {n: {**{k: int(v) for k, v in case_sizes(n).items()},
                             "dtype": np.dtype(CASES[n][1]).name} for n in names},
               "sharding": "independent shard per rank (batch rows / output-segment ranges)",
               "cache": "inputs larger than L2 (126 MB) for every case"}
@@ -305,15 +490,22 @@ def main():
     if args.impl == "reference":
         if rank != 0:
             return 0
-        r = cpu_run(names, args.steps, max(args.warmup, 1))
+        impl, kind, threads = cpu_impl()
+        steps, warm = max(1, min(args.steps, 3)), max(1, min(args.warmup, 1))
+        r = cpu_run(impl, kind, threads, names, steps, warm, full=(SCALE == 1))
         line = {"impl": "reference", "metric": "algorithmic_GBps_fwd_plus_vjp", "value": r["value"],
-                "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+                "unit": "GB/s", "n_gpus": args.gpus, "steps": steps, "warmup": warm,
+                "steps_requested": args.steps, "warmup_requested": args.warmup,
+                "note": "one step of the CPU implementation at these sizes takes many seconds: "
+                        "at most 3 timed steps after 1 warm-up, whatever was requested",
                 "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "f64", "data": "synthetic", "config": config,
                 "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
                 "e2e": {"value": r["value"], "unit": "GB/s", "h2d_bytes_per_step": 0,
                         "d2h_bytes_per_step": 0},
                 "per_op": r["per_op"], "gpu_launches": 0}
+        if not args.no_small:
+            line["small_configs"] = cpu_small_configs(impl, kind, names)
         emit(line)
         return 0
 
@@ -329,13 +521,22 @@ def main():
         # keep stdout for the one JSON line: NCCL's version / debug lines go to stderr
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=dev)
+    from mops_b200 import _lib, sharding
+    import mops_b200 as M
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---- data: pinned host copies (e2e source) and device-resident copies
+    def max_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- data: pinned host copies (e2e source, checker input) and device-resident copies
     host, devd, nbytes = {}, {}, {}
     for n in names:
         op = CASES[n][0]
@@ -347,8 +548,9 @@ def main():
         devd[n] = {k: (v.to(dev) if isinstance(v, torch.Tensor) else v) for k, v in host[n].items()}
         del d
     reduce_gw = world > 1
+    launched = {}
 
-    def run_case(n, data, timers=None):
+    def run_case(n, data, timers=None, reduce=reduce_gw):
         op = CASES[n][0]
         fwd, vjp = api(op)
         if timers is not None:
@@ -356,8 +558,11 @@ def main():
         out = fwd(*fwd_args(op, data))
         if timers is not None:
             timers[1].record()
+            launched[(n, "fwd")] = _lib.last_kernels()
         grads = vjp(*vjp_args(op, data))
-        if reduce_gw and op in ("opsaw", "sasaw") and grads[2].is_cuda:
+        if timers is not None:
+            launched[(n, "vjp")] = _lib.last_kernels()
+        if reduce and op in ("opsaw", "sasaw") and grads[2].is_cuda:
             dist.all_reduce(grads[2])
         if timers is not None:
             timers[2].record()
@@ -375,98 +580,171 @@ def main():
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sampler.enabled = True
     start.record()
+    last = {}
     for s in range(args.steps):
         for i, n in enumerate(names):
-            run_case(n, devd[n], events[s][i])
+            last[n] = run_case(n, devd[n], events[s][i])
     stop.record()
     barrier()
     sampler.enabled = False
-    t_ms = start.elapsed_time(stop)
+    t_ms = max_over_ranks(start.elapsed_time(stop))
     per_op_ms = {n: [statistics.mean(events[s][i][0].elapsed_time(events[s][i][1])
                                      for s in range(args.steps)),
                      statistics.mean(events[s][i][1].elapsed_time(events[s][i][2])
                                      for s in range(args.steps))] for i, n in enumerate(names)}
-    if world > 1:
-        t = torch.tensor([t_ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        t_ms = float(t.item())
     step_bytes = sum(sum(nbytes[n]) for n in names)
     value = step_bytes * world * args.steps / (t_ms / 1e3) / 1e9
+
+    # ---- parity of the timed buffers (rank 0's), outside the timed region
+    verified = {}
+    if not args.no_verify and rank == 0 and SCALE == 1:
+        sys.path.insert(0, os.path.join(ROOT, "tests"))
+        import subrange
+        from oracle.mops_oracle import Oracle
+        oracle = Oracle()
+        for n in names:
+            op = CASES[n][0]
+            d = {k: (v.numpy() if isinstance(v, torch.Tensor) else v) for k, v in host[n].items()}
+            results = named_results(op, *last[n])
+
+            def library_vjp(sub, op=op):
+                t = {k: (torch.from_numpy(np.ascontiguousarray(v)).to(dev)
+                         if isinstance(v, np.ndarray) else v) for k, v in sub.items()}
+                return api(op)[1](*vjp_args(op, t))[2]
+
+            if reduce_gw and "grad_W" in results:
+                results = {k: v for k, v in results.items() if k != "grad_W"}  # summed over ranks
+            try:
+                report = subrange.check_case(oracle, op, d, results, inputs=devd[n],
+                                             library_vjp=library_vjp)
+                worst = max((r["max_abs_err"] / max(r["scale"], 1e-300) for r in report
+                             if r["n"] > 1), default=0.0)
+                verified[n] = {"verified": True, "comparisons": len(report),
+                               "worst_rel_to_max": worst}
+            except subrange.Mismatch as e:
+                verified[n] = {"verified": False, "error": str(e)}
+    last.clear()
 
     # ---- spread of every call: the same calls again, each one between its own pair of events
     # (outside the timed step; rank 0's view)
     spread = {}
-    if not (args.no_spread or args.no_e2e):  # quick / profiling runs skip it with the e2e leg
+    if not args.no_spread:
         reps = 20
         for n in names:
             ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(reps)]
             for r in range(reps):
-                run_case(n, devd[n], ev[r])
+                run_case(n, devd[n], ev[r], reduce=False)
             torch.cuda.synchronize()
-            f = sorted(e[0].elapsed_time(e[1]) for e in ev)
-            v = sorted(e[1].elapsed_time(e[2]) for e in ev)
-            q = lambda xs, p: xs[min(len(xs) - 1, int(p * len(xs)))]
-            spread[n] = {"reps": reps, "fwd_ms_median": q(f, 0.5), "fwd_ms_p10": q(f, 0.1),
-                         "fwd_ms_p90": q(f, 0.9), "vjp_ms_median": q(v, 0.5),
-                         "vjp_ms_p10": q(v, 0.1), "vjp_ms_p90": q(v, 0.9)}
+            fm, f10, f90 = quantiles([e[0].elapsed_time(e[1]) for e in ev])
+            vm, v10, v90 = quantiles([e[1].elapsed_time(e[2]) for e in ev])
+            spread[n] = {"reps": reps, "fwd_ms_median": fm, "fwd_ms_p10": f10, "fwd_ms_p90": f90,
+                         "vjp_ms_median": vm, "vjp_ms_p10": v10, "vjp_ms_p90": v90}
 
-    # ---- end to end: every step copies each case's inputs from pinned host memory to the
-    # device, calls forward and VJP through the public API and copies all results back into
-    # pinned host buffers. Three CUDA streams (copy in, compute, copy out) chained by events:
-    # the copies of different cases overlap each other (PCIe is full duplex) and the kernels.
+    # ---- strong scaling: all ranks split rank 0's problem
+    strong = None
+    if world > 1 and not args.no_strong:
+        strong = {}
+        for n in names:
+            op = CASES[n][0]
+            # rank 0's device-resident operands go to every rank over NCCL
+            full = {}
+            meta = [None]
+            if rank == 0:
+                meta = [{k: ((tuple(v.shape), str(v.dtype)) if isinstance(v, torch.Tensor) else v)
+                         for k, v in devd[n].items()}]
+            dist.broadcast_object_list(meta, src=0)
+            for k, m in meta[0].items():
+                if isinstance(m, tuple):
+                    if rank == 0:
+                        full[k] = devd[n][k]
+                    else:
+                        full[k] = torch.empty(m[0], dtype=getattr(torch, m[1].replace("torch.", "")),
+                                              device=dev)
+                    dist.broadcast(full[k], src=0)
+                else:
+                    full[k] = m
+            # cut: batch rows (HPE, SAP) or output-row ranges that balance the entries
+            if op in ("hpe", "sap"):
+                a, b = sharding.batch_range(full["A"].shape[0], world, rank)
+                per_row = ("A", "B", "grad_output")
+                shard = {k: (v[a:b].contiguous() if k in per_row and isinstance(v, torch.Tensor)
+                             else v) for k, v in full.items()}
+            else:
+                key = "indices_output_1" if op == "sasaw" else "indices_output"
+                n_rows = full["output_size"] if op == "opsa" else full["W"].shape[0]
+                cuts = [None]
+                if rank == 0:
+                    cuts = [sharding.segment_cuts(host[n][key].numpy(), n_rows, world)]
+                dist.broadcast_object_list(cuts, src=0)
+                rho, eps = cuts[0]
+                lo, hi = eps[rank], eps[rank + 1]
+                per_entry = ("A", "B", key, "indices_W", "indices_W_1")
+                shard = {k: (v[lo:hi].contiguous() if k in per_entry and isinstance(v, torch.Tensor)
+                             else v) for k, v in full.items()}
+                if op == "opsa":  # the output is sharded by rows: rebase the scatter index
+                    shard[key] = shard[key] - rho[rank]
+                    shard["output_size"] = rho[rank + 1] - rho[rank]
+                    shard["grad_output"] = full["grad_output"][rho[rank]:rho[rank + 1]].contiguous()
+            del full
+            for _ in range(2):
+                run_case(n, shard, reduce=False)
+            barrier()
+            ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+            for s in range(args.steps):
+                run_case(n, shard, ev[s], reduce=False)
+            torch.cuda.synchronize()
+            f = max_over_ranks(statistics.mean(e[0].elapsed_time(e[1]) for e in ev))
+            v = max_over_ranks(statistics.mean(e[1].elapsed_time(e[2]) for e in ev))
+            entry = {"fwd_ms_max_over_ranks": f, "vjp_ms_max_over_ranks": v}
+            if op in ("opsaw", "sasaw"):
+                # the one exchange step: the partial grad_W of every rank, summed
+                _, grads = run_case(n, shard, reduce=False)
+                barrier()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                dist.all_reduce(grads[2])
+                e1.record()
+                torch.cuda.synchronize()
+                entry["grad_W_allreduce_ms"] = max_over_ranks(e0.elapsed_time(e1))
+                entry["grad_W_bytes"] = grads[2].numel() * grads[2].element_size()
+            strong[n] = entry
+            del shard
+        barrier()
+
+    # ---- end to end: the public API on pinned host arrays inside a HostQueue
     e2e = None
     if not args.no_e2e:
-        s_in, s_run, s_out = (torch.cuda.Stream(device=dev) for _ in range(3))
-        host_out = {}
-
         def e2e_step():
-            staged, keep = [], []
-            with torch.cuda.stream(s_in):
+            keep = []
+            with M.HostQueue():
                 for n in names:
-                    data = {k: (v.to(dev, non_blocking=True) if isinstance(v, torch.Tensor) else v)
-                            for k, v in host[n].items()}
-                    ready = torch.cuda.Event()
-                    ready.record(s_in)
-                    staged.append((n, data, ready))
-            for n, data, ready in staged:
-                s_run.wait_event(ready)
-                with torch.cuda.stream(s_run):
-                    out, grads = run_case(n, data)
-                    done = torch.cuda.Event()
-                    done.record(s_run)
-                results = (out,) + tuple(grads if isinstance(grads, tuple) else (grads,))
-                if n not in host_out:
-                    host_out[n] = [torch.empty(r.shape, dtype=r.dtype, pin_memory=True)
-                                   for r in results]
-                s_out.wait_event(done)
-                with torch.cuda.stream(s_out):
-                    for r, h in zip(results, host_out[n]):
-                        h.copy_(r, non_blocking=True)
-                keep.append((data, results))  # device buffers stay alive until the step ends
-            s_out.synchronize()
-            s_run.synchronize()
+                    keep.append(run_case(n, host[n], reduce=False))
+            return keep
 
         torch.cuda.synchronize()
         for _ in range(3):
-            e2e_step()
+            res = e2e_step()
         h2d = sum(tensor_bytes(tuple(v for v in host[n].values() if isinstance(v, torch.Tensor)))
                   for n in names)
-        d2h = sum(tensor_bytes(tuple(host_out[n])) for n in names)
+        d2h = sum(tensor_bytes((out,) + tuple(g if isinstance(g, tuple) else (g,)))
+                  for out, g in res)
+        del res
         barrier()
         t0 = time.perf_counter()
         e2e_steps = max(1, min(args.steps, 3))
         for _ in range(e2e_steps):
             e2e_step()
         torch.cuda.synchronize()
-        t_e2e = time.perf_counter() - t0
-        if world > 1:
-            t = torch.tensor([t_e2e], device=dev, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            t_e2e = float(t.item())
+        t_e2e = max_over_ranks(time.perf_counter() - t0)
         e2e = {"value": step_bytes * world * e2e_steps / t_e2e / 1e9, "unit": "GB/s",
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-               "ms_per_step": t_e2e / e2e_steps * 1e3}
+               "ms_per_step": t_e2e / e2e_steps * 1e3,
+               "api": "mops_b200.<op>(pinned host arrays) inside mops_b200.HostQueue"}
     sampler.stop()
+
+    small = None
+    if not args.no_small and rank == 0 and SCALE == 1:
+        small = gpu_small_configs(names, dev)
 
     if rank != 0:
         if world > 1:
@@ -478,36 +756,76 @@ def main():
         peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured"
     else:
         peak, peak_src = FALLBACK_HBM_GBS, "fallback"
+    clocks = sampler.summary()
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    clk_hz = (clocks["sm_mhz"] or clocks["sm_max_mhz"] or 1965.0) * 1e6
+    traffic = load_traffic()
     per_op = {}
     dominant = None
     for n in names:
+        op = CASES[n][0]
         f_ms, v_ms = per_op_ms[n]
         bf, bv = nbytes[n]
         items = devd[n]["A"].shape[0]
-        per_op[n] = {"fwd_ms": f_ms, "vjp_ms": v_ms, "fwd_GBps": bf / f_ms / 1e6,
-                     "vjp_GBps": bv / v_ms / 1e6, "fwd_frac_of_hbm": bf / f_ms / 1e6 / peak,
-                     "vjp_frac_of_hbm": bv / v_ms / 1e6 / peak,
-                     "fwd_items_per_s": items / f_ms * 1e3, "vjp_items_per_s": items / v_ms * 1e3,
-                     "fwd_bytes": bf, "vjp_bytes": bv, **spread.get(n, {}),
-                     "fwd_traffic": traffic(n, "fwd"), "vjp_traffic": traffic(n, "vjp")}
+        entry = {"fwd_ms": f_ms, "vjp_ms": v_ms, "fwd_GBps": bf / f_ms / 1e6,
+                 "vjp_GBps": bv / v_ms / 1e6, "fwd_frac_of_hbm": bf / f_ms / 1e6 / peak,
+                 "vjp_frac_of_hbm": bv / v_ms / 1e6 / peak,
+                 "fwd_items_per_s": items / f_ms * 1e3, "vjp_items_per_s": items / v_ms * 1e3,
+                 "fwd_bytes": bf, "vjp_bytes": bv, "bound": BOUND[n], **spread.get(n, {})}
         for lvl, ms, b in (("fwd", f_ms, bf), ("vjp", v_ms, bv)):
+            k = launched.get((n, lvl), [])
+            entry[f"{lvl}_kernels"] = k
+            dram, wavefronts, note = measured(traffic, n, lvl, k)
+            entry[f"{lvl}_traffic"] = dram
+            if note:
+                entry[f"{lvl}_traffic_note"] = note
+            if BOUND[n] == "hbm":
+                entry[f"{lvl}_frac_of_bound"] = b / ms / 1e6 / peak
+            elif BOUND[n] == "smem":
+                # one shared-memory wavefront per clock per SM
+                entry[f"{lvl}_frac_of_bound"] = None if wavefronts is None else \
+                    wavefronts / (sms * clk_hz * ms / 1e3)
+            else:
+                hd = {k2: (v.numpy() if isinstance(v, torch.Tensor) else v)
+                      for k2, v in host[n].items()}
+                flops = workloads.useful_flops(op, lvl, hd)
+                entry[f"{lvl}_useful_GFLOP"] = flops / 1e9
+                entry[f"{lvl}_frac_of_bound"] = flops / (ms / 1e3) / \
+                    (sms * FP64_FLOP_PER_CLK_PER_SM * clk_hz)
             if dominant is None or ms > dominant[2]:
                 dominant = (n, lvl, ms, b)
+        if n in verified:
+            entry.update(verified[n])
+        if strong is not None and n in strong:
+            s = strong[n]
+            entry["strong"] = {**s, "n_gpus": world,
+                               "fwd_speedup_vs_1gpu": f_ms / s["fwd_ms_max_over_ranks"],
+                               "vjp_speedup_vs_1gpu": v_ms / s["vjp_ms_max_over_ranks"]}
+        per_op[n] = entry
     dn, dl, dms, db = dominant
-    roofline = {"bound": "hbm", "kernel": f"{dn} {dl}", "achieved": db / dms / 1e6, "peak": peak,
+    roofline = {"bound": "hbm", "kernel": f"{dn} {dl}: " + "; ".join(launched.get((dn, dl), [])),
+                "achieved": db / dms / 1e6, "peak": peak,
                 "peak_source": peak_src, "unit": "GB/s", "frac": db / dms / 1e6 / peak,
-                "traffic": traffic(dn, dl)}
+                "traffic": per_op[dn][f"{dl}_traffic"],
+                "binding_resource": BOUND[dn],
+                "frac_of_binding_resource": per_op[dn][f"{dl}_frac_of_bound"]}
     launches = sum(sum(LAUNCHES[n]) for n in names) * args.steps
     line = {"metric": "algorithmic_GBps_fwd_plus_vjp", "value": value, "unit": "GB/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": t_ms / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f64" if names != ["opsa_f32"] else "f32",
             "data": "synthetic", "config": config, "roofline": roofline, "per_op": per_op,
-            "clocks": sampler.summary(), "gpu_launches": launches, "peak_hbm_GBps": peak}
+            "clocks": clocks, "gpu_launches": launches, "peak_hbm_GBps": peak,
+            "fp64_peak_TFLOPs": sms * FP64_FLOP_PER_CLK_PER_SM * clk_hz / 1e12}
+    if verified:
+        line["verified"] = all(v["verified"] for v in verified.values())
     if e2e is not None:
         line["e2e"] = e2e
+    if small is not None:
+        line["small_configs"] = small
     if world == 1 and not args.no_cpu_baseline:
-        r = cpu_run(names, 1, 1)
+        impl, kind, threads = cpu_impl()
+        r = cpu_run(impl, kind, threads, names, 1, 1, full=False)
         line["cpu_baseline"] = {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")}
         line["cpu_baseline"]["per_op"] = r["per_op"]
     emit(line)

@@ -183,6 +183,17 @@ MOPS_EXPORT void* mops_b200_get_stream(void);
  * are then not reported by that call. Per thread. */
 MOPS_EXPORT void mops_b200_set_wait(int wait);
 MOPS_EXPORT int mops_b200_get_wait(void);
+/* Concurrency: any number of threads may call at the same time. The few status words through
+ * which the kernels report unsorted or out-of-range indices are kept per (calling thread,
+ * device, stream): calls that one thread issues on one stream run in order and share them
+ * safely; calls on different streams, which may overlap on the GPU when wait == 0, each have
+ * their own. Do not hand one thread's stream to mops_b200_set_stream of another thread while
+ * asynchronous calls of both are in flight on it unless the application orders them itself. */
+
+/* Names (with template arguments) of the main kernels the calling thread's last mops_cuda_*
+ * call dispatched to, "; "-separated; valid until that thread's next call. For tools that
+ * pair a timing with the profile of the same kernel instantiation. */
+MOPS_EXPORT const char* mops_b200_last_kernels(void);
 
 /* SASAW forward for callers that cannot allocate device memory at the time they call: a
  * host program whose own pool has reserved the whole device, where a cudaMalloc made by a
@@ -196,7 +207,8 @@ MOPS_EXPORT int mops_b200_get_wait(void);
  * beyond that it returns 1 with a message. All calls share the one array per GPU (held until
  * the process exits, about 100 KB), so calls whose GPU work overlaps race: serialise them.
  * The first call on each device looks up the array's address and must be made outside any
- * stream capture. Runs on the thread's stream (mops_b200_set_stream) and returns when done. */
+ * stream capture; the first launch of each kernel may also make the driver load its code.
+ * Runs on the thread's stream (mops_b200_set_stream) and returns when done. */
 MOPS_EXPORT int mops_b200_cuda_sparse_accumulation_scatter_add_with_weights_noalloc_f64(
     MOPS_ARGS_SASAW(f64));
 

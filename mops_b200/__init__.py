@@ -13,16 +13,23 @@ Accepted arrays
     run, and the result comes back as a host array of the same kind. This is the
     "host buffers in, host buffers out" path timed as ``e2e`` by ``bench.py``.
 
+  * Inside ``with mops_b200.HostQueue():`` calls on host arrays do not wait: their copies
+    in, kernels and copies out are queued on three CUDA streams and overlap across calls;
+    results are valid when the block ends.
+
 Differences from the reference front end: no CuPy dispatch (CuPy is replaced by torch CUDA
 tensors); OPSAW and SASAW run on the GPU instead of raising "CUDA implementation does not
 exist yet".
 """
+import threading
+
 import numpy as np
 
 from . import _lib
 from ._lib import MopsError  # noqa: F401
 
-__all__ = [f"{op}{lvl}" for op in _lib.OPERATIONS for lvl in _lib.LEVELS] + ["MopsError"]
+__all__ = [f"{op}{lvl}" for op in _lib.OPERATIONS for lvl in _lib.LEVELS] + ["MopsError",
+                                                                             "HostQueue"]
 
 
 def _torch():
@@ -72,6 +79,75 @@ def _check_scalar(value, operation, name):
         raise TypeError(f"`{name}` must be a scalar in {operation}, got {type(value)}")
 
 
+class HostQueue:
+    """Overlaps the host<->device traffic of consecutive calls on host arrays.
+
+    Inside ``with HostQueue() as q:`` every operation called with host arrays (NumPy arrays or
+    CPU torch tensors; pinned memory makes the copies asynchronous) is queued instead of
+    waited for: operands are copied in on one stream, the kernels run on a second, results
+    are copied out to pinned host memory on a third, chained by events. While one call
+    computes, the next call's operands arrive and the previous call's results leave (PCIe is
+    full duplex). A host array that several queued calls share (the operands of a forward and
+    of its VJP) is copied once. The arrays a call returns are filled when ``q.wait()``
+    returns or the block ends; until then their contents are undefined, and the operands
+    must not be modified. Like ``mops_b200_set_wait(0)``, queued calls do not report index
+    errors found on the device.
+    """
+
+    _local = threading.local()
+
+    def __init__(self, device=None):
+        torch = _torch()
+        if not torch.cuda.is_available():
+            raise MopsError("no CUDA device available")
+        index = torch.cuda.current_device() if device is None else torch.device(device).index
+        self.device = torch.device("cuda", index)
+        self.copy_in, self.compute, self.copy_out = (torch.cuda.Stream(device=self.device)
+                                                     for _ in range(3))
+        self._operands = {}  # (address, bytes, dtype) -> (device tensor, event, host array)
+        self._keep = []
+
+    @classmethod
+    def current(cls):
+        return getattr(cls._local, "queue", None)
+
+    def __enter__(self):
+        if HostQueue.current() is not None:
+            raise MopsError("HostQueue blocks do not nest")
+        HostQueue._local.queue = self
+        return self
+
+    def __exit__(self, *exc):
+        HostQueue._local.queue = None
+        self.wait()
+        return False
+
+    def wait(self):
+        """Returns when every queued call is complete and its results are in host memory."""
+        self.copy_out.synchronize()
+        self.compute.synchronize()
+        self.copy_in.synchronize()
+        self._operands.clear()
+        self._keep.clear()
+
+    def operand(self, host_tensor, convert=None):
+        """Device copy of a host tensor (made once per wait() period) and its ready event."""
+        torch = _torch()
+        key = (host_tensor.data_ptr(), host_tensor.numel() * host_tensor.element_size(),
+               host_tensor.dtype, convert)
+        hit = self._operands.get(key)
+        if hit is None:
+            with torch.cuda.stream(self.copy_in):
+                dev = host_tensor.to(self.device, non_blocking=True)
+                if convert is not None:
+                    dev = dev.to(convert)
+                ready = torch.cuda.Event()
+                ready.record(self.copy_in)
+            hit = (dev.contiguous(), ready, host_tensor)
+            self._operands[key] = hit
+        return hit[0], hit[1]
+
+
 class _Arena:
     """Moves one call's arrays to the device and its results back to where the inputs live."""
 
@@ -83,9 +159,14 @@ class _Arena:
         self.torch = torch
         self.numpy = isinstance(first, np.ndarray)
         self.pinned = (not self.numpy) and (not first.is_cuda) and first.is_pinned()
+        self.queue = None
         if self.numpy or not first.is_cuda:
-            self.device = torch.device("cuda", torch.cuda.current_device())
+            self.queue = HostQueue.current()
+            self.device = (self.queue.device if self.queue is not None
+                           else torch.device("cuda", torch.cuda.current_device()))
             self.host = True
+            self.ready = []
+            self.done = None
         else:
             self.device = first.device
             self.host = False
@@ -102,14 +183,28 @@ class _Arena:
         t = self.torch.from_numpy(np.ascontiguousarray(x)) if isinstance(x, np.ndarray) else x
         if t.dtype != self.dtype:
             raise TypeError("all floating-point arrays of one call must have the same dtype")
+        if self.queue is not None and not t.is_cuda:
+            dev, ready = self.queue.operand(t.contiguous())
+            self.ready.append(ready)
+            return dev
         return t.to(self.device, non_blocking=True).contiguous()
 
     def ints(self, x):
         t = self.torch.from_numpy(np.ascontiguousarray(x)) if isinstance(x, np.ndarray) else x
+        if self.queue is not None and not t.is_cuda:
+            dev, ready = self.queue.operand(t.contiguous(), convert=self.torch.int32)
+            self.ready.append(ready)
+            return dev
         return t.to(self.device, non_blocking=True).to(self.torch.int32).contiguous()
 
     def empty(self, shape):
-        return self.torch.empty(tuple(int(s) for s in shape), dtype=self.dtype, device=self.device)
+        shape = tuple(int(s) for s in shape)
+        if self.queue is not None:
+            with self.torch.cuda.stream(self.queue.compute):
+                t = self.torch.empty(shape, dtype=self.dtype, device=self.device)
+            self.queue._keep.append(t)
+            return t
+        return self.torch.empty(shape, dtype=self.dtype, device=self.device)
 
     def back(self, t):
         """Result to where the inputs live. Pinned host inputs get pinned host results (from
@@ -118,6 +213,13 @@ class _Arena:
             return None
         if not self.host:
             return t
+        if self.queue is not None:
+            q = self.queue
+            q.copy_out.wait_event(self.done)
+            with self.torch.cuda.stream(q.copy_out):
+                out = self.torch.empty(t.shape, dtype=t.dtype, device="cpu", pin_memory=True)
+                out.copy_(t, non_blocking=True)
+            return out.numpy() if self.numpy else out
         if self.pinned:
             out = self.torch.empty(t.shape, dtype=t.dtype, device="cpu", pin_memory=True)
             out.copy_(t, non_blocking=True)
@@ -136,6 +238,22 @@ class _Arena:
             else:
                 structs.append(_lib.make_struct(t.data_ptr(), t.shape))
         lib = _lib.library()
+        if self.queue is not None:
+            q = self.queue
+            for ready in self.ready:
+                q.compute.wait_event(ready)
+            with torch.cuda.device(self.device), torch.cuda.stream(q.compute):
+                previous, waited = lib.mops_b200_get_stream(), lib.mops_b200_get_wait()
+                lib.mops_b200_set_stream(q.compute.cuda_stream)
+                lib.mops_b200_set_wait(0)
+                try:
+                    _lib.call(f"mops_cuda_{name}_{self.suffix}", structs)
+                finally:
+                    lib.mops_b200_set_stream(previous)
+                    lib.mops_b200_set_wait(waited)
+                self.done = torch.cuda.Event()
+                self.done.record(q.compute)
+            return
         with torch.cuda.device(self.device):
             previous = lib.mops_b200_get_stream()
             lib.mops_b200_set_stream(torch.cuda.current_stream().cuda_stream)

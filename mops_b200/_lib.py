@@ -29,7 +29,7 @@ def abi_symbols():
 
 
 EXTENSION_SYMBOLS = ("mops_b200_set_stream", "mops_b200_get_stream", "mops_b200_set_wait",
-                     "mops_b200_get_wait", "mops_b200_version",
+                     "mops_b200_get_wait", "mops_b200_version", "mops_b200_last_kernels",
                      "mops_b200_cuda_sparse_accumulation_scatter_add_with_weights_noalloc_f64")
 
 
@@ -57,11 +57,18 @@ def library():
             getattr(lib, name)  # AttributeError here = incomplete ABI
         lib.mops_get_last_error_message.restype = ctypes.c_char_p
         lib.mops_b200_version.restype = ctypes.c_char_p
+        lib.mops_b200_last_kernels.restype = ctypes.c_char_p
         lib.mops_b200_set_stream.argtypes = [ctypes.c_void_p]
         lib.mops_b200_get_stream.restype = ctypes.c_void_p
         lib.mops_b200_set_wait.argtypes = [ctypes.c_int]
         _LIB = lib
     return _LIB
+
+
+def last_kernels():
+    """Main kernels (with template arguments) of this thread's last call, as a list."""
+    text = library().mops_b200_last_kernels().decode("utf8")
+    return [k for k in text.split("; ") if k]
 
 
 def last_error():

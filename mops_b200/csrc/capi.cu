@@ -156,4 +156,5 @@ extern "C" void mops_b200_set_stream(void* stream) { mops_b200::set_stream(strea
 extern "C" void* mops_b200_get_stream(void) { return mops_b200::get_stream(); }
 extern "C" void mops_b200_set_wait(int wait) { mops_b200::set_wait(wait != 0); }
 extern "C" int mops_b200_get_wait(void) { return mops_b200::get_wait() ? 1 : 0; }
+extern "C" const char* mops_b200_last_kernels(void) { return mops_b200::last_kernels(); }
 extern "C" const char* mops_b200_version(void) { return "mops-b200 0.1 (sm_100a)"; }

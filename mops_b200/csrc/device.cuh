@@ -2,11 +2,12 @@
 // sorted scatter index, the sortedness check, and reductions.
 //
 // Replaces mops/src/internal/cuda_utils.{cuh,cu} (atomic add with a pre-sm_60 fallback, the
-// shared-memory bump allocator) and mops/src/internal/cuda_first_occurences.cu (a separate
-// memset + kernel + device synchronisation that writes a first/last-occurrence table into a
-// cached global buffer before every scatter op). Here each warp finds the bounds of its own
-// output row with a 32-way search over the sorted index, so there is no table, no extra
-// launch and no synchronisation.
+// shared-memory bump allocator) and mops/src/internal/cuda_first_occurences.cu (a memset + a
+// kernel + a device synchronisation that write a first/last-occurrence table into a cached,
+// process-wide global buffer before every scatter op). Here `segment_offsets` writes the
+// table of segment starts in one launch on the call's stream (no memset, no synchronisation,
+// call-scoped or plan-owned memory) and checks order and range in the same pass; the
+// warp-wide search (`warp_segment`) serves the kernels that work without a table.
 #ifndef MOPS_B200_DEVICE_CUH
 #define MOPS_B200_DEVICE_CUH
 

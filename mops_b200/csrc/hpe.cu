@@ -534,6 +534,7 @@ void launch_fwd(const Call& call, T* O, const T* A, const T* C, const int32_t* P
     const size_t smem = two ? smem2 : fwd_smem<T, K>(N);
     void* scratch = nullptr;
     HpePlan plan = make_plan<T>(call, &scratch, C, P, J, K, N, true, false, two ? 65 : kPad);
+    note_kernel_f("hpe_fwd_rows<%s,K=%d,R=%d>", scalar_name<T>(), K, two ? 2 : 1);
     if (two) {
         auto kernel = hpe_fwd_rows<T, K, 2>;
         if (smem > 48 * 1024)
@@ -580,6 +581,7 @@ void launch_vjp(const Call& call, T* gA, const T* gO, const T* A, const T* C, co
         kernel<<<static_cast<unsigned>(ceil_div(I, 32 * rpl)), kWarps * 32, smem, call.stream>>>(
             gA, gO, A, plan, I, N);
     };
+    note_kernel_f("hpe_vjp_rows<%s,K=%d,R=%d>", scalar_name<T>(), K, rpl);
     if (rpl == 4)
         launch(hpe_vjp_rows<T, K, 4>);
     else if (rpl == 2)
@@ -618,6 +620,7 @@ void run_forward(const Call& call, T* O, const T* A, const T* C, const int32_t* 
         MOPS_B200_ORDER_SWITCH(K, CALL)
 #undef CALL
     } else {
+        note_kernel_f("hpe_fwd_wide<%s>", scalar_name<T>());
         hpe_fwd_wide<T><<<static_cast<unsigned>(ceil_div(I, 128)), 128, 0, call.stream>>>(
             O, A, C, P, I, N, J, K, call.status);
     }
@@ -633,6 +636,7 @@ void run_backward(const Call& call, T* gA, const T* gO, const T* A, const T* C, 
         MOPS_B200_ORDER_SWITCH(K, CALL)
 #undef CALL
     } else {
+        note_kernel_f("hpe_vjp_wide<%s>", scalar_name<T>());
         hpe_vjp_wide<T><<<static_cast<unsigned>(ceil_div(I, 128)), 128, 0, call.stream>>>(
             gA, gO, A, C, P, I, N, J, K, call.status);
     }

@@ -358,6 +358,8 @@ void launch_fwd_tile(const Call& call, const FwdPlan& plan, T* O, const T* A, co
                      const T* W, const int32_t* PW, const int64_t* offsets, int K, int L,
                      int64_t nO) {
     auto kernel = opsa_fwd_rows<T, TK, NV, VEC, WEIGHTED>;
+    note_kernel_f("opsa_fwd_rows<%s,TK=%d,NV=%d,VEC=%d,W=%d>", scalar_name<T>(), TK, NV, VEC,
+                  WEIGHTED ? 1 : 0);
     const size_t smem = plan.smem_per_warp * kFwdWarps;
     if (smem > 48 * 1024) {
         MOPS_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -524,6 +526,8 @@ void forward(const Call& call, T* O, const T* A, const T* B, const T* W, const i
             if (K <= 16 && L <= 32) {
                 const unsigned blocks = static_cast<unsigned>(
                     std::min<int64_t>(ceil_div(nO, 4), static_cast<int64_t>(sm_count(call.device)) * 4));
+                note_kernel_f("opsa_fwd_mma<MT=%d,NT=%d,W=%d>", K <= 8 ? 1 : 2, (L + 7) / 8,
+                              WEIGHTED ? 1 : 0);
                 if (K <= 8)
                     launch_fwd_mma_l<1, WEIGHTED>(L, blocks, call.stream, O, A, B, W, PW, offsets, K,
                                                   L, nO, call.status);
@@ -996,6 +1000,9 @@ void launch_vjp_mma(int K, int L, unsigned blocks, cudaStream_t stream, Args... 
 template <typename T, int KP, int VL, bool WEIGHTED, typename... Args>
 void launch_vjp_tile(const Call& call, const VjpPlan& plan, int64_t J, Args... args) {
     auto kernel = opsa_vjp_entries<T, KP, VL, WEIGHTED>;
+    if (!plan.only_if_unsorted)
+        note_kernel_f("opsa_vjp_entries<%s,KP=%d,VL=%d,W=%d>", scalar_name<T>(), KP, VL,
+                      WEIGHTED ? 1 : 0);
     if (plan.smem > 48 * 1024) {
         MOPS_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           static_cast<int>(plan.smem)));
@@ -1057,6 +1064,8 @@ void backward(const Call& call, T* gA, T* gB, T* gW, const T* gO, const T* A, co
                 P, J, nO, offsets, call.status);
             const unsigned blocks =
                 static_cast<unsigned>(std::min<int64_t>(ceil_div(nO, 4), sms * 3));
+            note_kernel_f("opsa_vjp_mma<%s,KT=%d,LT8=%d,W=%d>", scalar_name<T>(), (K + 3) / 4,
+                          (L + 7) / 8, WEIGHTED ? 1 : 0);
             launch_vjp_mma<T, WEIGHTED>(K, L, blocks, call.stream, gA, gB, gW, gO, A, B, W, PW,
                                         offsets, K, L, nO, nO, call.status);
             MOPS_CUDA_OK(cudaGetLastError());

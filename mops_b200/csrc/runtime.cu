@@ -1,5 +1,9 @@
+#include <cstdarg>
+#include <cstdio>
+#include <map>
 #include <mutex>
 #include <unordered_map>
+#include <utility>
 
 #include "runtime.hpp"
 
@@ -19,9 +23,12 @@ struct ThreadState {
     cudaStream_t stream = nullptr;
     bool wait = true;
     uint32_t epoch = 0;
-    // One status block per device this thread has used. The blocks are a few bytes and live
-    // until the process exits.
-    std::unordered_map<int, Status> blocks;
+    // One status block per (device, stream) this thread has used: calls on one stream run in
+    // order, so a call's words cannot be overwritten before its own kernels have read them,
+    // and calls on different streams (which may overlap) never share a block. The blocks are
+    // a few bytes and live until the process exits.
+    std::map<std::pair<int, cudaStream_t>, Status> blocks;
+    std::string kernels; // main kernels dispatched by the current / last call
 };
 
 thread_local ThreadState g_thread;
@@ -62,7 +69,9 @@ Call begin_call() {
     call.stream = g_thread.stream;
     call.wait = g_thread.wait;
 
-    auto it = g_thread.blocks.find(call.device);
+    g_thread.kernels.clear();
+    const auto key = std::make_pair(call.device, call.stream);
+    auto it = g_thread.blocks.find(key);
     if (it == g_thread.blocks.end()) {
         Status block{};
         void* host = nullptr;
@@ -76,7 +85,7 @@ Call begin_call() {
         MOPS_CUDA_OK(cudaMalloc(reinterpret_cast<void**>(&block.dev),
                                 kStatusWords * sizeof(uint32_t)));
         MOPS_CUDA_OK(cudaMemset(block.dev, 0, kStatusWords * sizeof(uint32_t)));
-        it = g_thread.blocks.emplace(call.device, block).first;
+        it = g_thread.blocks.emplace(key, block).first;
     }
     call.status = it->second;
     g_thread.epoch += 1;
@@ -84,6 +93,20 @@ Call begin_call() {
     call.status.epoch = g_thread.epoch;
     return call;
 }
+
+void note_kernel(const std::string& name) {
+    if (!g_thread.kernels.empty()) g_thread.kernels += "; ";
+    g_thread.kernels += name;
+}
+void note_kernel_f(const char* format, ...) {
+    char text[160];
+    va_list args;
+    va_start(args, format);
+    vsnprintf(text, sizeof(text), format, args);
+    va_end(args);
+    note_kernel(text);
+}
+const char* last_kernels() { return g_thread.kernels.c_str(); }
 
 void wait_stream(const Call& call) { MOPS_CUDA_OK(cudaStreamSynchronize(call.stream)); }
 

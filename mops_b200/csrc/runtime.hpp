@@ -52,8 +52,17 @@ struct Call {
     } while (0)
 
 // Starts a call on the calling thread's stream (default: the legacy default stream, like the
-// reference) for the current device; allocates that thread's status block on first use.
+// reference) for the current device; allocates that thread's status block for this
+// (device, stream) on first use.
 Call begin_call();
+
+// Which main kernels the calling thread's current call dispatched to, with their template
+// arguments ("hpe_vjp_rows<f64,K=4,R=4>"), so that a measurement can be paired with the
+// profile of the same instantiation. Cleared by begin_call.
+void note_kernel(const std::string& name);
+void note_kernel_f(const char* format, ...); // printf-style
+const char* last_kernels();
+template <typename T> inline const char* scalar_name() { return sizeof(T) == 8 ? "f64" : "f32"; }
 
 // True when the call found its scatter index unsorted (host view; only meaningful after the
 // stream has been synchronised).

@@ -807,6 +807,7 @@ bool forward_small(const Call& call, T* O, const T* A, const T* B, const T* C, c
     SmallPlan<T> plan = make_small_plan<T>(call, &scratch, C, PS, PT, PO, K, nS, nT, nO, NS, R + 1,
                                            0, b_small ? 1 : 0, b_small ? 0 : 1);
     const unsigned blocks = static_cast<unsigned>(ceil_div(I, R));
+    note_kernel_f("sap_fwd_small<%s,NS=%d> rows/block=%d", scalar_name<T>(), NS, R);
 #define MOPS_B200_LAUNCH(NS_)                                                                      \
     {                                                                                              \
         allow_smem(sap_fwd_small<T, NS_>, smem);                                                   \
@@ -842,6 +843,7 @@ bool backward_small(const Call& call, T* gA, T* gB, const T* gO, const T* A, con
     SmallPlan<T> plan = make_small_plan<T>(call, &scratch, C, PS, PT, PO, K, nS, nT, nO, NS, R + 1,
                                            1, b_small ? 1 : 0, b_small ? 0 : 1);
     const unsigned blocks = static_cast<unsigned>(ceil_div(I, R));
+    note_kernel_f("sap_vjp_small<%s,NS=%d> rows/block=%d", scalar_name<T>(), NS, R);
 #define MOPS_B200_LAUNCH(NS_)                                                                      \
     {                                                                                              \
         allow_smem(sap_vjp_small<T, NS_>, smem);                                                   \
@@ -914,6 +916,7 @@ void mops::cuda::sparse_accumulation_of_products(Tensor<scalar_t, 2> output, Ten
                                                   indices_B.data, indices_output.data, K, nA, nB,
                                                   nO, R + 1, true, false);
         auto kernel = in_smem ? sap_fwd_rows<scalar_t, true> : sap_fwd_rows<scalar_t, false>;
+        note_kernel_f("sap_fwd_rows<%s,smem=%d>", scalar_name<scalar_t>(), in_smem ? 1 : 0);
         allow_smem(kernel, smem);
         kernel<<<static_cast<unsigned>(ceil_div(I, R)), R, smem, call.stream>>>(
             output.data, A.data, B.data, plan, I, nA, nB, nO, static_cast<int>(K));

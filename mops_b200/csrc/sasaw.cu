@@ -1438,6 +1438,7 @@ bool forward_fast(const Call& call, T* O, const Problem<T>& p) {
     segment_offsets<<<static_cast<unsigned>(pre_blocks), 256, 0, call.stream>>>(
         p.Io, p.E, p.nW0, offsets, call.status);
     allow_smem(sasaw_fwd_fast<T, TP, NAP, true>, smem_seg);
+    note_kernel_f("sasaw_fwd_fast<%s,TP=%d,NAP=%d>", scalar_name<T>(), TP, NAP);
     sasaw_fwd_fast<T, TP, NAP, true><<<static_cast<unsigned>(ceil_div(p.nW0, warps_seg)),
                                        warps_seg * 32, smem_seg, call.stream>>>(
         O, p.A, p.B, p.W, p.Jw, p.Io, offsets, cp, p.E, p.nA, p.L, p.nW0, p.nW1, p.nO1, false,
@@ -1475,6 +1476,7 @@ bool backward_fast(const Call& call, T* gA, T* gB, T* gW, const T* gO, const Pro
     void* scratch = nullptr;
     if (!build_coupling(call, p, cp, &scratch, TP, ds)) return false;
     allow_smem(sasaw_vjp_fast<T, TP, NAP>, smem);
+    note_kernel_f("sasaw_vjp_fast<%s,TP=%d,NAP=%d>", scalar_name<T>(), TP, NAP);
     const int64_t blocks =
         std::min<int64_t>(ceil_div(p.E, warps), static_cast<int64_t>(sm_count(call.device)) * 16);
     sasaw_vjp_fast<T, TP, NAP><<<static_cast<unsigned>(blocks), warps * 32, smem, call.stream>>>(
@@ -1505,6 +1507,7 @@ template <typename T, int TP> bool forward_mma_launch(const Call& call, T* O, co
                              reinterpret_cast<uintptr_t>(p.B) % 16 == 0 &&
                              reinterpret_cast<uintptr_t>(O) % 16 == 0;
     allow_smem(sasaw_fwd_mma<TP, true>, smem);
+    note_kernel_f("sasaw_fwd_mma<TP=%d,SEG=1>", TP);
     const int64_t seg_blocks = std::min<int64_t>(ceil_div(p.nW0, warps), sms * 3);
     sasaw_fwd_mma<TP, true><<<static_cast<unsigned>(seg_blocks), warps * 32, smem, call.stream>>>(
         O, p.A, p.B, p.W, p.Jw, p.Io, offsets, cp, p.E, p.nA, p.L, p.nW0, p.nW1, p.nO1,
@@ -1555,6 +1558,7 @@ bool backward_mma_launch(const Call& call, T* gA, T* gB, T* gW, const T* gO, con
     void* scratch = nullptr;
     if (!build_coupling(call, p, cp, &scratch, Lay::TS, Lay::d_stride(p.nA), true)) return false;
     allow_smem(sasaw_vjp_mma<TP, KS3>, smem);
+    note_kernel_f("sasaw_vjp_mma<TP=%d,KS3=%d>", TP, KS3);
     const bool wide_copies = p.L % 2 == 0 && reinterpret_cast<uintptr_t>(p.W) % 16 == 0 &&
                              reinterpret_cast<uintptr_t>(p.B) % 16 == 0;
     const int64_t blocks = std::min<int64_t>(ceil_div(ceil_div(p.E, 8), warps),
@@ -1890,6 +1894,16 @@ void forward_noalloc(double* O, const Problem<double>& p) {
             std::to_string(kNoAllocMaxCells) + " (output_size x W.shape[1]) cells; got " +
             std::to_string(p.N) + " and " + std::to_string(ncell) +
             ". Use mops_cuda_sparse_accumulation_scatter_add_with_weights_f64 instead");
+    }
+    if (ncell == 0 && rowsize > 0 && p.nW0 > 0 && p.E > 0 && p.N > 0) {
+        // W.shape[1] == 0 with a non-empty coupling table: every indices_W_2 entry is out of
+        // range. The regular entry point reports the same (its table builder stands down and
+        // the entry-wise kernel finds the bad indices); here it is decided on the host, before
+        // any launch, because the grouping kernel cannot run on an empty cell grid.
+        throw std::runtime_error(
+            "Index array indices_W_2 in operation "
+            "cuda_sparse_accumulation_scatter_add_with_weights (allocation-free) contains "
+            "negative or too large elements; this would cause out-of-bounds accesses");
     }
     Call call;
     unsigned char* base = noalloc_scratch_for_current_device(&call.device);

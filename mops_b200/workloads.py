@@ -124,3 +124,24 @@ def algorithmic_bytes(op, level, w):
 def items(op, w):
     """Units one call processes: batch rows for HPE/SAP, entries (edges) for the scatter ops."""
     return w["A"].shape[0]
+
+
+def useful_flops(op, level, w):
+    """Floating-point operations one call needs when the work is organised the way the kernels
+    organise it (multiply-add = 2). Only SASAW differs from the naive count: the coupling table
+    is first contracted with the edge's A row into a dense nO2 x nW2 matrix T_e (2*cells*nA),
+    which is then applied to the 32-wide rows (2*nO2*nW2*L per product)."""
+    if op != "sasaw":
+        raise KeyError(op)
+    E, nA = w["A"].shape
+    L = w["B"].shape[1]
+    nW2, nO2 = w["W"].shape[1], w["output_size"]
+    cells = nW2 * nO2
+    contract = 2 * cells * nA          # T_e = D a_e   (and grad_A_e = D^T U_e)
+    product = 2 * cells * L            # one nO2 x nW2 by nW2 x L product (or its transposes)
+    scale_b = nW2 * L                  # B[e,:] * W[J_e]
+    if level == "fwd":
+        return E * (contract + product + scale_b)
+    # VJP: T_e, X = T_e^T gO (grad_B, grad_W), U = gO (B*W)^T, grad_A = D^T U, and the
+    # element-wise products that turn X into grad_B / grad_W
+    return E * (2 * contract + 2 * product + 3 * scale_b)

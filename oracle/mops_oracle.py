@@ -234,6 +234,21 @@ class Reference:
         if status != 0:
             raise ReferenceError_(self.lib.mops_get_last_error_message().decode())
 
+    def prepared(self, op, level, dtype, *args):
+        """A zero-argument callable that makes the same C-ABI call on preallocated arrays
+        again and again (for timing: no struct building or allocation per call)."""
+        sym = f"{self.prefix}{self.NAMES[op]}{level}_{_SUFFIX[np.dtype(dtype)]}"
+        fn = getattr(self.lib, sym)
+        fn.restype = ctypes.c_int
+        structs = [_as_struct(a) for a in args]
+        fn.argtypes = [type(s) for s in structs]
+
+        def call():
+            if fn(*structs) != 0:
+                raise ReferenceError_(self.lib.mops_get_last_error_message().decode())
+        call.keep = args  # the arrays must outlive the callable
+        return call
+
     def hpe(self, A, C, P):
         A, C, P = _c(A), _c(C), _i32(P)
         O = np.empty(A.shape[0], A.dtype)

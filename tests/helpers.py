@@ -20,8 +20,9 @@ def host(x):
     return None if x is None else x.cpu().numpy()
 
 
-def run_library(op, d, second_order=False):
-    """All levels of ``op`` on a dict of CUDA tensors -> {name: numpy array}."""
+def run_library(op, d, second_order=False, to_host=True):
+    """All levels of ``op`` on a dict of CUDA tensors -> {name: numpy array} (or the CUDA
+    tensors themselves with ``to_host=False``)."""
     import mops_b200 as M
     out = {}
     if op == "hpe":
@@ -68,7 +69,7 @@ def run_library(op, d, second_order=False):
                 d["grad_output"], d["A"], d["B"], d["C"], d["W"], *idx)
     else:
         raise KeyError(op)
-    return {k: host(v) for k, v in out.items()}
+    return {k: host(v) for k, v in out.items()} if to_host else out
 
 
 def run_checker(impl, op, d, dtype, second_order=False):

@@ -83,6 +83,11 @@ def test_sasaw_full_small_config(oracle):
     compare("sasaw", workloads.sasaw(), np.float64, oracle)
 
 
+def test_sasaw_full_small_config_against_reference_library(reference):
+    """The same full shape against the unmodified reference CPU library."""
+    compare("sasaw", workloads.sasaw(), np.float64, reference)
+
+
 # ---------------------------------------------------------------- edge cases
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("K", list(range(0, 11)))
@@ -321,6 +326,68 @@ def test_host_arrays_round_trip(oracle):
     out = M.outer_product_scatter_add(d["A"], d["B"], d["indices_output"], 50)
     assert isinstance(out, np.ndarray)
     assert_parity(out, oracle.opsa(d["A"], d["B"], d["indices_output"], 50), "numpy opsa")
+
+
+def test_host_queue_overlaps_calls_and_matches_the_oracle(oracle):
+    """Host arrays through ``HostQueue``: forward and VJP of three operations queued back to
+    back (shared operands copied once), results valid after the block; NumPy and pinned
+    torch inputs."""
+    import torch
+    import mops_b200 as M
+    d1, d2, d3 = workloads.opsa(J=5000, nO=80), workloads.sap(I=300), workloads.sasaw(E=900, n=30)
+    pin = lambda d: {k: (torch.from_numpy(v).pin_memory() if isinstance(v, np.ndarray) else v)
+                     for k, v in d.items()}
+    p2 = pin(d2)
+    with M.HostQueue() as q:
+        O1 = M.outer_product_scatter_add(d1["A"], d1["B"], d1["indices_output"], 80)
+        gA1, gB1 = M.outer_product_scatter_add_vjp(d1["grad_output"], d1["A"], d1["B"],
+                                                   d1["indices_output"])
+        idx = (p2["indices_A"], p2["indices_B"], p2["indices_output"])
+        O2 = M.sparse_accumulation_of_products(p2["A"], p2["B"], p2["C"], *idx, 50)
+        gA2, gB2 = M.sparse_accumulation_of_products_vjp(p2["grad_output"], p2["A"], p2["B"],
+                                                         p2["C"], *idx)
+        i3 = (d3["indices_A"], d3["indices_W_1"], d3["indices_W_2"], d3["indices_output_1"],
+              d3["indices_output_2"])
+        O3 = M.sparse_accumulation_scatter_add_with_weights(d3["A"], d3["B"], d3["C"], d3["W"],
+                                                            *i3, 9)
+        g3 = M.sparse_accumulation_scatter_add_with_weights_vjp(d3["grad_output"], d3["A"],
+                                                                d3["B"], d3["C"], d3["W"], *i3)
+        assert len(q._operands) == 4 + 7 + 10  # every distinct host array is copied once
+    assert isinstance(O1, np.ndarray) and isinstance(O2, torch.Tensor) and O2.is_pinned()
+    w1 = run_checker(oracle, "opsa", d1, np.float64)
+    w2 = run_checker(oracle, "sap", d2, np.float64)
+    w3 = run_checker(oracle, "sasaw", d3, np.float64)
+    for got, want, what in ((O1, w1["output"], "O1"), (gA1, w1["grad_A"], "gA1"),
+                            (gB1, w1["grad_B"], "gB1"), (O2.numpy(), w2["output"], "O2"),
+                            (gA2.numpy(), w2["grad_A"], "gA2"), (gB2.numpy(), w2["grad_B"], "gB2"),
+                            (O3, w3["output"], "O3"), (g3[0], w3["grad_A"], "gA3"),
+                            (g3[1], w3["grad_B"], "gB3"), (g3[2], w3["grad_W"], "gW3")):
+        assert_parity(got, want, "host queue " + what)
+    # outside a queue the same call is synchronous again
+    out = M.outer_product_scatter_add(d1["A"], d1["B"], d1["indices_output"], 80)
+    assert_parity(out, w1["output"], "after the queue")
+
+
+# ---------------------------------------------------------------- the timed configurations
+@pytest.mark.parametrize("name", ["hpe", "sap", "opsa", "opsa_f32", "opsaw", "sasaw"])
+def test_timed_configurations_against_oracle_subranges(oracle, name):
+    """The six configurations bench.py times, at their full per-GPU size (I = 2^20 / 2^22
+    rows, J = 2^24 entries, E = 2^22 edges over 2^16 nodes): blocks of rows / output segments
+    against the oracle, grad_W on a 2^16-edge slice of the same problem, and the adjoint
+    identity over the whole result (tests/subrange.py). 1e-12 (f64) / 1e-5 (f32) of the
+    largest magnitude of each compared block."""
+    import bench
+    import subrange
+    op, dtype = bench.CASES[name][0], bench.CASES[name][1]
+    d = bench.generate(name, 0)
+    t = to_dev(d, dtype)
+    results = run_library(op, t, to_host=False)
+
+    def library_vjp(sub):
+        return run_library(op, to_dev(sub, dtype), to_host=False)["grad_W"]
+
+    report = subrange.check_case(oracle, op, d, results, inputs=t, library_vjp=library_vjp)
+    assert len(report) >= 6, report
 
 
 # ---------------------------------------------------------------- full-size properties
