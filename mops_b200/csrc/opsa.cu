@@ -26,7 +26,9 @@
 // warp-wide broadcasts because neighbouring entries share an output row. Results are
 // staged back in place and written with coalesced stores; gW is accumulated with RED.
 #include <algorithm>
+#include <cstdlib>
 
+#include "bulk.cuh"
 #include "checks.hpp"
 #include "device.cuh"
 
@@ -64,6 +66,8 @@ template <typename T, int N> __device__ __forceinline__ void store_vec(T* p, con
     for (int i = 0; i < N; i++) u.s[i] = in[i];
     *reinterpret_cast<V*>(p) = u.v;
 }
+
+#include "opsa_pipe.cuh"
 
 // ------------------------------------------------------------------------------ forward
 struct FwdPlan {
@@ -496,6 +500,121 @@ void launch_fwd_mma_l(int L, unsigned blocks, cudaStream_t stream, Args... args)
     }
 }
 
+// ------------------------------------------------------------- streaming kernels, host side
+// Tuning overrides (development aid): MOPS_B200_PIPE=0 turns the streaming kernels off,
+// MOPS_B200_PIPE_CH / MOPS_B200_PIPE_STAGES change the ring geometry.
+inline int env_int(const char* name, int fallback) {
+    const char* v = std::getenv(name);
+    return v != nullptr && *v != '\0' ? std::atoi(v) : fallback;
+}
+
+template <typename T, bool WEIGHTED>
+bool pipe_usable(const T* A, const T* B, const T* W, const void* extra, int K, int L, bool vjp) {
+    auto aligned = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+    if (env_int("MOPS_B200_PIPE", 1) == 0) return false;
+    if (K < 1 || K > 16 || L < 1 || L > 32) return false;
+    if (!aligned(A) || !aligned(B) || !aligned(extra)) return false;
+    if (WEIGHTED && (!aligned(W) || (L * sizeof(T)) % 16 != 0)) return false;
+    if (vjp && (static_cast<size_t>(K) * L * sizeof(T)) % 16 != 0) return false;
+    return true;
+}
+
+template <typename T, bool WEIGHTED> PipeLayout choose_pipe_layout(int K, int L, bool vjp) {
+    // Two stages of 32 entries per warp measured best (f64 OPSA forward 0.91 ms, VJP 1.64 ms
+    // against 0.97 / 1.85 with three stages of 16): the smaller ring lets more warps share an
+    // SM, and one chunk in flight per warp already keeps about 100 KB per SM in flight.
+    int ch = env_int("MOPS_B200_PIPE_CH", 32), stages = env_int("MOPS_B200_PIPE_STAGES", 2);
+    ch = std::max(4, std::min(32, ch / 4 * 4));
+    stages = std::max(2, std::min(8, stages));
+    return pipe_layout(sizeof(T), K, L, WEIGHTED, vjp, ch, stages);
+}
+
+template <typename Kernel>
+unsigned pipe_grid(const Call& call, Kernel kernel, size_t smem, int64_t nO) {
+    if (smem > 48 * 1024)
+        MOPS_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          static_cast<int>(smem)));
+    int per_sm = 0;
+    MOPS_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kPipeWarps * 32, smem));
+    per_sm = std::max(1, per_sm);
+    return static_cast<unsigned>(std::min<int64_t>(
+        ceil_div(nO, kPipeWarps), static_cast<int64_t>(sm_count(call.device)) * per_sm));
+}
+
+template <typename T, int MT, bool WEIGHTED, typename... Args>
+void launch_fwd_pipe_l(const Call& call, const PipeLayout& lay, int64_t nO, Args... args) {
+    const size_t smem = static_cast<size_t>(lay.warp_bytes) * kPipeWarps;
+#define MOPS_B200_CASE(NT_)                                                                        \
+    {                                                                                              \
+        auto kernel = opsa_fwd_pipe<T, MT, NT_, WEIGHTED>;                                         \
+        const unsigned blocks = pipe_grid(call, kernel, smem, nO);                                 \
+        kernel<<<blocks, kPipeWarps * 32, smem, call.stream>>>(args..., lay, call.status);         \
+    }
+    switch ((lay.L + 7) / 8) {
+    case 1: MOPS_B200_CASE(1) break;
+    case 2: MOPS_B200_CASE(2) break;
+    case 3: MOPS_B200_CASE(3) break;
+    default: MOPS_B200_CASE(4) break;
+    }
+#undef MOPS_B200_CASE
+}
+
+// Forward through the streaming kernel; false when it does not apply (the caller then takes
+// another kernel).
+template <typename T, bool WEIGHTED>
+bool forward_pipe(const Call& call, T* O, const T* A, const T* B, const T* W, const int32_t* PW,
+                  const int64_t* offsets, int64_t J, int K, int L, int64_t nO) {
+    if (!pipe_usable<T, WEIGHTED>(A, B, W, nullptr, K, L, false)) return false;
+    const PipeLayout lay = choose_pipe_layout<T, WEIGHTED>(K, L, false);
+    if (static_cast<size_t>(lay.warp_bytes) * kPipeWarps > static_cast<size_t>(max_optin_smem(call.device)))
+        return false;
+    note_kernel_f("opsa_fwd_pipe<%s,MT=%d,NT=%d,W=%d> ch=%d stages=%d", scalar_name<T>(),
+                  K <= 8 ? 1 : 2, (L + 7) / 8, WEIGHTED ? 1 : 0, lay.ch, lay.stages);
+    if (K <= 8)
+        launch_fwd_pipe_l<T, 1, WEIGHTED>(call, lay, nO, O, A, B, W, PW, offsets, J, nO, nO);
+    else
+        launch_fwd_pipe_l<T, 2, WEIGHTED>(call, lay, nO, O, A, B, W, PW, offsets, J, nO, nO);
+    MOPS_CUDA_OK(cudaGetLastError());
+    return true;
+}
+
+template <typename T, int KT, bool WEIGHTED, typename... Args>
+void launch_vjp_pipe_l(const Call& call, const PipeLayout& lay, int64_t nO, Args... args) {
+    const size_t smem = static_cast<size_t>(lay.warp_bytes) * kPipeWarps;
+#define MOPS_B200_CASE(LT_)                                                                        \
+    {                                                                                              \
+        auto kernel = opsa_vjp_pipe<T, KT, LT_, WEIGHTED>;                                         \
+        const unsigned blocks = pipe_grid(call, kernel, smem, nO);                                 \
+        kernel<<<blocks, kPipeWarps * 32, smem, call.stream>>>(args..., lay, call.status);         \
+    }
+    switch ((lay.L + 7) / 8) {
+    case 1: MOPS_B200_CASE(1) break;
+    case 2: MOPS_B200_CASE(2) break;
+    case 3: MOPS_B200_CASE(3) break;
+    default: MOPS_B200_CASE(4) break;
+    }
+#undef MOPS_B200_CASE
+}
+
+template <typename T, bool WEIGHTED>
+bool backward_pipe(const Call& call, T* gA, T* gB, T* gW, const T* gO, const T* A, const T* B,
+                   const T* W, const int32_t* PW, const int64_t* offsets, int64_t J, int K, int L,
+                   int64_t nO) {
+    const PipeLayout lay = choose_pipe_layout<T, WEIGHTED>(K, L, true);
+    if (static_cast<size_t>(lay.warp_bytes) * kPipeWarps > static_cast<size_t>(max_optin_smem(call.device)))
+        return false;
+    note_kernel_f("opsa_vjp_pipe<%s,KT=%d,LT8=%d,W=%d> ch=%d stages=%d", scalar_name<T>(),
+                  (K + 3) / 4, (L + 7) / 8, WEIGHTED ? 1 : 0, lay.ch, lay.stages);
+    switch ((K + 3) / 4) {
+    case 1: launch_vjp_pipe_l<T, 1, WEIGHTED>(call, lay, nO, gA, gB, gW, gO, A, B, W, PW, offsets, J, nO, nO); break;
+    case 2: launch_vjp_pipe_l<T, 2, WEIGHTED>(call, lay, nO, gA, gB, gW, gO, A, B, W, PW, offsets, J, nO, nO); break;
+    case 3: launch_vjp_pipe_l<T, 3, WEIGHTED>(call, lay, nO, gA, gB, gW, gO, A, B, W, PW, offsets, J, nO, nO); break;
+    default: launch_vjp_pipe_l<T, 4, WEIGHTED>(call, lay, nO, gA, gB, gW, gO, A, B, W, PW, offsets, J, nO, nO); break;
+    }
+    MOPS_CUDA_OK(cudaGetLastError());
+    return true;
+}
+
 template <typename T, bool WEIGHTED>
 void forward(const Call& call, T* O, const T* A, const T* B, const T* W, const int32_t* PW,
              const int32_t* P, int64_t J, int K, int L, int64_t nO) {
@@ -520,8 +639,9 @@ void forward(const Call& call, T* O, const T* A, const T* B, const T* W, const i
             P, J, nO, offsets, call.status);
         MOPS_CUDA_OK(cudaGetLastError());
         constexpr int widest = 16 / static_cast<int>(sizeof(T));
-        bool on_tensor_cores = false;
+        bool on_tensor_cores = forward_pipe<T, WEIGHTED>(call, O, A, B, W, PW, offsets, J, K, L, nO);
         if constexpr (sizeof(T) == 8 && WEIGHTED) {
+            if (!on_tensor_cores)
             // (without weights the staged kernel below measured as fast: 1.24 against 1.26 ms)
             if (K <= 16 && L <= 32) {
                 const unsigned blocks = static_cast<unsigned>(
@@ -1052,24 +1172,33 @@ void backward(const Call& call, T* gA, T* gB, T* gW, const T* gO, const T* A, co
 
     VjpPlan plan;
     plan.only_if_unsorted = false;
-    if constexpr (sizeof(T) == 8) { // (f32 widened to f64 here measured slower: 2.4 against 2.06 ms)
-        if (K <= 16 && L <= 32) {
-            // Sorted scatter index (checked on the device): one warp per output row on the
-            // tensor-core path; otherwise the entry-per-lane kernels below do the work.
-            const int sms = sm_count(call.device);
-            int64_t* offsets =
-                static_cast<int64_t*>(scratch_alloc(call, (nO + 1) * sizeof(int64_t)));
-            const int64_t pre_blocks = std::min<int64_t>(ceil_div(J + 1, 256), sms * 32);
-            segment_offsets<<<static_cast<unsigned>(pre_blocks), 256, 0, call.stream>>>(
-                P, J, nO, offsets, call.status);
-            const unsigned blocks =
-                static_cast<unsigned>(std::min<int64_t>(ceil_div(nO, 4), sms * 3));
-            note_kernel_f("opsa_vjp_mma<%s,KT=%d,LT8=%d,W=%d>", scalar_name<T>(), (K + 3) / 4,
-                          (L + 7) / 8, WEIGHTED ? 1 : 0);
-            launch_vjp_mma<T, WEIGHTED>(K, L, blocks, call.stream, gA, gB, gW, gO, A, B, W, PW,
-                                        offsets, K, L, nO, nO, call.status);
-            MOPS_CUDA_OK(cudaGetLastError());
-            scratch_free(call, offsets);
+    // Sorted scatter index (checked on the device): the streaming tensor-core kernel, or for
+    // f64 operands it cannot take (alignment) the kernel that loads its fragments from global
+    // memory; otherwise, and whenever the index turns out unsorted, the entry-per-lane kernels
+    // below do the work.
+    const bool streaming = pipe_usable<T, WEIGHTED>(A, B, W, gO, K, L, true);
+    if (K <= 16 && L <= 32 && (streaming || sizeof(T) == 8)) {
+        const int sms = sm_count(call.device);
+        int64_t* offsets = static_cast<int64_t*>(scratch_alloc(call, (nO + 1) * sizeof(int64_t)));
+        const int64_t pre_blocks = std::min<int64_t>(ceil_div(J + 1, 256), sms * 32);
+        segment_offsets<<<static_cast<unsigned>(pre_blocks), 256, 0, call.stream>>>(
+            P, J, nO, offsets, call.status);
+        bool launched = streaming && backward_pipe<T, WEIGHTED>(call, gA, gB, gW, gO, A, B, W, PW,
+                                                                offsets, J, K, L, nO);
+        if constexpr (sizeof(T) == 8) {
+            if (!launched) {
+                const unsigned blocks =
+                    static_cast<unsigned>(std::min<int64_t>(ceil_div(nO, 4), sms * 3));
+                note_kernel_f("opsa_vjp_mma<%s,KT=%d,LT8=%d,W=%d>", scalar_name<T>(), (K + 3) / 4,
+                              (L + 7) / 8, WEIGHTED ? 1 : 0);
+                launch_vjp_mma<T, WEIGHTED>(K, L, blocks, call.stream, gA, gB, gW, gO, A, B, W, PW,
+                                            offsets, K, L, nO, nO, call.status);
+                launched = true;
+            }
+        }
+        MOPS_CUDA_OK(cudaGetLastError());
+        scratch_free(call, offsets);
+        if (launched) {
             if (call.wait) {
                 wait_stream(call);
                 if (!host_saw_unsorted(call)) return;

@@ -1,0 +1,529 @@
+// Outer-product scatter-add (with and without weights), forward and VJP, as streaming kernels:
+// the entries of a sorted scatter index are walked in order, their A and B slices (contiguous
+// in memory), the gathered W rows and the grad_output rows arrive in shared memory through
+// bulk asynchronous copies (bulk.cuh) several chunks ahead, and the per-row contractions run
+// on the FP64 tensor-core instruction (f32 operands are widened on the way from shared memory
+// to the fragments, so f32 results carry f64 products and sums).
+//
+// Why: the kernels in opsa.cu that load MMA fragments straight from global memory keep the
+// data in flight in registers. A warp then has two or three steps (a few hundred bytes) in
+// flight and restarts its pipeline at every output row, and the measured time was the sum of
+// those exposed latencies, not the bytes moved. Here a warp owns a contiguous range of output
+// rows, hence one contiguous range of entries, which it streams through a ring of
+// shared-memory stages: one elected lane issues one copy per slice, the copy engine keeps tens
+// of kilobytes per SM in flight, row boundaries do not interrupt the stream, and the
+// instruction stream is almost only fragment reads and MMAs.
+//
+// Included by opsa.cu (inside its unnamed namespace).
+
+struct PipeLayout {
+    int K, L;     // widths of A and B
+    int LP;       // row stride of B (and W) inside a stage: L when the B slice is copied as one
+                  // piece, L + 4 when rows are copied one by one (weighted: conflict-free)
+    int row_pieces;      // weighted: 16-byte pieces of one B / W row
+    int row_pieces_log2; // its log2 when it is a power of two, else -1
+    int ch;       // entries per chunk: a multiple of 4, at most 32
+    int stages;   // chunks in flight per warp + 1
+    int a_off, b_off, w_off, pw_off; // byte offsets inside a stage (16-byte aligned)
+    int stage_bytes;
+    int g_off;    // grad_output ring (VJP): two rows of g_bytes each; unused in the forward
+    int g_bytes;
+    int bar_off;  // mbarriers: one per stage, then two for the grad_output ring
+    int warp_bytes;
+};
+
+constexpr int kPipeWarps = 4;
+
+inline int round16(size_t n) { return static_cast<int>((n + 15) / 16 * 16); }
+
+inline PipeLayout pipe_layout(size_t s, int K, int L, bool weighted, bool vjp, int ch, int stages) {
+    PipeLayout p{};
+    p.K = K, p.L = L;
+    p.LP = weighted ? L + 4 : L;
+    p.ch = ch, p.stages = stages;
+    p.row_pieces = static_cast<int>(L * s / 16);
+    p.row_pieces_log2 = -1;
+    for (int b = 0; b < 6; b++)
+        if (p.row_pieces == (1 << b)) p.row_pieces_log2 = b;
+    p.a_off = 0;
+    p.b_off = round16(static_cast<size_t>(ch) * K * s);
+    p.w_off = p.b_off + round16(static_cast<size_t>(ch) * p.LP * s);
+    p.pw_off = weighted ? p.w_off + round16(static_cast<size_t>(ch) * p.LP * s) : p.w_off;
+    p.stage_bytes = weighted ? p.pw_off + round16(static_cast<size_t>(ch) * 4) : p.pw_off;
+    p.g_bytes = static_cast<int>(static_cast<size_t>(K) * L * s);
+    p.g_off = stages * p.stage_bytes;
+    p.bar_off = p.g_off + (vjp ? 2 * round16(p.g_bytes) : 0);
+    p.warp_bytes = (p.bar_off + 8 * (stages + 2) + 127) / 128 * 128;
+    return p;
+}
+
+// Issues the copies of the chunk that starts at entry e0 into one stage. pw_lane: lane i holds
+// the (range-checked) W row of entry e0 + i. All lanes call it.
+template <typename S, bool WEIGHTED>
+__device__ __forceinline__ void pipe_issue_chunk(const PipeLayout& lay, unsigned char* stage,
+                                                 uint64_t* bar, const S* __restrict__ A,
+                                                 const S* __restrict__ B, const S* __restrict__ W,
+                                                 int64_t e0, int64_t J, int32_t pw_lane, int lane) {
+    const int K = lay.K, L = lay.L;
+    const int n = static_cast<int>(J - e0 < lay.ch ? J - e0 : lay.ch);
+    S* As = reinterpret_cast<S*>(stage + lay.a_off);
+    S* Bs = reinterpret_cast<S*>(stage + lay.b_off);
+    const unsigned a_bytes = static_cast<unsigned>(n) * K * sizeof(S), a_bulk = a_bytes & ~15u;
+    const unsigned b_bytes = static_cast<unsigned>(n) * L * sizeof(S);
+    const unsigned b_bulk = WEIGHTED ? 0u : (b_bytes & ~15u);
+    if (lane == 0) {
+        mbarrier_arrive_expect(bar, a_bulk + b_bulk);
+        if (a_bulk) bulk_copy_in(As, A + e0 * K, a_bulk, bar);
+        if (b_bulk) bulk_copy_in(Bs, B + e0 * L, b_bulk, bar);
+    }
+    if (WEIGHTED) {
+        // B rows and the gathered W rows go into padded rows, 16 bytes per lane copy; the
+        // barrier counts every lane's arrival (made when that lane's copies are complete).
+        S* Ws = reinterpret_cast<S*>(stage + lay.w_off);
+        int32_t* pws = reinterpret_cast<int32_t*>(stage + lay.pw_off);
+        if (lane < n) pws[lane] = pw_lane;
+        __syncwarp();
+        constexpr int kPer = 16 / static_cast<int>(sizeof(S)); // scalars per piece
+        const int pieces = n * lay.row_pieces;
+        for (int i = lane; i < pieces; i += 32) {
+            const int r = lay.row_pieces_log2 >= 0 ? i >> lay.row_pieces_log2 : i / lay.row_pieces;
+            const int c = (i - r * lay.row_pieces) * kPer;
+            lane_copy16(Bs + r * lay.LP + c, B + (e0 + r) * L + c);
+            lane_copy16(Ws + r * lay.LP + c, W + static_cast<int64_t>(pws[r]) * L + c);
+        }
+        lane_copies_arrive(bar);
+    }
+    // The slices end where the arrays end: the last few scalars (less than 16 bytes) of the
+    // very last chunk are fetched with plain loads.
+    if (a_bulk != a_bytes)
+        for (int i = a_bulk / sizeof(S) + lane; i < n * K; i += 32) As[i] = A[e0 * K + i];
+    if (!WEIGHTED && b_bulk != b_bytes)
+        for (int i = b_bulk / sizeof(S) + lane; i < n * L; i += 32) Bs[i] = B[e0 * L + i];
+}
+
+// State shared by the two kernels: which rows and entries the warp owns, the ring, and the
+// window of segment offsets (32 at a time, one per lane).
+struct PipeWarp {
+    int64_t r0, r1;           // output rows [r0, r1)
+    int64_t e_begin, e_last;  // their entries
+    int64_t e_first;          // e_begin rounded down to a multiple of four: 16-byte aligned slices
+    int nchunks;
+};
+
+__device__ __forceinline__ PipeWarp pipe_partition(const int64_t* __restrict__ offsets, int64_t nO,
+                                                   int ch, int warp) {
+    PipeWarp w;
+    const int64_t total = static_cast<int64_t>(gridDim.x) * kPipeWarps;
+    const int64_t gwarp = static_cast<int64_t>(blockIdx.x) * kPipeWarps + warp;
+    const int64_t per = (nO + total - 1) / total;
+    w.r0 = gwarp * per < nO ? gwarp * per : nO;
+    w.r1 = w.r0 + per < nO ? w.r0 + per : nO;
+    w.e_begin = offsets[w.r0];
+    w.e_last = offsets[w.r1];
+    w.e_first = w.e_begin & ~static_cast<int64_t>(3);
+    w.nchunks = w.e_last > w.e_begin ? static_cast<int>((w.e_last - w.e_first + ch - 1) / ch) : 0;
+    return w;
+}
+
+// ------------------------------------------------------------------------------- forward
+// O[r] = A[seg]^T (B[seg] * W[PW[seg]]) with the entries as the MMA's k dimension, four per
+// step. MT = ceil(K / 8), NT = ceil(L / 8).
+template <typename S, int MT, int NT, bool WEIGHTED>
+__global__ void __launch_bounds__(kPipeWarps * 32, 4)
+opsa_fwd_pipe(S* __restrict__ O, const S* __restrict__ A, const S* __restrict__ B,
+              const S* __restrict__ W, const int32_t* __restrict__ PW,
+              const int64_t* __restrict__ offsets, int64_t J, int64_t nO, int64_t nW,
+              PipeLayout lay, Status st) {
+    using T = double;
+    extern __shared__ __align__(128) unsigned char pipe_smem[];
+    if (saw_unsorted(st)) return; // the atomic kernel of the same call does the work
+    const int lane = threadIdx.x & 31;
+    const int warp = __shfl_sync(kFullMask, threadIdx.x >> 5, 0); // uniform for the compiler
+    const int qr = lane >> 2, qc = lane & 3;
+    const int K = lay.K, L = lay.L, LP = lay.LP, CH = lay.ch, NS = lay.stages;
+    unsigned char* area = pipe_smem + static_cast<size_t>(warp) * lay.warp_bytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(area + lay.bar_off);
+    if (lane == 0) {
+        for (int s = 0; s < NS; s++) mbarrier_init(bars + s, WEIGHTED ? 33 : 1);
+        mbarrier_init_fence();
+    }
+    __syncwarp();
+    const PipeWarp w = pipe_partition(offsets, nO, CH, warp);
+    if (w.r0 >= w.r1) return;
+
+    auto load_pw = [&](int c) -> int32_t {
+        int32_t pw = 0;
+        const int64_t e = w.e_first + static_cast<int64_t>(c) * CH + lane;
+        if (WEIGHTED && lane < CH && e < J) {
+            pw = __ldg(PW + e);
+            if (clamp_index(pw, static_cast<int32_t>(nW))) report_bad_index(st, 1);
+        }
+        return pw;
+    };
+    int issued = 0;
+    int32_t pw_reg = load_pw(0);
+    auto issue_next = [&]() {
+        if (issued < w.nchunks) {
+            const int s = issued % NS;
+            pipe_issue_chunk<S, WEIGHTED>(lay, area + s * lay.stage_bytes, bars + s, A, B, W,
+                                          w.e_first + static_cast<int64_t>(issued) * CH, J, pw_reg,
+                                          lane);
+            issued++;
+            if (WEIGHTED && issued < w.nchunks) pw_reg = load_pw(issued);
+        }
+    };
+    for (int i = 0; i < NS - 1; i++) issue_next();
+
+    // segment ends of 32 rows at a time: lane i holds offsets[wbase + 1 + i]
+    int64_t wbase = w.r0;
+    auto load_window = [&](int64_t base) {
+        const int64_t i = base + 1 + lane;
+        return offsets[i < nO ? i : nO];
+    };
+    int64_t win = load_window(wbase);
+    auto row_end = [&](int64_t r) -> int64_t {
+        if (r - wbase >= 32) {
+            wbase = r;
+            win = load_window(wbase);
+        }
+        return __shfl_sync(kFullMask, win, static_cast<int>(r - wbase));
+    };
+
+    T acc[MT][NT][2];
+    auto clear = [&] {
+#pragma unroll
+        for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) acc[mt][nt][0] = acc[mt][nt][1] = T(0);
+    };
+    const int64_t rowsize = static_cast<int64_t>(K) * L;
+    const bool pair_ok = L % 2 == 0 && reinterpret_cast<uintptr_t>(O) % (2 * sizeof(S)) == 0;
+    // element (mt, nt, h) is O[r, k = 8 mt + qr, l = 8 nt + 2 qc + h]
+    auto flush = [&](int64_t r) {
+        S* dst = O + r * rowsize;
+#pragma unroll
+        for (int mt = 0; mt < MT; mt++) {
+            const int k = 8 * mt + qr;
+            if (k >= K) continue;
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                const int l = 8 * nt + 2 * qc;
+                if (l >= L) continue;
+                S* d2 = dst + k * L + l;
+                if (pair_ok) {
+                    typename VecOf<S, 2>::type v2;
+                    v2.x = static_cast<S>(acc[mt][nt][0]), v2.y = static_cast<S>(acc[mt][nt][1]);
+                    *reinterpret_cast<typename VecOf<S, 2>::type*>(d2) = v2;
+                } else {
+                    d2[0] = static_cast<S>(acc[mt][nt][0]);
+                    if (l + 1 < L) d2[1] = static_cast<S>(acc[mt][nt][1]);
+                }
+            }
+        }
+    };
+
+    clear();
+    int64_t e = w.e_begin, row = w.r0;
+    int64_t hi = row_end(row);
+    // Rows whose last entry has been consumed (and rows without entries) are written out.
+    auto finish_rows = [&] {
+        while (row < w.r1 && e == hi) {
+            flush(row);
+            clear();
+            row++;
+            if (row < w.r1) hi = row_end(row);
+        }
+    };
+
+    for (int c = 0; c < w.nchunks; c++) {
+        issue_next(); // into the stage that the previous iteration released
+        const int s = c % NS;
+        if (!mbarrier_wait(bars + s, (c / NS) & 1)) {
+            if (lane == 0) report_stalled(st);
+            return;
+        }
+        __syncwarp();
+        const unsigned char* stage = area + s * lay.stage_bytes;
+        const S* As = reinterpret_cast<const S*>(stage + lay.a_off);
+        const S* Bs = reinterpret_cast<const S*>(stage + lay.b_off);
+        const S* Ws = reinterpret_cast<const S*>(stage + lay.w_off);
+        const int64_t c_lo = w.e_first + static_cast<int64_t>(c) * CH;
+        const int64_t c_hi = c_lo + CH < w.e_last ? c_lo + CH : w.e_last;
+        while (true) {
+            finish_rows();
+            if (row >= w.r1 || e >= c_hi) break;
+            const int64_t seg_end = hi < c_hi ? hi : c_hi;
+            // entries [e, seg_end) of the current row, four per MMA step: fragment
+            // A^T[k = 8 mt + qr][entry qc], (B*W)[entry qc][l = 8 nt + qr]
+            const int first = static_cast<int>(e - c_lo), last = static_cast<int>(seg_end - c_lo);
+#pragma unroll 2
+            for (int s0 = first; s0 < last; s0 += 4) {
+                const int idx = s0 + qc;
+                const bool valid = idx < last;
+                T af[MT], bf[NT];
+#pragma unroll
+                for (int mt = 0; mt < MT; mt++) {
+                    const int k = 8 * mt + qr;
+                    af[mt] = (valid && k < K) ? static_cast<T>(As[idx * K + k]) : T(0);
+                }
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) {
+                    const int l = 8 * nt + qr;
+                    const bool in = valid && l < L;
+                    T v = in ? static_cast<T>(Bs[idx * LP + l]) : T(0);
+                    if (WEIGHTED && in) v *= static_cast<T>(Ws[idx * LP + l]);
+                    bf[nt] = v;
+                }
+#pragma unroll
+                for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+                    for (int nt = 0; nt < NT; nt++) dmma(acc[mt][nt], af[mt], bf[nt]);
+            }
+            e = seg_end;
+        }
+        __syncwarp(); // the stage may be refilled by the copies issued next
+    }
+    finish_rows();
+}
+
+// ----------------------------------------------------------------------------------- VJP
+// For the entries of one output row, grad_A[seg] = (B*W)[seg] gO[r]^T and X = A[seg] gO[r]
+// (grad_B = X * W, grad_W[PW] += X * B) with gO[r] as the common factor, kept in registers as
+// MMA fragments while the row lasts; entries are the MMA's m dimension, eight per tile.
+// KT = ceil(K / 4), LT8 = ceil(L / 8).
+template <typename S, int KT, int LT8, bool WEIGHTED>
+__global__ void __launch_bounds__(kPipeWarps * 32, 3)
+opsa_vjp_pipe(S* __restrict__ gA, S* __restrict__ gB, S* __restrict__ gW,
+              const S* __restrict__ gO, const S* __restrict__ A, const S* __restrict__ B,
+              const S* __restrict__ W, const int32_t* __restrict__ PW,
+              const int64_t* __restrict__ offsets, int64_t J, int64_t nO, int64_t nW,
+              PipeLayout lay, Status st) {
+    using T = double;
+    using S2 = typename VecOf<S, 2>::type;
+    constexpr int NTK = (KT + 1) / 2; // 8-wide tiles over K
+    constexpr int KSL = 2 * LT8;      // k-steps over L
+    constexpr int NTL = LT8;          // 8-wide tiles over L
+    constexpr int KSK = KT;           // k-steps over K
+    extern __shared__ __align__(128) unsigned char pipe_smem[];
+    if (saw_unsorted(st)) return; // the entry-per-lane kernel of the same call does the work
+    const int lane = threadIdx.x & 31;
+    const int warp = __shfl_sync(kFullMask, threadIdx.x >> 5, 0);
+    const int qr = lane >> 2, qc = lane & 3;
+    const int K = lay.K, L = lay.L, LP = lay.LP, CH = lay.ch, NS = lay.stages;
+    unsigned char* area = pipe_smem + static_cast<size_t>(warp) * lay.warp_bytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(area + lay.bar_off);
+    uint64_t* gbars = bars + NS;
+    if (lane == 0) {
+        for (int s = 0; s < NS; s++) mbarrier_init(bars + s, WEIGHTED ? 33 : 1);
+        mbarrier_init(gbars, 1);
+        mbarrier_init(gbars + 1, 1);
+        mbarrier_init_fence();
+    }
+    __syncwarp();
+    const PipeWarp w = pipe_partition(offsets, nO, CH, warp);
+    if (w.r0 >= w.r1 || w.nchunks == 0) return; // gradients exist per entry only
+
+    const bool want_a = gA != nullptr, want_b = gB != nullptr || (WEIGHTED && gW != nullptr);
+    const bool pair_ok = L % 2 == 0 && (gB == nullptr || reinterpret_cast<uintptr_t>(gB) % (2 * sizeof(S)) == 0);
+    const int64_t rowsize = static_cast<int64_t>(K) * L;
+    const int g_slot_bytes = (lay.g_bytes + 15) / 16 * 16;
+
+    auto load_pw = [&](int c) -> int32_t {
+        int32_t pw = 0;
+        const int64_t e = w.e_first + static_cast<int64_t>(c) * CH + lane;
+        if (WEIGHTED && lane < CH && e < J) {
+            pw = __ldg(PW + e);
+            if (clamp_index(pw, static_cast<int32_t>(nW))) report_bad_index(st, 1);
+        }
+        return pw;
+    };
+    int issued = 0;
+    int32_t pw_reg = load_pw(0);
+    auto issue_next = [&]() {
+        if (issued < w.nchunks) {
+            const int s = issued % NS;
+            pipe_issue_chunk<S, WEIGHTED>(lay, area + s * lay.stage_bytes, bars + s, A, B, W,
+                                          w.e_first + static_cast<int64_t>(issued) * CH, J, pw_reg,
+                                          lane);
+            issued++;
+            if (WEIGHTED && issued < w.nchunks) pw_reg = load_pw(issued);
+        }
+    };
+    // grad_output rows r0, r0 + 1, ... go through a ring of two slots
+    auto issue_g = [&](int64_t r) {
+        if (r < w.r1 && lane == 0) {
+            const int slot = static_cast<int>(r - w.r0) & 1;
+            mbarrier_arrive_expect(gbars + slot, static_cast<unsigned>(lay.g_bytes));
+            bulk_copy_in(area + lay.g_off + slot * g_slot_bytes, gO + r * rowsize,
+                         static_cast<unsigned>(lay.g_bytes), gbars + slot);
+        }
+    };
+    issue_g(w.r0);
+    issue_g(w.r0 + 1);
+    for (int i = 0; i < NS - 1; i++) issue_next();
+
+    int64_t wbase = w.r0;
+    auto load_window = [&](int64_t base) {
+        const int64_t i = base + 1 + lane;
+        return offsets[i < nO ? i : nO];
+    };
+    int64_t win = load_window(wbase);
+    auto row_end = [&](int64_t r) -> int64_t {
+        if (r - wbase >= 32) {
+            wbase = r;
+            win = load_window(wbase);
+        }
+        return __shfl_sync(kFullMask, win, static_cast<int>(r - wbase));
+    };
+
+    // gO[r] as the B operand of both products
+    T ga_k[NTK][KSL]; // [k-step over l][n = k]: gO[k = 8 nt + qr][l = 4 ks + qc]
+    T gb_k[NTL][KSK]; // [k-step over k][n = l]: gO[k = 4 ks + qc][l = 8 nt + qr]
+    bool stalled = false;
+    // Waits for row r's grad_output, takes its fragments (if the row has entries) and hands
+    // the slot to row r + 2.
+    auto enter_row = [&](int64_t r, bool has_entries) {
+        const int use = static_cast<int>(r - w.r0);
+        if (!mbarrier_wait(gbars + (use & 1), (use >> 1) & 1)) {
+            stalled = true;
+            return;
+        }
+        if (has_entries) {
+            const S* g = reinterpret_cast<const S*>(area + lay.g_off + (use & 1) * g_slot_bytes);
+#pragma unroll
+            for (int nt = 0; nt < NTK; nt++)
+#pragma unroll
+                for (int ks = 0; ks < KSL; ks++) {
+                    const int k = 8 * nt + qr, l = 4 * ks + qc;
+                    ga_k[nt][ks] = (want_a && k < K && l < L) ? static_cast<T>(g[k * L + l]) : T(0);
+                }
+#pragma unroll
+            for (int nt = 0; nt < NTL; nt++)
+#pragma unroll
+                for (int ks = 0; ks < KSK; ks++) {
+                    const int k = 4 * ks + qc, l = 8 * nt + qr;
+                    gb_k[nt][ks] = (want_b && k < K && l < L) ? static_cast<T>(g[k * L + l]) : T(0);
+                }
+        }
+        __syncwarp(); // every lane has its fragments: the slot can be refilled
+        issue_g(r + 2);
+    };
+
+    int64_t e = w.e_begin, row = w.r0;
+    int64_t hi = row_end(row);
+    enter_row(row, hi > e);
+    auto next_rows = [&] {
+        while (row < w.r1 && e == hi && !stalled) {
+            row++;
+            if (row < w.r1) {
+                hi = row_end(row);
+                enter_row(row, hi > e);
+            }
+        }
+    };
+
+    for (int c = 0; c < w.nchunks && !stalled; c++) {
+        issue_next();
+        const int s = c % NS;
+        if (!mbarrier_wait(bars + s, (c / NS) & 1)) {
+            stalled = true;
+            break;
+        }
+        __syncwarp();
+        const unsigned char* stage = area + s * lay.stage_bytes;
+        const S* As = reinterpret_cast<const S*>(stage + lay.a_off);
+        const S* Bs = reinterpret_cast<const S*>(stage + lay.b_off);
+        const S* Ws = reinterpret_cast<const S*>(stage + lay.w_off);
+        const int32_t* pws = reinterpret_cast<const int32_t*>(stage + lay.pw_off);
+        const int64_t c_lo = w.e_first + static_cast<int64_t>(c) * CH;
+        const int64_t c_hi = c_lo + CH < w.e_last ? c_lo + CH : w.e_last;
+        while (true) {
+            next_rows();
+            if (stalled || row >= w.r1 || e >= c_hi) break;
+            const int64_t seg_end = hi < c_hi ? hi : c_hi;
+            const int first = static_cast<int>(e - c_lo), last = static_cast<int>(seg_end - c_lo);
+            for (int t0 = first; t0 < last; t0 += 8) {
+                const int idx = t0 + qr; // this lane's entry of the tile, within the chunk
+                const bool valid = idx < last;
+                const int64_t eg = c_lo + idx;
+                if (want_a) {
+                    // grad_A[entry qr][k = 8 nt + 2 qc + {0,1}] = sum_l (B*W)[entry][l] gO[k][l]
+                    T bf[KSL];
+#pragma unroll
+                    for (int ks = 0; ks < KSL; ks++) {
+                        const int l = 4 * ks + qc;
+                        const bool in = valid && l < L;
+                        T v = in ? static_cast<T>(Bs[idx * LP + l]) : T(0);
+                        if (WEIGHTED && in) v *= static_cast<T>(Ws[idx * LP + l]);
+                        bf[ks] = v;
+                    }
+#pragma unroll
+                    for (int nt = 0; nt < NTK; nt++) {
+                        T cfrag[2];
+                        dmma0(cfrag, bf[0], ga_k[nt][0]);
+#pragma unroll
+                        for (int ks = 1; ks < KSL; ks++) dmma(cfrag, bf[ks], ga_k[nt][ks]);
+                        const int k = 8 * nt + 2 * qc;
+                        S* dst = gA + eg * K + k;
+                        if (valid && k < K) dst[0] = static_cast<S>(cfrag[0]);
+                        if (valid && k + 1 < K) dst[1] = static_cast<S>(cfrag[1]);
+                    }
+                }
+                if (want_b) {
+                    // X[entry qr][l = 8 nt + 2 qc + {0,1}] = sum_k A[entry][k] gO[k][l]
+                    T af[KSK];
+#pragma unroll
+                    for (int ks = 0; ks < KSK; ks++) {
+                        const int k = 4 * ks + qc;
+                        af[ks] = (valid && k < K) ? static_cast<T>(As[idx * K + k]) : T(0);
+                    }
+                    const int32_t wrow = (WEIGHTED && valid) ? pws[idx] : 0;
+#pragma unroll
+                    for (int nt = 0; nt < NTL; nt++) {
+                        T cfrag[2];
+                        dmma0(cfrag, af[0], gb_k[nt][0]);
+#pragma unroll
+                        for (int ks = 1; ks < KSK; ks++) dmma(cfrag, af[ks], gb_k[nt][ks]);
+                        const int l = 8 * nt + 2 * qc;
+                        if (!valid || l >= L) continue;
+                        const bool two = l + 1 < L;
+                        if (WEIGHTED) {
+                            const S* wp = Ws + idx * LP + l;
+                            const S* bp = Bs + idx * LP + l;
+                            const T w0 = wp[0], b0 = bp[0];
+                            const T w1 = two ? static_cast<T>(wp[1]) : T(0);
+                            const T b1 = two ? static_cast<T>(bp[1]) : T(0);
+                            if (gW != nullptr) {
+                                S* gw = gW + static_cast<int64_t>(wrow) * L + l;
+                                red_add(gw, static_cast<S>(cfrag[0] * b0));
+                                if (two) red_add(gw + 1, static_cast<S>(cfrag[1] * b1));
+                            }
+                            cfrag[0] *= w0;
+                            cfrag[1] *= w1;
+                        }
+                        if (gB != nullptr) {
+                            S* dst = gB + eg * L + l;
+                            if (pair_ok) {
+                                S2 v2;
+                                v2.x = static_cast<S>(cfrag[0]), v2.y = static_cast<S>(cfrag[1]);
+                                *reinterpret_cast<S2*>(dst) = v2;
+                            } else {
+                                dst[0] = static_cast<S>(cfrag[0]);
+                                if (two) dst[1] = static_cast<S>(cfrag[1]);
+                            }
+                        }
+                    }
+                }
+            }
+            e = seg_end;
+        }
+        __syncwarp(); // the stage may be refilled by the copies issued next
+    }
+    if (stalled) {
+        if (lane == 0) report_stalled(st);
+        return;
+    }
+    // Rows after the last entry have no gradients to produce, but their grad_output copies
+    // may still be in flight into this block's shared memory: wait for them before leaving.
+    next_rows();
+}

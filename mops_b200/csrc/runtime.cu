@@ -120,6 +120,10 @@ void end_call(const Call& call, const char* operation, const char* const* index_
     if (!call.wait) return;
     MOPS_CUDA_OK(cudaStreamSynchronize(call.stream));
     volatile uint32_t* host = call.status.host;
+    if (host[kStalled] == call.status.epoch)
+        throw std::runtime_error(std::string("internal error in operation ") + operation +
+                                 ": a kernel gave up waiting for an asynchronous copy; the "
+                                 "results of this call are incomplete");
     std::string names;
     for (int i = 0; i < n_index_names && i < kMaxIndexArrays; i++) {
         if (host[kBadIndex0 + i] == call.status.epoch) {

@@ -24,8 +24,9 @@ namespace mops_b200 {
 // no atomics, so the host-mapped copy needs nothing special from the interconnect.
 enum StatusWord : int {
     kUnsortedEpoch = 0, // a scatter index was not in ascending order
-    kBadIndex0 = 1,     // words 1..7: index array 0..6 of the op held an out-of-range value
-    kMaxIndexArrays = 7,
+    kBadIndex0 = 1,     // words 1..6: index array 0..5 of the op held an out-of-range value
+    kMaxIndexArrays = 6,
+    kStalled = 7,       // a kernel gave up waiting for one of its own asynchronous copies
     kStatusWords = 8
 };
 

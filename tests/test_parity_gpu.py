@@ -410,7 +410,8 @@ def test_full_size_properties():
         h += 1
     Oa = M.outer_product_scatter_add(A[:h], B[:h], P[:h], nO)
     Ob = M.outer_product_scatter_add(A[h:].contiguous(), B[h:].contiguous(), P[h:].contiguous(), nO)
-    assert torch.equal(Oa + Ob, O)
+    # (not bitwise: the streaming kernel groups a row's entries by where its chunks fall)
+    assert torch.allclose(Oa + Ob, O, rtol=1e-13, atol=1e-12)
     gO = torch.randn(nO, K, L, **f)
     gA, gB = M.outer_product_scatter_add_vjp(gO, A, B, P)
     lhs, rhs = float((gO * O).sum()), float((gA * A).sum())
