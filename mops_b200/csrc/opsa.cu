@@ -520,10 +520,14 @@ bool pipe_usable(const T* A, const T* B, const T* W, const void* extra, int K, i
 }
 
 template <typename T, bool WEIGHTED> PipeLayout choose_pipe_layout(int K, int L, bool vjp) {
-    // Two stages of 32 entries per warp measured best (f64 OPSA forward 0.91 ms, VJP 1.64 ms
-    // against 0.97 / 1.85 with three stages of 16): the smaller ring lets more warps share an
-    // SM, and one chunk in flight per warp already keeps about 100 KB per SM in flight.
-    int ch = env_int("MOPS_B200_PIPE_CH", 32), stages = env_int("MOPS_B200_PIPE_STAGES", 2);
+    // Measured on B200 (J = 2^24 / E = 2^22): without weights two stages of 32 entries per
+    // warp are best (f64 forward 0.91 ms, VJP 1.64 ms against 0.97 / 1.85 with three stages
+    // of 16): the smaller ring lets more warps share an SM, and one chunk in flight per warp
+    // already keeps about 100 KB per SM in flight. With weights a stage also holds the padded
+    // B and W rows (680 bytes per entry), so chunks of 8 keep the warp count up (forward
+    // 0.59 ms, VJP 1.12 ms against 0.92 / 1.63 with chunks of 32).
+    int ch = env_int("MOPS_B200_PIPE_CH", WEIGHTED ? 8 : 32);
+    int stages = env_int("MOPS_B200_PIPE_STAGES", 2);
     ch = std::max(4, std::min(32, ch / 4 * 4));
     stages = std::max(2, std::min(8, stages));
     return pipe_layout(sizeof(T), K, L, WEIGHTED, vjp, ch, stages);

@@ -28,6 +28,7 @@
 // is not sorted. VJP: one warp per edge (lane = b), independent of the index order; gW is
 // accumulated with RED because indices_W_1 is not sorted.
 #include <algorithm>
+#include <cstdlib>
 #include <mutex>
 #include <type_traits>
 
@@ -1259,6 +1260,339 @@ sasaw_fwd_mma(double* __restrict__ O, const double* __restrict__ A, const double
     }
 }
 
+// ----------------------------------------------------------- tensor-core kernels, quads
+// The kernels above spend most of their FP64 tensor-core issue slots on padding: with nine
+// angular channels every dimension is padded to 12 or 16, the ninth output row costs a whole
+// second 8-row tile, and only about four in ten issued MMA lanes do useful work. The kernels
+// below remove the padding by choosing which index goes where in the m8n8k4 shape:
+//   * cells are numbered compactly (m3 * W.shape[1] + m2), so T for eight edges takes
+//     ceil(cells / 8) tiles instead of ceil(padded cells / 8);
+//   * a contraction length of 4 k + 1 (nine components of A) is 4 k by MMA plus one
+//     multiply-add per accumulator element for the last component;
+//   * phase B contracts over (m2, edge) together: edges of one output row are taken four at
+//     a time and one k-step holds one m2 of four edges, so nine channels take nine k-steps
+//     with no padding at all (instead of three padded k-steps per edge = twelve per four edges);
+//   * the ninth output row is not a second MMA tile: its sums are formed by the FP64 FMA pipe
+//     from the very fragment registers the MMA consumes (one multiply-add per fragment element),
+//     and its four partial sums per quad of lanes are added once per output row.
+// A warp owns a contiguous range of output rows and walks their edges in quads; the (W rows,
+// B row) blocks of the next quad are in flight (16-byte asynchronous copies by all lanes)
+// while the current one is consumed, across row boundaries.
+
+struct QuadLayout {
+    int ncc;  // compact cells: output_size * W.shape[1]
+    int nct;  // 8-cell tiles
+    int DS;   // row stride of D (A.shape[1] rounded up to 4 or 12 modulo 16: conflict-free)
+    int ES;   // distance between the T slots of consecutive edges (4 modulo 16)
+    int EB;   // distance between the staged blocks of consecutive edges (4 modulo 16)
+    int d_scalars;
+    int warp_scalars;
+};
+
+__host__ __device__ constexpr QuadLayout quad_layout(int nA, int nW1, int nO1) {
+    QuadLayout q{};
+    q.ncc = nO1 * nW1;
+    q.nct = (q.ncc + 7) / 8;
+    q.DS = a_stride((nA + 3) / 4 * 4);
+    q.ES = q.ncc + ((4 - q.ncc % 16) + 16) % 16;
+    q.EB = (nW1 + 1) * 32 + 4;
+    q.d_scalars = q.nct * 8 * q.DS;
+    q.warp_scalars = 8 * q.ES + 2 * 4 * q.EB;
+    return q;
+}
+
+// Copies 16 bytes, or writes 16 zero bytes when src_bytes == 0 (the source is not read then).
+__device__ __forceinline__ void cp_async16_zfill(void* smem_dst, const void* global_src,
+                                                 int src_bytes) {
+    const unsigned dst = static_cast<unsigned>(__cvta_generic_to_shared(smem_dst));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(global_src),
+                 "r"(src_bytes)
+                 : "memory");
+}
+
+// Where a warp is in its walk over the quads of its rows; edges are counted from the warp's
+// first edge and rows from its first row, so the bookkeeping is 32-bit.
+struct QuadPos {
+    int row, lo, hi, e; // output row, its edges [lo, hi), first edge of the quad
+    bool valid;
+};
+
+// MODE 0: output_size <= 8; MODE 1: output_size == 9 (eight rows by MMA, one by FMA);
+// MODE 2: 10..16 (two MMA tiles). NA, NW, NO: A.shape[1], W.shape[1], output_size when they
+// are known at compile time (all loops unroll and all shared-memory offsets are immediates:
+// a quarter of the instructions of the generic form), 0 = taken from the arguments.
+// f64, all three <= 16, L even, 16-byte aligned W, B and O, sorted scatter index.
+template <int MODE, int NA, int NW, int NO>
+__global__ void __launch_bounds__(256, 1)
+sasaw_fwd_quad(double* __restrict__ O, const double* __restrict__ A, const double* __restrict__ B,
+               const double* __restrict__ W, const int32_t* __restrict__ Jw,
+               const int64_t* __restrict__ offsets, Coupling<double> cp, int64_t E, int nA_arg,
+               int L, int64_t nW0, int nW1_arg, int nO1_arg, Status st) {
+    using T = double;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    if (saw_unsorted(st)) return; // the kernels for unsorted input do the work
+    const int nA = NA > 0 ? NA : nA_arg, nW1 = NW > 0 ? NW : nW1_arg, nO1 = NO > 0 ? NO : nO1_arg;
+    const int warps = blockDim.x >> 5, lane = threadIdx.x & 31;
+    const int warp = __shfl_sync(kFullMask, threadIdx.x >> 5, 0); // uniform for the compiler
+    const int qr = lane >> 2, qc = lane & 3;
+    const QuadLayout q = quad_layout(nA, nW1, nO1);
+    T* D_s = reinterpret_cast<T*>(smem_raw); // [8 * nct][DS], rows >= ncc zero
+    T* slots = D_s + q.d_scalars + static_cast<size_t>(q.warp_scalars) * warp; // [8][ES]
+    T* stages = slots + 8 * q.ES;                                              // [2][4][EB]
+    for (int i = threadIdx.x; i < q.d_scalars; i += blockDim.x)
+        D_s[i] = i < q.ncc * q.DS ? cp.D[i] : T(0);
+    for (int i = lane; i < q.warp_scalars; i += 32) slots[i] = T(0);
+    __syncthreads();
+
+    const int64_t total_warps = static_cast<int64_t>(gridDim.x) * warps;
+    const int64_t gwarp = static_cast<int64_t>(blockIdx.x) * warps + warp;
+    const int64_t per = (nW0 + total_warps - 1) / total_warps;
+    const int64_t r0 = gwarp * per < nW0 ? gwarp * per : nW0;
+    const int64_t r1 = r0 + per < nW0 ? r0 + per : nW0;
+    if (r0 >= r1) return;
+    const int nrows = static_cast<int>(r1 - r0);
+    // this warp's edges, operands and output, rebased to its first edge / row
+    const int64_t e_base = offsets[r0];
+    const T* A0 = A + e_base * nA;
+    const T* B0 = B + e_base * L;
+    const int32_t* J0 = Jw + e_base;
+    const size_t rowsize = static_cast<size_t>(nO1) * L;
+    T* O0 = O + r0 * rowsize;
+
+    const int ksa = nA / 4;                          // whole k-steps over the components of A
+    const bool rank1 = nA % 4 == 1;                  // the last component by multiply-add
+    const int ksa_mma = ksa + (nA % 4 >= 2 ? 1 : 0); // else one more, partly filled, k-step
+
+    // segment ends of 32 rows at a time: lane i holds offsets[r0 + wbase + 1 + i] - e_base
+    int wbase = 0, win = 0;
+    auto load_window = [&](int base) {
+        const int64_t i = r0 + base + 1 + lane;
+        return static_cast<int>(offsets[i < nW0 ? i : nW0] - e_base);
+    };
+    auto row_end = [&](int r) -> int {
+        if (r - wbase >= 32) {
+            wbase = r;
+            win = load_window(wbase);
+        }
+        return __shfl_sync(kFullMask, win, r - wbase);
+    };
+
+    // fragment element (nt, h) of tile 0 is output element [m3 = qr][b = b0 + 8 nt + 2 qc + h];
+    // x1: MODE 1 partial sums of row 8 for b = b0 + 8 nt + qr over this lane's edges (lane
+    // qc takes edge qc of every quad); MODE 2 the second tile, rows 8 + qr
+    T acc0[4][2], x1[4][2];
+    auto clear = [&] {
+#pragma unroll
+        for (int nt = 0; nt < 4; nt++)
+            acc0[nt][0] = acc0[nt][1] = x1[nt][0] = x1[nt][1] = T(0);
+    };
+    auto store_pair = [&](T* d2, int b, int width, T v0, T v1) {
+        if (b + 1 < width) {
+            *reinterpret_cast<double2*>(d2) = make_double2(v0, v1);
+        } else if (b < width) {
+            d2[0] = v0;
+        }
+    };
+    auto flush = [&](int row, int b0) {
+        T* dst = O0 + row * rowsize + b0;
+        const int width = L - b0;
+        if (MODE != 0 || qr < nO1) {
+#pragma unroll
+            for (int nt = 0; nt < 4; nt++)
+                store_pair(dst + qr * L + 8 * nt + 2 * qc, 8 * nt + 2 * qc, width, acc0[nt][0],
+                           acc0[nt][1]);
+        }
+        if (MODE == 2 && 8 + qr < nO1) {
+#pragma unroll
+            for (int nt = 0; nt < 4; nt++)
+                store_pair(dst + (8 + qr) * L + 8 * nt + 2 * qc, 8 * nt + 2 * qc, width, x1[nt][0],
+                           x1[nt][1]);
+        }
+        if (MODE == 1) {
+            // add the four lanes of a quad; lane (qr, qc) ends with b = 8 qc + qr
+            const bool up2 = (qc & 2) != 0, up1 = (qc & 1) != 0;
+            const T s0 = (up2 ? x1[2][0] : x1[0][0]) +
+                         __shfl_xor_sync(kFullMask, up2 ? x1[0][0] : x1[2][0], 2);
+            const T s1 = (up2 ? x1[3][0] : x1[1][0]) +
+                         __shfl_xor_sync(kFullMask, up2 ? x1[1][0] : x1[3][0], 2);
+            const T v = (up1 ? s1 : s0) + __shfl_xor_sync(kFullMask, up1 ? s0 : s1, 1);
+            const int b = 8 * qc + qr;
+            if (b < width) dst[8 * L + b] = v;
+        }
+    };
+    auto zero_row = [&](int row, int b0) {
+        T* dst = O0 + row * rowsize + b0;
+        const int width = L - b0 < 32 ? L - b0 : 32;
+        for (int m3 = 0; m3 < nO1; m3++)
+            if (lane < width) dst[m3 * L + lane] = T(0);
+    };
+
+    // A fragments of a batch of eight edges: af[ks] = A[eb + qr][4 ks + qc] (the B operand of
+    // phase A: k = component, n = edge), al[h] = last component of edge eb + 2 qc + h
+    auto load_a = [&](int eb, int hi, T (&af)[4], T (&al)[2]) {
+        const int ea = eb + qr;
+        const T* a = A0 + static_cast<int64_t>(ea) * nA + qc;
+#pragma unroll
+        for (int ks = 0; ks < 4; ks++)
+            af[ks] = (ks < ksa_mma && ea < hi && 4 * ks + qc < nA) ? __ldg(a + 4 * ks) : T(0);
+        const int e2 = eb + 2 * qc;
+        const T* a2 = A0 + static_cast<int64_t>(e2) * nA + nA - 1;
+        al[0] = (rank1 && e2 < hi) ? __ldg(a2) : T(0);
+        al[1] = (rank1 && e2 + 1 < hi) ? __ldg(a2 + nA) : T(0);
+    };
+    // T[cell, edge] = sum_m D[cell, m] A[edge, m] for the eight edges of a batch
+    auto phase_a = [&](const T (&af)[4], const T (&al)[2]) {
+        const T* drow = D_s + qr * q.DS + qc;
+        T* dst = slots + (2 * qc) * q.ES + qr;
+#pragma unroll
+        for (int t = 0; t < (NO > 0 ? (NO * NW + 7) / 8 : 32); t++) {
+            if (NO == 0 && t >= q.nct) break;
+            T c[2] = {T(0), T(0)};
+#pragma unroll
+            for (int ks = 0; ks < 4; ks++)
+                if (ks < ksa_mma) dmma(c, drow[t * 8 * q.DS + 4 * ks], af[ks]);
+            if (rank1) {
+                const T dl = drow[t * 8 * q.DS + nA - 1 - qc];
+                c[0] = fma(dl, al[0], c[0]);
+                c[1] = fma(dl, al[1], c[1]);
+            }
+            if (8 * t + qr < q.ncc) {
+                dst[8 * t] = c[0];
+                dst[8 * t + q.ES] = c[1];
+            }
+        }
+    };
+    // Lane i < 4 takes the W row index of edge e + i.
+    auto load_j = [&](const QuadPos& p) -> int32_t {
+        int32_t j = 0;
+        if (p.valid && lane < 4 && p.e + lane < p.hi) {
+            j = __ldg(J0 + p.e + lane);
+            if (clamp_index(j, static_cast<int32_t>(nW0))) report_bad_index(st, kBitJ);
+        }
+        return j;
+    };
+    // Asynchronous copies of W[J_e, :, b0 .. b0+31] and B[e, b0 .. b0+31] of the four edges of
+    // a quad into stage s: a lane moves 16 bytes per copy, two rows per round; blocks of
+    // edges past the row's end and columns past L are zero-filled. Always commits a group.
+    const int64_t w_stride = static_cast<int64_t>(nW1) * L;
+    auto issue = [&](int s, const QuadPos& p, int32_t j_lane, int b0) {
+        if (p.valid) {
+            const int col = 2 * (lane & 15);
+            const bool col_ok = b0 + col < L;
+            T* buf = stages + s * 4 * q.EB + col + (lane >> 4) * 32;
+            const int src_col = b0 + (col_ok ? col : 0);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int32_t j = __shfl_sync(kFullMask, j_lane, i);
+                const bool ok = col_ok && p.e + i < p.hi;
+                const T* wsrc = W + j * w_stride + src_col + (lane >> 4) * L;
+                const T* bsrc = B0 + static_cast<int64_t>(ok ? p.e + i : p.e) * L + src_col;
+                T* dst = buf + i * q.EB;
+                const int bytes = ok ? 16 : 0;
+#pragma unroll
+                for (int rr = 0; rr < (NW > 0 ? (NW + 2) / 2 : 9); rr++) {
+                    const int r = 2 * rr + (lane >> 4);
+                    if (r <= nW1)
+                        cp_async16_zfill(dst + rr * 64, r < nW1 ? wsrc + static_cast<int64_t>(2 * rr) * L : bsrc,
+                                         bytes);
+                }
+            }
+        }
+        cp_async_commit();
+    };
+    // O[m3, b] += sum over (m2, edge of the quad) of T_edge[m3, m2] (B_edge[b] W[J_edge, m2, b]):
+    // one k-step per m2, lane qc holds edge qc of the quad.
+    auto phase_b = [&](int s, int quad_in_batch) {
+        const T* wl = stages + s * 4 * q.EB + qc * q.EB + qr; // + m2 * 32 + 8 nt
+        const T* tl = slots + (4 * quad_in_batch + qc) * q.ES; // T of this lane's edge
+        T bb[4];
+#pragma unroll
+        for (int nt = 0; nt < 4; nt++) bb[nt] = wl[nW1 * 32 + 8 * nt];
+        const bool row_ok = MODE != 0 || qr < nO1;
+        const bool row1_ok = MODE == 2 && 8 + qr < nO1;
+        const T* t0 = tl + (row_ok ? qr * nW1 : 0);
+        const T* t1 = tl + (MODE == 1 ? 8 * nW1 : (row1_ok ? (8 + qr) * nW1 : 0));
+#pragma unroll
+        for (int m2 = 0; m2 < (NW > 0 ? NW : 16); m2++) {
+            if (NW == 0 && m2 >= nW1) break;
+            const T a0 = row_ok ? t0[m2] : T(0);
+            T a1 = T(0);
+            if (MODE == 1) a1 = t1[m2];
+            if (MODE == 2) a1 = row1_ok ? t1[m2] : T(0);
+#pragma unroll
+            for (int nt = 0; nt < 4; nt++) {
+                const T bw = wl[m2 * 32 + 8 * nt] * bb[nt];
+                dmma(acc0[nt], a0, bw);
+                if (MODE == 1) x1[nt][0] = fma(a1, bw, x1[nt][0]);
+                if (MODE == 2) dmma(x1[nt], a1, bw);
+            }
+        }
+    };
+
+    for (int b0 = 0; b0 < L; b0 += 32) {
+        wbase = 0;
+        win = load_window(0);
+        // next quad after p; rows without edges are written as zeros on the way
+        auto advance = [&](QuadPos p) -> QuadPos {
+            if (!p.valid) return p;
+            p.e += 4;
+            while (p.e >= p.hi) {
+                p.row++;
+                if (p.row >= nrows) {
+                    p.valid = false;
+                    return p;
+                }
+                p.lo = p.hi;
+                p.hi = row_end(p.row);
+                p.e = p.lo;
+                if (p.hi == p.lo) zero_row(p.row, b0);
+            }
+            return p;
+        };
+        QuadPos start;
+        start.row = -1, start.valid = true;
+        start.lo = start.hi = 0;
+        start.e = -4;
+        QuadPos p0 = advance(start);
+        QuadPos p1 = advance(p0), p2 = advance(p1), p3 = advance(p2);
+        int32_t j2 = load_j(p2), j3 = load_j(p3);
+        issue(0, p0, load_j(p0), b0);
+        issue(1, p1, load_j(p1), b0);
+        T af[4], al[2], af_n[4], al_n[2];
+        if (p0.valid) load_a(p0.e, p0.hi, af, al);
+        if (p1.valid && ((p1.e - p1.lo) & 7) == 0) load_a(p1.e, p1.hi, af_n, al_n);
+        clear();
+        int s = 0;
+        while (p0.valid) {
+            const int in_row = p0.e - p0.lo;
+            if ((in_row & 7) == 0) { // first quad of a batch of eight edges
+                phase_a(af, al);
+            }
+            cp_async_wait<1>();
+            __syncwarp();
+            phase_b(s, (in_row >> 2) & 1);
+            __syncwarp(); // stage s and (after the batch's second quad) the slots are free
+            issue(s, p2, j2, b0);
+            if (!p1.valid || p1.row != p0.row) {
+                flush(p0.row, b0);
+                clear();
+            }
+            if (p1.valid && ((p1.e - p1.lo) & 7) == 0) {
+#pragma unroll
+                for (int ks = 0; ks < 4; ks++) af[ks] = af_n[ks];
+                al[0] = al_n[0], al[1] = al_n[1];
+            }
+            p0 = p1, p1 = p2, p2 = p3, j2 = j3;
+            p3 = advance(p3);
+            j3 = load_j(p3);
+            if (p1.valid && ((p1.e - p1.lo) & 7) == 0) load_a(p1.e, p1.hi, af_n, al_n);
+            s ^= 1;
+        }
+        cp_async_wait<0>();
+        __syncwarp();
+    }
+}
+
 // Any sizes, no shared memory: one thread per (edge, b) walking the whole coupling table.
 // Needs zero-filled O (forward) / gA, gW (VJP).
 template <typename T>
@@ -1488,7 +1822,10 @@ bool backward_fast(const Call& call, T* gA, T* gB, T* gW, const T* gO, const Pro
 }
 
 // Tensor-core variants (f64, output_size <= 16 as well).
-template <typename T, int TP> bool forward_mma_launch(const Call& call, T* O, const Problem<T>& p) {
+// `segmented_done`: another kernel has already handled sorted input; only the kernels for an
+// unsorted scatter index are enqueued (they stand down by themselves when it was sorted).
+template <typename T, int TP>
+bool forward_mma_launch(const Call& call, T* O, const Problem<T>& p, bool segmented_done = false) {
     using Lay = VjpMma<TP>;
     const int warps = 4;
     const size_t smem =
@@ -1499,23 +1836,27 @@ template <typename T, int TP> bool forward_mma_launch(const Call& call, T* O, co
     Coupling<T> cp{};
     void* scratch = nullptr;
     if (!build_coupling(call, p, cp, &scratch, Lay::TS, Lay::d_stride(p.nA), true)) return false;
-    int64_t* offsets = static_cast<int64_t*>(scratch_alloc(call, (p.nW0 + 1) * sizeof(int64_t)));
-    const int64_t pre_blocks = std::min<int64_t>(ceil_div(p.E + 1, 256), sms * 32);
-    segment_offsets<<<static_cast<unsigned>(pre_blocks), 256, 0, call.stream>>>(
-        p.Io, p.E, p.nW0, offsets, call.status);
     const bool wide_copies = p.L % 2 == 0 && reinterpret_cast<uintptr_t>(p.W) % 16 == 0 &&
                              reinterpret_cast<uintptr_t>(p.B) % 16 == 0 &&
                              reinterpret_cast<uintptr_t>(O) % 16 == 0;
-    allow_smem(sasaw_fwd_mma<TP, true>, smem);
-    note_kernel_f("sasaw_fwd_mma<TP=%d,SEG=1>", TP);
-    const int64_t seg_blocks = std::min<int64_t>(ceil_div(p.nW0, warps), sms * 3);
-    sasaw_fwd_mma<TP, true><<<static_cast<unsigned>(seg_blocks), warps * 32, smem, call.stream>>>(
-        O, p.A, p.B, p.W, p.Jw, p.Io, offsets, cp, p.E, p.nA, p.L, p.nW0, p.nW1, p.nO1,
-        wide_copies, call.status);
-    MOPS_CUDA_OK(cudaGetLastError());
-    scratch_free(call, offsets);
+    if (!segmented_done) {
+        int64_t* offsets =
+            static_cast<int64_t*>(scratch_alloc(call, (p.nW0 + 1) * sizeof(int64_t)));
+        const int64_t pre_blocks = std::min<int64_t>(ceil_div(p.E + 1, 256), sms * 32);
+        segment_offsets<<<static_cast<unsigned>(pre_blocks), 256, 0, call.stream>>>(
+            p.Io, p.E, p.nW0, offsets, call.status);
+        allow_smem(sasaw_fwd_mma<TP, true>, smem);
+        note_kernel_f("sasaw_fwd_mma<TP=%d,SEG=1>", TP);
+        const int64_t seg_blocks = std::min<int64_t>(ceil_div(p.nW0, warps), sms * 3);
+        sasaw_fwd_mma<TP, true><<<static_cast<unsigned>(seg_blocks), warps * 32, smem,
+                                  call.stream>>>(O, p.A, p.B, p.W, p.Jw, p.Io, offsets, cp, p.E,
+                                                 p.nA, p.L, p.nW0, p.nW1, p.nO1, wide_copies,
+                                                 call.status);
+        MOPS_CUDA_OK(cudaGetLastError());
+        scratch_free(call, offsets);
+    }
     bool need_fallback = true; // asynchronous calls cannot look: always enqueue
-    if (call.wait) {
+    if (call.wait && !segmented_done) {
         wait_stream(call);
         need_fallback = host_saw_unsorted(call);
     }
@@ -1532,16 +1873,81 @@ template <typename T, int TP> bool forward_mma_launch(const Call& call, T* O, co
     return true;
 }
 
+inline int env_flag(const char* name, int fallback) {
+    const char* v = std::getenv(name);
+    return v != nullptr && *v != '\0' ? std::atoi(v) : fallback;
+}
+
+// Sorted scatter index through the quad kernel. Returns 0 when it does not apply, 1 when it
+// ran and the index was seen to be sorted (nothing left to do), 2 when it was launched but
+// the kernels for unsorted input must still be enqueued (asynchronous call, or the index
+// turned out unsorted).
+template <typename T> int forward_quad(const Call& call, T* O, const Problem<T>& p) {
+    if constexpr (!std::is_same<T, double>::value) {
+        return 0;
+    } else {
+        // (MOPS_B200_SASAW_QUAD=0: development switch back to the batch-of-eight kernels)
+        if (env_flag("MOPS_B200_SASAW_QUAD", 1) == 0) return 0;
+        auto aligned = [](const void* ptr) { return reinterpret_cast<uintptr_t>(ptr) % 16 == 0; };
+        if (p.L % 2 != 0 || !aligned(p.W) || !aligned(p.B) || !aligned(O)) return 0;
+        const QuadLayout q = quad_layout(p.nA, p.nW1, p.nO1);
+        const size_t d_bytes = static_cast<size_t>(q.d_scalars) * sizeof(T);
+        const size_t warp_bytes = static_cast<size_t>(q.warp_scalars) * sizeof(T);
+        const size_t limit = static_cast<size_t>(max_optin_smem(call.device));
+        if (d_bytes + 2 * warp_bytes > limit) return 0;
+        const int warps = static_cast<int>(std::min<size_t>(8, (limit - d_bytes) / warp_bytes));
+        const size_t smem = d_bytes + warps * warp_bytes;
+        const int sms = sm_count(call.device);
+        Coupling<T> cp{};
+        void* scratch = nullptr;
+        if (!build_coupling(call, p, cp, &scratch, p.nW1, q.DS, false)) return 0;
+        int64_t* offsets =
+            static_cast<int64_t*>(scratch_alloc(call, (p.nW0 + 1) * sizeof(int64_t)));
+        const int64_t pre_blocks = std::min<int64_t>(ceil_div(p.E + 1, 256), sms * 32);
+        segment_offsets<<<static_cast<unsigned>(pre_blocks), 256, 0, call.stream>>>(
+            p.Io, p.E, p.nW0, offsets, call.status);
+        const int mode = p.nO1 <= 8 ? 0 : (p.nO1 == 9 ? 1 : 2);
+        const unsigned blocks = static_cast<unsigned>(std::min<int64_t>(ceil_div(p.nW0, warps), sms));
+        const bool fixed = p.nA == p.nW1 && p.nA == p.nO1 && (p.nA == 4 || p.nA == 9 || p.nA == 16);
+        note_kernel_f("sasaw_fwd_quad<MODE=%d,%s> warps=%d", mode, fixed ? "fixed widths" : "any widths", warps);
+#define MOPS_B200_CASE(MODE_, NA_, NW_, NO_)                                                       \
+    {                                                                                              \
+        allow_smem(sasaw_fwd_quad<MODE_, NA_, NW_, NO_>, smem);                                    \
+        sasaw_fwd_quad<MODE_, NA_, NW_, NO_><<<blocks, warps * 32, smem, call.stream>>>(           \
+            O, p.A, p.B, p.W, p.Jw, offsets, cp, p.E, p.nA, p.L, p.nW0, p.nW1, p.nO1, call.status); \
+    }
+        // the widths of l <= 1, 2, 3 spherical-harmonic channels are compiled in
+        if (p.nA == 9 && p.nW1 == 9 && p.nO1 == 9) MOPS_B200_CASE(1, 9, 9, 9)
+        else if (p.nA == 4 && p.nW1 == 4 && p.nO1 == 4) MOPS_B200_CASE(0, 4, 4, 4)
+        else if (p.nA == 16 && p.nW1 == 16 && p.nO1 == 16) MOPS_B200_CASE(2, 16, 16, 16)
+        else if (mode == 0) MOPS_B200_CASE(0, 0, 0, 0)
+        else if (mode == 1) MOPS_B200_CASE(1, 0, 0, 0)
+        else MOPS_B200_CASE(2, 0, 0, 0)
+#undef MOPS_B200_CASE
+        MOPS_CUDA_OK(cudaGetLastError());
+        scratch_free(call, offsets);
+        scratch_free(call, scratch);
+        if (call.wait) {
+            wait_stream(call);
+            if (!host_saw_unsorted(call)) return 1;
+        }
+        return 2;
+    }
+}
+
 template <typename T> bool forward_mma(const Call& call, T* O, const Problem<T>& p) {
     if constexpr (!std::is_same<T, double>::value) {
         return false;
     } else {
-        if (fast_width(p.nO1) == 0 || fast_width(p.nA) == 0) return false;
+        if (fast_width(p.nO1) == 0 || fast_width(p.nA) == 0 || fast_width(p.nW1) == 0)
+            return false;
+        const int quad = forward_quad(call, O, p);
+        if (quad == 1) return true;
         switch (fast_width(p.nW1)) {
-        case 4: return forward_mma_launch<T, 4>(call, O, p);
-        case 8: return forward_mma_launch<T, 8>(call, O, p);
-        case 12: return forward_mma_launch<T, 12>(call, O, p);
-        case 16: return forward_mma_launch<T, 16>(call, O, p);
+        case 4: return forward_mma_launch<T, 4>(call, O, p, quad == 2);
+        case 8: return forward_mma_launch<T, 8>(call, O, p, quad == 2);
+        case 12: return forward_mma_launch<T, 12>(call, O, p, quad == 2);
+        case 16: return forward_mma_launch<T, 16>(call, O, p, quad == 2);
         default: return false;
         }
     }
