@@ -697,12 +697,14 @@ sasaw_vjp_mma(double* __restrict__ gA, double* __restrict__ gB, double* __restri
               const double* __restrict__ B, const double* __restrict__ W,
               const int32_t* __restrict__ Jw, const int32_t* __restrict__ Io,
               Coupling<double> cp, int64_t E, int nA, int L, int64_t nW0, int nW1, int nO1,
-              bool wide_copies, Status st) {
+              bool wide_copies, bool only_if_unsorted, Status st) {
     using T = double;
     using Lay = VjpMma<TP>;
     constexpr int TS = Lay::TS, WS = Lay::WS, NT2 = Lay::NT2;
     constexpr int MT3 = KS3 > 2 ? 2 : 1; // 8-high tiles over m3
     extern __shared__ __align__(16) unsigned char smem_raw[];
+    // (a kernel for sorted input ran before this one and has done the work unless it stood down)
+    if (only_if_unsorted && !saw_unsorted(st)) return;
     // the shuffle tells the compiler that the warp number is the same in all lanes, so that
     // everything derived from it (edge ranges, loop counts) stays in uniform control flow
     const int warps = blockDim.x >> 5, lane = threadIdx.x & 31;
@@ -1593,6 +1595,387 @@ sasaw_fwd_quad(double* __restrict__ O, const double* __restrict__ A, const doubl
     }
 }
 
+// VJP over quads of edges, for a sorted scatter index and compile-time widths NA = A.shape[1],
+// NW = W.shape[1], NO = output_size (LL = B.shape[1] when known at compile time, else 0).
+// Per batch of eight edges of one output row r (T, U in one slot per edge, cells compact):
+//   phase A  T[cell, e] = sum_m D[cell, m] A[e, m]                       (as in the forward)
+//   per quad X[(m2, e), b] = sum_m3 T_e[m3, m2] gO[r, m3, b]: the rows of the MMA are (m2
+//            pair, edge of the quad), so nine channels fill 4.5 tiles instead of 8; a ninth
+//            m3 is one multiply-add per accumulator element. grad_B[e, b] = sum_m2 X W[J_e,
+//            m2, b] is summed in registers (one exchange between two lanes per quad),
+//            grad_W[J_e, m2, b] += X B[e, b] goes out by RED straight from the fragments;
+//            U[m3, (m2, e)] = sum_b gO[r, m3, b] (B[e, b] W[J_e, m2, b]) with the columns
+//            numbered the same way (a ninth m3 again on the FMA pipe), written over T_e;
+//   phase C  grad_A[e, m] = sum_cell U[e, cell] D[cell, m] for the eight edges at once.
+// About 25 tensor-core instructions per edge instead of 74.
+template <int NA, int NW, int NO, int LL>
+__global__ void __launch_bounds__(256, 1)
+sasaw_vjp_quad(double* __restrict__ gA, double* __restrict__ gB, double* __restrict__ gW,
+               const double* __restrict__ gO, const double* __restrict__ A,
+               const double* __restrict__ B, const double* __restrict__ W,
+               const int32_t* __restrict__ Jw, const int64_t* __restrict__ offsets,
+               Coupling<double> cp, int L_arg, int64_t nW0, Status st) {
+    using T = double;
+    constexpr QuadLayout q = quad_layout(NA, NW, NO);
+    constexpr int ES = q.ES, EB = q.EB, DS = q.DS;
+    constexpr int KSA = NA / 4 + (NA % 4 >= 2 ? 1 : 0); // phase A: k-steps over m1
+    constexpr bool RANK_A = NA % 4 == 1;                // ... and the last component by FMA
+    constexpr int NMT = (NW + 1) / 2;                   // tiles over (m2 pair, edge of the quad)
+    constexpr int KS3 = NO / 4 + (NO % 4 >= 2 ? 1 : 0); // X: k-steps over m3
+    constexpr bool RANK_3 = NO % 4 == 1;                // ... and the last m3 by FMA
+    constexpr int MT3 = NO > 9 ? 2 : 1;                 // U: 8-row tiles over m3
+    constexpr bool ROW8 = NO == 9;                      // ... and the ninth row by FMA
+    constexpr int NTA = NA > 9 ? 2 : 1;                 // phase C: 8-wide tiles over m1
+    constexpr bool COL8 = NA == 9;                      // ... and the ninth column by FMA
+    constexpr int KC = (q.ncc + 3) / 4;                 // phase C: k-steps over the cells
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    if (saw_unsorted(st)) return; // the edge-by-edge kernel of the same call does the work
+    const int L = LL > 0 ? LL : L_arg;
+    const int warps = blockDim.x >> 5, lane = threadIdx.x & 31;
+    const int warp = __shfl_sync(kFullMask, threadIdx.x >> 5, 0); // uniform for the compiler
+    const int qr = lane >> 2, qc = lane & 3;
+    const int qe = qr & 3, qh = qr >> 2; // as a row of an (m2 pair, edge) tile: edge, which m2
+    T* D_s = reinterpret_cast<T*>(smem_raw); // [8 * nct][DS], rows >= ncc zero
+    T* slots = D_s + q.d_scalars + static_cast<size_t>(q.warp_scalars) * warp; // [8][ES]
+    T* stages = slots + 8 * ES;                                               // [2][4][EB]
+    for (int i = threadIdx.x; i < q.d_scalars; i += blockDim.x)
+        D_s[i] = i < q.ncc * DS ? cp.D[i] : T(0);
+    for (int i = lane; i < q.warp_scalars; i += 32) slots[i] = T(0);
+    __syncthreads();
+
+    const int64_t total_warps = static_cast<int64_t>(gridDim.x) * warps;
+    const int64_t gwarp = static_cast<int64_t>(blockIdx.x) * warps + warp;
+    const int64_t per = (nW0 + total_warps - 1) / total_warps;
+    const int64_t r0 = gwarp * per < nW0 ? gwarp * per : nW0;
+    const int64_t r1 = r0 + per < nW0 ? r0 + per : nW0;
+    if (r0 >= r1) return;
+    const int nrows = static_cast<int>(r1 - r0);
+    const int64_t e_base = offsets[r0];
+    const T* A0 = A + e_base * NA;
+    const T* B0 = B + e_base * L;
+    const int32_t* J0 = Jw + e_base;
+    T* gA0 = gA != nullptr ? gA + e_base * NA : nullptr;
+    T* gB0 = gB != nullptr ? gB + e_base * L : nullptr;
+    const size_t rowsize = static_cast<size_t>(NO) * L;
+    const T* gO0 = gO + r0 * rowsize;
+    const int64_t w_stride = static_cast<int64_t>(NW) * L;
+    const bool want_a = gA != nullptr, want_bw = gB != nullptr || gW != nullptr;
+
+    int wbase = 0, win = 0;
+    auto load_window = [&](int base) {
+        const int64_t i = r0 + base + 1 + lane;
+        return static_cast<int>(offsets[i < nW0 ? i : nW0] - e_base);
+    };
+    auto row_end = [&](int r) -> int {
+        if (r - wbase >= 32) {
+            wbase = r;
+            win = load_window(wbase);
+        }
+        return __shfl_sync(kFullMask, win, r - wbase);
+    };
+    auto advance = [&](QuadPos p) -> QuadPos {
+        if (!p.valid) return p;
+        p.e += 4;
+        while (p.e >= p.hi) {
+            p.row++;
+            if (p.row >= nrows) {
+                p.valid = false;
+                return p;
+            }
+            p.lo = p.hi;
+            p.hi = row_end(p.row);
+            p.e = p.lo;
+        }
+        return p;
+    };
+    auto load_j = [&](const QuadPos& p) -> int32_t {
+        int32_t j = 0;
+        if (p.valid && lane < 4 && p.e + lane < p.hi) {
+            j = __ldg(J0 + p.e + lane);
+            if (clamp_index(j, static_cast<int32_t>(nW0))) report_bad_index(st, kBitJ);
+        }
+        return j;
+    };
+    auto load_a = [&](int eb, int hi, T (&af)[4], T (&al)[2]) {
+        const int ea = eb + qr;
+        const T* a = A0 + static_cast<int64_t>(ea) * NA + qc;
+#pragma unroll
+        for (int ks = 0; ks < 4; ks++)
+            af[ks] = (ks < KSA && ea < hi && 4 * ks + qc < NA) ? __ldg(a + 4 * ks) : T(0);
+        const int e2 = eb + 2 * qc;
+        const T* a2 = A0 + static_cast<int64_t>(e2) * NA + NA - 1;
+        al[0] = (RANK_A && e2 < hi) ? __ldg(a2) : T(0);
+        al[1] = (RANK_A && e2 + 1 < hi) ? __ldg(a2 + NA) : T(0);
+    };
+    auto phase_a = [&](const T (&af)[4], const T (&al)[2]) {
+        const T* drow = D_s + qr * DS + qc;
+        T* dst = slots + (2 * qc) * ES + qr;
+#pragma unroll
+        for (int t = 0; t < q.nct; t++) {
+            T c[2] = {T(0), T(0)};
+#pragma unroll
+            for (int ks = 0; ks < KSA; ks++) dmma(c, drow[t * 8 * DS + 4 * ks], af[ks]);
+            if (RANK_A) {
+                const T dl = drow[t * 8 * DS + NA - 1 - qc];
+                c[0] = fma(dl, al[0], c[0]);
+                c[1] = fma(dl, al[1], c[1]);
+            }
+            if (8 * t + qr < q.ncc) {
+                dst[8 * t] = c[0];
+                dst[8 * t + ES] = c[1];
+            }
+        }
+    };
+    auto issue = [&](int s, const QuadPos& p, int32_t j_lane, int b0) {
+        if (p.valid) {
+            const int col = 2 * (lane & 15);
+            const bool col_ok = b0 + col < L;
+            T* buf = stages + s * 4 * EB + col + (lane >> 4) * 32;
+            const int src_col = b0 + (col_ok ? col : 0);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int32_t j = __shfl_sync(kFullMask, j_lane, i);
+                const bool ok = col_ok && p.e + i < p.hi;
+                const T* wsrc = W + j * w_stride + src_col + (lane >> 4) * L;
+                const T* bsrc = B0 + static_cast<int64_t>(ok ? p.e + i : p.e) * L + src_col;
+                T* dst = buf + i * EB;
+                const int bytes = ok ? 16 : 0;
+#pragma unroll
+                for (int rr = 0; rr < (NW + 2) / 2; rr++) {
+                    const int r = 2 * rr + (lane >> 4);
+                    if (r <= NW)
+                        cp_async16_zfill(dst + rr * 64,
+                                         r < NW ? wsrc + static_cast<int64_t>(2 * rr) * L : bsrc, bytes);
+                }
+            }
+        }
+        cp_async_commit();
+    };
+
+    // grad_output fragments of the current output row and 32-wide chunk of b
+    T gx[KS3 > 0 ? KS3 : 1][4]; // X: B operand gO[m3 = 4 ks + qc][b0 + 8 nt + qr]
+    T gx8[4][2];                // RANK_3: gO[NO - 1][b0 + 8 nt + 2 qc + h]
+    T gu[MT3][8];               // U: A operand gO[m3 = 8 mt + qr][b0 + 4 kb + qc]
+    T gu8[8];                   // ROW8: gO[8][b0 + 4 kb + qc]
+    auto load_g = [&](int row, int b0) {
+        const T* g = gO0 + row * rowsize + b0;
+        const int width = L - b0;
+#pragma unroll
+        for (int ks = 0; ks < KS3; ks++)
+#pragma unroll
+            for (int nt = 0; nt < 4; nt++) {
+                const int m3 = 4 * ks + qc, b = 8 * nt + qr;
+                gx[ks][nt] = (want_bw && m3 < NO - (RANK_3 ? 1 : 0) && b < width) ? __ldg(g + m3 * L + b) : T(0);
+            }
+#pragma unroll
+        for (int nt = 0; nt < 4; nt++)
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const int b = 8 * nt + 2 * qc + h;
+                gx8[nt][h] = (RANK_3 && want_bw && b < width) ? __ldg(g + (NO - 1) * L + b) : T(0);
+            }
+#pragma unroll
+        for (int mt = 0; mt < MT3; mt++)
+#pragma unroll
+            for (int kb = 0; kb < 8; kb++) {
+                const int m3 = 8 * mt + qr, b = 4 * kb + qc;
+                gu[mt][kb] = (want_a && m3 < NO - (ROW8 ? 1 : 0) && b < width) ? __ldg(g + m3 * L + b) : T(0);
+            }
+#pragma unroll
+        for (int kb = 0; kb < 8; kb++) {
+            const int b = 4 * kb + qc;
+            gu8[kb] = (ROW8 && want_a && b < width) ? __ldg(g + 8 * L + b) : T(0);
+        }
+    };
+
+    for (int b0 = 0; b0 < L; b0 += 32) {
+        const int width = L - b0;
+        wbase = 0;
+        win = load_window(0);
+        QuadPos start;
+        start.row = -1, start.valid = true;
+        start.lo = start.hi = 0;
+        start.e = -4;
+        QuadPos p0 = advance(start);
+        QuadPos p1 = advance(p0), p2 = advance(p1), p3 = advance(p2);
+        int32_t j0 = load_j(p0), j1 = load_j(p1), j2 = load_j(p2), j3 = load_j(p3);
+        issue(0, p0, j0, b0);
+        issue(1, p1, j1, b0);
+        T af[4], al[2], af_n[4], al_n[2];
+        if (p0.valid) load_a(p0.e, p0.hi, af, al);
+        if (p1.valid && ((p1.e - p1.lo) & 7) == 0) load_a(p1.e, p1.hi, af_n, al_n);
+        int s = 0, cur_row = -1;
+        while (p0.valid) {
+            const int in_row = p0.e - p0.lo;
+            const int qi = (in_row >> 2) & 1; // which quad of the batch
+            if ((in_row & 7) == 0 && want_bw) phase_a(af, al);
+            cp_async_wait<1>();
+            __syncwarp();
+            if (p0.row != cur_row) {
+                load_g(p0.row, b0);
+                cur_row = p0.row;
+            }
+            const T* stage = stages + s * 4 * EB;
+            const int my_e = p0.e + qe;        // this lane's edge as a tile row / column
+            const bool ev = my_e < p0.hi;
+            const int32_t jq = __shfl_sync(kFullMask, j0, qe);
+
+            if (want_bw) {
+                const T* tb = slots + (4 * qi + qe) * ES + qc * NW + qh; // + 4 ks NW + 2 mt
+                const T* t8 = slots + (4 * qi + qe) * ES + (NO - 1) * NW + qh;
+                const T* wv = stage + qe * EB + qh * 32 + 2 * qc; // + 2 mt * 32 + 8 nt
+                const T* bv = stage + qe * EB + NW * 32 + 2 * qc; // + 8 nt
+                T* gwp = gW != nullptr
+                             ? gW + jq * w_stride + static_cast<int64_t>(qh) * L + b0 + 2 * qc
+                             : nullptr;
+                T gb[4][2], b2[4][2];
+#pragma unroll
+                for (int nt = 0; nt < 4; nt++) {
+                    const double2 v = *reinterpret_cast<const double2*>(bv + 8 * nt);
+                    b2[nt][0] = v.x, b2[nt][1] = v.y;
+                    gb[nt][0] = gb[nt][1] = T(0);
+                }
+#pragma unroll
+                for (int mt = 0; mt < NMT; mt++) {
+                    const bool m2_ok = 2 * mt + 1 < NW || qh == 0; // lane's m2 = 2 mt + qh
+                    T a[KS3 > 0 ? KS3 : 1];
+#pragma unroll
+                    for (int ks = 0; ks < KS3; ks++)
+                        a[ks] = (m2_ok && 4 * ks + qc < NO - (RANK_3 ? 1 : 0)) ? tb[4 * ks * NW + 2 * mt] : T(0);
+                    const T a8 = (RANK_3 && m2_ok) ? t8[2 * mt] : T(0);
+#pragma unroll
+                    for (int nt = 0; nt < 4; nt++) {
+                        T c[2] = {T(0), T(0)};
+#pragma unroll
+                        for (int ks = 0; ks < KS3; ks++) dmma(c, a[ks], gx[ks][nt]);
+                        if (RANK_3) {
+                            c[0] = fma(a8, gx8[nt][0], c[0]);
+                            c[1] = fma(a8, gx8[nt][1], c[1]);
+                        }
+                        const int b = 8 * nt + 2 * qc;
+                        if (m2_ok) {
+                            const double2 w2 = *reinterpret_cast<const double2*>(wv + 2 * mt * 32 + 8 * nt);
+                            gb[nt][0] = fma(c[0], w2.x, gb[nt][0]);
+                            gb[nt][1] = fma(c[1], w2.y, gb[nt][1]);
+                            if (gwp != nullptr && ev) {
+                                T* gw = gwp + static_cast<int64_t>(2 * mt) * L + 8 * nt;
+                                if (b < width) red_add(gw, c[0] * b2[nt][0]);
+                                if (b + 1 < width) red_add(gw + 1, c[1] * b2[nt][1]);
+                            }
+                        }
+                    }
+                }
+                if (gB0 != nullptr) {
+                    // lanes qh = 0 and qh = 1 hold the two halves of the sum over m2: exchange,
+                    // so that qh = 0 ends with nt = 0, 1 and qh = 1 with nt = 2, 3
+#pragma unroll
+                    for (int i = 0; i < 2; i++) {
+                        T v[2];
+#pragma unroll
+                        for (int h = 0; h < 2; h++) {
+                            const T keep = qh ? gb[2 + i][h] : gb[i][h];
+                            const T send = qh ? gb[i][h] : gb[2 + i][h];
+                            v[h] = keep + __shfl_xor_sync(kFullMask, send, 16);
+                        }
+                        const int b = 8 * (2 * qh + i) + 2 * qc;
+                        T* dst = gB0 + static_cast<int64_t>(my_e) * L + b0 + b;
+                        if (ev && b + 1 < width)
+                            *reinterpret_cast<double2*>(dst) = make_double2(v[0], v[1]);
+                        else if (ev && b < width)
+                            dst[0] = v[0];
+                    }
+                }
+            }
+            __syncwarp(); // every lane has read T of this quad: the slots may take U
+            if (want_a) {
+                const T* wu = stage + qe * EB + qh * 32 + qc; // + 2 nt * 32 + 4 kb
+                const T* bu = stage + qe * EB + NW * 32 + qc; // + 4 kb
+                T bbu[8];
+#pragma unroll
+                for (int kb = 0; kb < 8; kb++) bbu[kb] = bu[4 * kb];
+                // column n = 2 qc + h of tile nt is (edge 2 (qc & 1) + h, m2 = 2 nt + (qc >> 1))
+                T* us = slots + (4 * qi + 2 * (qc & 1)) * ES + qr * NW + (qc >> 1);
+#pragma unroll
+                for (int nt = 0; nt < NMT; nt++) {
+                    T u[MT3][2], u8 = T(0);
+#pragma unroll
+                    for (int mt = 0; mt < MT3; mt++) u[mt][0] = u[mt][1] = T(0);
+#pragma unroll
+                    for (int kb = 0; kb < 8; kb++) {
+                        const T bw = wu[2 * nt * 32 + 4 * kb] * bbu[kb];
+#pragma unroll
+                        for (int mt = 0; mt < MT3; mt++) dmma(u[mt], gu[mt][kb], bw);
+                        if (ROW8) u8 = fma(gu8[kb], bw, u8);
+                    }
+                    const bool col_ok = 2 * nt + 1 < NW || (qc >> 1) == 0;
+#pragma unroll
+                    for (int mt = 0; mt < MT3; mt++) {
+                        if (col_ok && 8 * mt + qr < NO - (ROW8 ? 1 : 0)) {
+                            us[8 * mt * NW + 2 * nt] = u[mt][0];
+                            us[8 * mt * NW + 2 * nt + ES] = u[mt][1];
+                        }
+                    }
+                    if (ROW8) {
+                        u8 += __shfl_xor_sync(kFullMask, u8, 1);
+                        u8 += __shfl_xor_sync(kFullMask, u8, 2);
+                        // the lane's column as the B operand: edge qe, m2 = 2 nt + qh
+                        if (qc == 0 && (2 * nt + 1 < NW || qh == 0))
+                            slots[(4 * qi + qe) * ES + 8 * NW + 2 * nt + qh] = u8;
+                    }
+                }
+            }
+            __syncwarp(); // stage s is free; U of this quad is in the slots
+            issue(s, p2, j2, b0);
+            const bool batch_end = !p1.valid || ((p1.e - p1.lo) & 7) == 0;
+            if (want_a && batch_end) {
+                // grad_A[e, m] = sum_cell U[e, cell] D[cell, m] for the batch's eight edges
+                T ga[NTA][2], ga8 = T(0);
+#pragma unroll
+                for (int nt = 0; nt < NTA; nt++) ga[nt][0] = ga[nt][1] = T(0);
+                const T* ur = slots + qr * ES + qc;
+                const T* dc = D_s + qc * DS + qr;
+#pragma unroll 7
+                for (int kc = 0; kc < KC; kc++) {
+                    const T au = ur[4 * kc];
+#pragma unroll
+                    for (int nt = 0; nt < NTA; nt++) dmma(ga[nt], au, dc[4 * kc * DS + 8 * nt]);
+                    if (COL8) ga8 = fma(au, D_s[(4 * kc + qc) * DS + 8], ga8);
+                }
+                const int eb = p0.e - (in_row & 4);
+                const bool ok = eb + qr < p0.hi;
+                T* dst = gA0 + static_cast<int64_t>(eb + qr) * NA;
+#pragma unroll
+                for (int nt = 0; nt < NTA; nt++)
+#pragma unroll
+                    for (int h = 0; h < 2; h++) {
+                        const int m = 8 * nt + 2 * qc + h;
+                        if (ok && m < NA - (COL8 ? 1 : 0))
+                            dst[m] = b0 > 0 ? dst[m] + ga[nt][h] : ga[nt][h];
+                    }
+                if (COL8) {
+                    ga8 += __shfl_xor_sync(kFullMask, ga8, 1);
+                    ga8 += __shfl_xor_sync(kFullMask, ga8, 2);
+                    if (ok && qc == 0) dst[8] = b0 > 0 ? dst[8] + ga8 : ga8;
+                }
+                __syncwarp(); // the slots are rewritten by the next batch's phase A
+            }
+            if (p1.valid && ((p1.e - p1.lo) & 7) == 0) {
+#pragma unroll
+                for (int ks = 0; ks < 4; ks++) af[ks] = af_n[ks];
+                al[0] = al_n[0], al[1] = al_n[1];
+            }
+            p0 = p1, p1 = p2, p2 = p3;
+            j0 = j1, j1 = j2, j2 = j3;
+            p3 = advance(p3);
+            j3 = load_j(p3);
+            if (p1.valid && ((p1.e - p1.lo) & 7) == 0) load_a(p1.e, p1.hi, af_n, al_n);
+            s ^= 1;
+        }
+        cp_async_wait<0>();
+        __syncwarp();
+    }
+}
+
 // Any sizes, no shared memory: one thread per (edge, b) walking the whole coupling table.
 // Needs zero-filled O (forward) / gA, gW (VJP).
 template <typename T>
@@ -1954,7 +2337,8 @@ template <typename T> bool forward_mma(const Call& call, T* O, const Problem<T>&
 }
 
 template <typename T, int TP, int KS3>
-bool backward_mma_launch(const Call& call, T* gA, T* gB, T* gW, const T* gO, const Problem<T>& p) {
+bool backward_mma_launch(const Call& call, T* gA, T* gB, T* gW, const T* gO, const Problem<T>& p,
+                         bool only_if_unsorted) {
     using Lay = VjpMma<TP>;
     const int warps = 4;
     const size_t smem =
@@ -1964,17 +2348,67 @@ bool backward_mma_launch(const Call& call, T* gA, T* gB, T* gW, const T* gO, con
     void* scratch = nullptr;
     if (!build_coupling(call, p, cp, &scratch, Lay::TS, Lay::d_stride(p.nA), true)) return false;
     allow_smem(sasaw_vjp_mma<TP, KS3>, smem);
-    note_kernel_f("sasaw_vjp_mma<TP=%d,KS3=%d>", TP, KS3);
+    if (!only_if_unsorted) note_kernel_f("sasaw_vjp_mma<TP=%d,KS3=%d>", TP, KS3);
     const bool wide_copies = p.L % 2 == 0 && reinterpret_cast<uintptr_t>(p.W) % 16 == 0 &&
                              reinterpret_cast<uintptr_t>(p.B) % 16 == 0;
     const int64_t blocks = std::min<int64_t>(ceil_div(ceil_div(p.E, 8), warps),
                                              static_cast<int64_t>(sm_count(call.device)) * 3);
     sasaw_vjp_mma<TP, KS3><<<static_cast<unsigned>(blocks), warps * 32, smem, call.stream>>>(
         gA, gB, gW, gO, p.A, p.B, p.W, p.Jw, p.Io, cp, p.E, p.nA, p.L, p.nW0, p.nW1, p.nO1,
-        wide_copies, call.status);
+        wide_copies, only_if_unsorted, call.status);
     MOPS_CUDA_OK(cudaGetLastError());
     scratch_free(call, scratch);
     return true;
+}
+
+// VJP through the quad kernel (sorted scatter index, compiled-in widths). Returns 0 when it
+// does not apply, 1 when it ran and the index was seen to be sorted, 2 when it was launched
+// but the edge-by-edge kernel must still be enqueued for the unsorted case.
+template <typename T>
+int backward_quad(const Call& call, T* gA, T* gB, T* gW, const T* gO, const Problem<T>& p) {
+    if constexpr (!std::is_same<T, double>::value) {
+        return 0;
+    } else {
+        if (env_flag("MOPS_B200_SASAW_QUAD", 1) == 0) return 0;
+        if (!(p.nA == 9 && p.nW1 == 9 && p.nO1 == 9)) return 0;
+        auto aligned = [](const void* ptr) { return reinterpret_cast<uintptr_t>(ptr) % 16 == 0; };
+        if (p.L % 2 != 0 || !aligned(p.W) || !aligned(p.B) || !aligned(gB)) return 0;
+        constexpr QuadLayout q = quad_layout(9, 9, 9);
+        const size_t d_bytes = static_cast<size_t>(q.d_scalars) * sizeof(T);
+        const size_t warp_bytes = static_cast<size_t>(q.warp_scalars) * sizeof(T);
+        const size_t limit = static_cast<size_t>(max_optin_smem(call.device));
+        if (d_bytes + 2 * warp_bytes > limit) return 0;
+        const int warps = static_cast<int>(std::min<size_t>(8, (limit - d_bytes) / warp_bytes));
+        const size_t smem = d_bytes + warps * warp_bytes;
+        const int sms = sm_count(call.device);
+        Coupling<T> cp{};
+        void* scratch = nullptr;
+        if (!build_coupling(call, p, cp, &scratch, p.nW1, q.DS, false)) return 0;
+        int64_t* offsets =
+            static_cast<int64_t*>(scratch_alloc(call, (p.nW0 + 1) * sizeof(int64_t)));
+        const int64_t pre_blocks = std::min<int64_t>(ceil_div(p.E + 1, 256), sms * 32);
+        segment_offsets<<<static_cast<unsigned>(pre_blocks), 256, 0, call.stream>>>(
+            p.Io, p.E, p.nW0, offsets, call.status);
+        const unsigned blocks = static_cast<unsigned>(std::min<int64_t>(ceil_div(p.nW0, warps), sms));
+        note_kernel_f("sasaw_vjp_quad<9,9,9,L=%d> warps=%d", p.L == 32 ? 32 : 0, warps);
+        if (p.L == 32) {
+            allow_smem(sasaw_vjp_quad<9, 9, 9, 32>, smem);
+            sasaw_vjp_quad<9, 9, 9, 32><<<blocks, warps * 32, smem, call.stream>>>(
+                gA, gB, gW, gO, p.A, p.B, p.W, p.Jw, offsets, cp, p.L, p.nW0, call.status);
+        } else {
+            allow_smem(sasaw_vjp_quad<9, 9, 9, 0>, smem);
+            sasaw_vjp_quad<9, 9, 9, 0><<<blocks, warps * 32, smem, call.stream>>>(
+                gA, gB, gW, gO, p.A, p.B, p.W, p.Jw, offsets, cp, p.L, p.nW0, call.status);
+        }
+        MOPS_CUDA_OK(cudaGetLastError());
+        scratch_free(call, offsets);
+        scratch_free(call, scratch);
+        if (call.wait) {
+            wait_stream(call);
+            if (!host_saw_unsorted(call)) return 1;
+        }
+        return 2;
+    }
 }
 
 // Tensor-core VJP: f64, A.shape[1], W.shape[1] and output_size all between 1 and 16.
@@ -1985,9 +2419,13 @@ bool backward_mma(const Call& call, T* gA, T* gB, T* gW, const T* gO, const Prob
     } else {
         const int tp = fast_width(p.nW1), op = fast_width(p.nO1);
         if (tp == 0 || op == 0 || fast_width(p.nA) == 0) return false;
+        const int quad = backward_quad(call, gA, gB, gW, gO, p);
+        if (quad == 1) return true;
+        const bool rest = quad == 2; // only what the quad kernel left: an unsorted index
         switch (tp * 100 + op) {
 #define MOPS_B200_CASE(TP_, OP_)                                                                   \
-    case TP_ * 100 + OP_: return backward_mma_launch<T, TP_, OP_ / 4>(call, gA, gB, gW, gO, p);
+    case TP_ * 100 + OP_:                                                                          \
+        return backward_mma_launch<T, TP_, OP_ / 4>(call, gA, gB, gW, gO, p, rest);
             MOPS_B200_CASE(4, 4) MOPS_B200_CASE(4, 8) MOPS_B200_CASE(4, 12) MOPS_B200_CASE(4, 16)
             MOPS_B200_CASE(8, 4) MOPS_B200_CASE(8, 8) MOPS_B200_CASE(8, 12) MOPS_B200_CASE(8, 16)
             MOPS_B200_CASE(12, 4) MOPS_B200_CASE(12, 8) MOPS_B200_CASE(12, 12) MOPS_B200_CASE(12, 16)
