@@ -230,6 +230,28 @@ class ClockSampler(threading.Thread):
                 "samples": len(self.samples)}
 
 
+def bind_to_gpu_numa_node(pci_bus_id):
+    """Runs this process on the CPUs of the NUMA node the GPU hangs off, so that the pinned
+    host buffers of the end-to-end leg (allocated afterwards) are local to the GPU's PCIe root
+    and the copies do not cross the socket interconnect. Best effort; returns the node or None."""
+    try:
+        dev = pci_bus_id.lower()
+        node = int(open(f"/sys/bus/pci/devices/{dev}/numa_node").read().strip())
+        if node < 0:
+            return None
+        cpus = set()
+        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+            a, _, b = part.partition("-")
+            cpus.update(range(int(a), int(b or a) + 1))
+        cpus &= set(os.sched_getaffinity(0))
+        if not cpus:
+            return None
+        os.sched_setaffinity(0, cpus)
+        return node
+    except (OSError, ValueError, AttributeError):
+        return None
+
+
 def physical_gpu_index(local):
     vis = os.environ.get("CUDA_VISIBLE_DEVICES")
     if vis:
@@ -516,6 +538,12 @@ def main():
         raise SystemExit("bench.py --impl ours needs a CUDA device (no CPU fallback exists)")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    props = torch.cuda.get_device_properties(dev)
+    try:
+        pci = "%04x:%02x:%02x.0" % (props.pci_domain_id, props.pci_bus_id, props.pci_device_id)
+    except (AttributeError, TypeError):
+        pci = ""
+    numa_node = bind_to_gpu_numa_node(pci)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         # keep stdout for the one JSON line: NCCL's version / debug lines go to stderr
@@ -583,10 +611,7 @@ def main():
     last = {}
     for s in range(args.steps):
         for i, n in enumerate(names):
-            res = run_case(n, devd[n], events[s][i])
-            if s == args.steps - 1:
-                last[n] = res  # kept for the parity check (earlier steps free theirs at once)
-            del res
+            run_case(n, devd[n], events[s][i])
     stop.record()
     barrier()
     sampler.enabled = False
@@ -598,9 +623,14 @@ def main():
     step_bytes = sum(sum(nbytes[n]) for n in names)
     value = step_bytes * world * args.steps / (t_ms / 1e3) / 1e9
 
-    # ---- parity of the timed buffers (rank 0's), outside the timed region
+    # ---- parity, outside the timed region: one more (untimed) pass over the very input buffers
+    # that were timed, one case at a time, its results checked against the CPU oracle. (Keeping
+    # the timed steps' own results alive would make the allocator fetch new memory inside the
+    # timed region.)
     verified = {}
     if not args.no_verify and rank == 0 and SCALE == 1:
+        for n in names:
+            last[n] = None
         sys.path.insert(0, os.path.join(ROOT, "tests"))
         import subrange
         from oracle.mops_oracle import Oracle
@@ -608,6 +638,7 @@ def main():
         for n in names:
             op = CASES[n][0]
             d = {k: (v.numpy() if isinstance(v, torch.Tensor) else v) for k, v in host[n].items()}
+            last[n] = run_case(n, devd[n], reduce=False)
             results = named_results(op, *last[n])
 
             def library_vjp(sub, op=op):
@@ -615,8 +646,6 @@ def main():
                          if isinstance(v, np.ndarray) else v) for k, v in sub.items()}
                 return api(op)[1](*vjp_args(op, t))[2]
 
-            if reduce_gw and "grad_W" in results:
-                results = {k: v for k, v in results.items() if k != "grad_W"}  # summed over ranks
             try:
                 report = subrange.check_case(oracle, op, d, results, inputs=devd[n],
                                              library_vjp=library_vjp)
@@ -626,6 +655,8 @@ def main():
                                "worst_rel_to_max": worst}
             except subrange.Mismatch as e:
                 verified[n] = {"verified": False, "error": str(e)}
+            last[n] = None
+            del results
     last.clear()
 
     # ---- spread of every call: the same calls again, each one between its own pair of events
@@ -742,7 +773,8 @@ def main():
         e2e = {"value": step_bytes * world * e2e_steps / t_e2e / 1e9, "unit": "GB/s",
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                "ms_per_step": t_e2e / e2e_steps * 1e3,
-               "api": "mops_b200.<op>(pinned host arrays) inside mops_b200.HostQueue"}
+               "api": "mops_b200.<op>(pinned host arrays) inside mops_b200.HostQueue",
+               "host_numa_node": numa_node}
     sampler.stop()
 
     small = None

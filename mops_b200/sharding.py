@@ -60,7 +60,8 @@ def shard_scatter(arrays, index_name, n_rows, world, rank, per_entry):
     lo, hi = eps[rank], eps[rank + 1]
     local = dict(arrays)
     for name in per_entry:
-        local[name] = arrays[name][lo:hi]
+        if name in arrays:
+            local[name] = arrays[name][lo:hi]
     local[index_name] = arrays[index_name][lo:hi] - rho[rank]
     return local, (rho[rank], rho[rank + 1])
 

@@ -113,3 +113,51 @@ def test_two_rank_sharding_matches_unsharded_results():
         mp.spawn(_worker, args=(world, port, results), nprocs=world, join=True)
         got = dict(results)
     assert got and all(got.values()), got
+
+
+# ------------------------------------------------------------------ shards on a GPU
+SHARD_CASES = {"hpe": dict(I=9000, N=30, J=200, K=4), "sap": dict(I=9000),
+               "opsa": dict(J=200000, nO=3000), "opsaw": dict(E=120000, n=2000),
+               "sasaw": dict(E=60000, n=1000)}
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("world", [2, 3])
+@pytest.mark.parametrize("op", sorted(SHARD_CASES))
+def test_shards_run_on_the_gpu_assemble_to_the_unsharded_result(oracle, op, world):
+    """The ranks' shards of one problem (cut by mops_b200.sharding exactly as bench.py's
+    strong-scaling leg cuts them) are run one after the other on one GPU; the assembled
+    output, the concatenated per-row / per-entry gradients and the summed grad_W must equal
+    the unsharded GPU result, and match the oracle on sub-ranges."""
+    import subrange
+    from conftest import assert_parity
+    from helpers import run_library, to_dev
+    d = workloads.GENERATORS[op](**SHARD_CASES[op])
+    full = run_library(op, to_dev(d, np.float64))
+    parts = []
+    for rank in range(world):
+        if op in ("hpe", "sap"):
+            a, b = sharding.batch_range(d["A"].shape[0], world, rank)
+            loc = {k: (v[a:b] if k in ("A", "B", "grad_output") else v) for k, v in d.items()}
+        else:
+            key = "indices_output_1" if op == "sasaw" else "indices_output"
+            n_rows = d["output_size"] if op == "opsa" else d["W"].shape[0]
+            loc, (r0, r1) = sharding.shard_scatter(d, key, n_rows, world, rank,
+                                                   ("A", "B", "indices_W", "indices_W_1"))
+            if op == "opsa":   # the output itself is sharded by rows
+                loc["output_size"] = r1 - r0
+                loc["grad_output"] = d["grad_output"][r0:r1]
+            else:              # W couples all rows: full-height output, other rows stay zero
+                loc[key] = loc[key] + r0
+        parts.append(run_library(op, to_dev(loc, np.float64)))
+    cat = lambda k: np.concatenate([p[k] for p in parts], axis=0)
+    got = {}
+    if op in ("hpe", "sap", "opsa"):
+        got = {k: cat(k) for k in full}
+    else:
+        got["output"] = sum(p["output"] for p in parts)
+        got["grad_A"], got["grad_B"] = cat("grad_A"), cat("grad_B")
+        got["grad_W"] = sum(p["grad_W"] for p in parts)
+    for k in full:
+        assert_parity(got[k], full[k], f"{op}/{k} from {world} shards")
+    subrange.check_case(oracle, op, d, got)
