@@ -400,6 +400,7 @@ def gpu_small_configs(names, dev):
     """Call latency through the C ABI (mops_cuda_*: device pointers, complete on return) at
     the small configurations: wall-clock time of >= 100 synchronous calls each."""
     import torch
+    import mops_b200 as M
     from mops_b200 import _lib
     lib = _lib.library()
     out = {}
@@ -430,6 +431,20 @@ def gpu_small_configs(names, dev):
             m, p10, p90 = quantiles(ts)
             res.update({f"{tag}_us_median": m, f"{tag}_us_p10": p10, f"{tag}_us_p90": p90,
                         f"{tag}_kernels": _lib.last_kernels()})
+            # the same calls with a plan bound: tables are built by the first call only
+            with M.Plan() as plan:
+                for _ in range(10):
+                    _lib.check_status(fn(*structs))
+                ts = []
+                for _ in range(200):
+                    t0 = time.perf_counter()
+                    status = fn(*structs)
+                    ts.append((time.perf_counter() - t0) * 1e6)
+                    _lib.check_status(status)
+                m, p10, p90 = quantiles(ts)
+                res.update({f"{tag}_planned_us_median": m, f"{tag}_planned_us_p10": p10,
+                            f"{tag}_planned_us_p90": p90, f"{tag}_plan_tables": plan.tables})
+            plan.close()
         res["reps"] = 200
         out[n] = res
     return out

@@ -190,6 +190,32 @@ MOPS_EXPORT int mops_b200_get_wait(void);
  * their own. Do not hand one thread's stream to mops_b200_set_stream of another thread while
  * asynchronous calls of both are in flight on it unless the application orders them itself. */
 
+/* ---- Plans: device tables built once and reused (no counterpart in the reference, which
+ * rebuilds its first-occurrence table on every call, mops/src/internal/
+ * cuda_first_occurences.cu:82-117, and has no caller-visible object for it).
+ * Every operation first turns its index (and coefficient) arrays into a device table: the
+ * segment offsets of a scatter index (indices_output of OPSA / OPSAW, indices_output_1 of
+ * SASAW), HPE's packed monomial records, SAP's sorted triplets, SASAW's grouped coupling
+ * table. While a plan is bound to the calling thread, each such table is built by the first
+ * mops_cuda_* call that needs it and kept in the plan; later calls whose index arrays have
+ * the same device addresses and sizes reuse it. The forward and the VJP of one graph then
+ * share one segment table, no table is rebuilt, and calls with a sorted scatter index no
+ * longer wait for the device in mid-call to learn that it is sorted.
+ * Contract: while a plan holds tables derived from an array, the caller must not change that
+ * array's contents (or free it and reuse the address for other data); destroy the plan, or
+ * use a new one, when the graph changes. An unsorted scatter index, or one with out-of-range
+ * values, is not kept: such calls behave as without a plan. The call that builds a table
+ * waits for the stream once. Plans may be bound in several threads at the same time.
+ * mops_b200_plan_create / _destroy return 0 on success, 1 on error. */
+typedef struct mops_b200_plan mops_b200_plan_t;
+MOPS_EXPORT int mops_b200_plan_create(mops_b200_plan_t** plan);
+MOPS_EXPORT int mops_b200_plan_destroy(mops_b200_plan_t* plan);
+/* Binds `plan` to the calling thread (NULL unbinds). */
+MOPS_EXPORT void mops_b200_plan_bind(mops_b200_plan_t* plan);
+MOPS_EXPORT mops_b200_plan_t* mops_b200_plan_bound(void);
+/* Number of tables the plan currently holds. */
+MOPS_EXPORT int mops_b200_plan_tables(const mops_b200_plan_t* plan);
+
 /* Names (with template arguments) of the main kernels the calling thread's last mops_cuda_*
  * call dispatched to, "; "-separated; valid until that thread's next call. For tools that
  * pair a timing with the profile of the same kernel instantiation. */

@@ -21,6 +21,7 @@ Differences from the reference front end: no CuPy dispatch (CuPy is replaced by 
 tensors); OPSAW and SASAW run on the GPU instead of raising "CUDA implementation does not
 exist yet".
 """
+import ctypes
 import threading
 
 import numpy as np
@@ -28,8 +29,8 @@ import numpy as np
 from . import _lib
 from ._lib import MopsError  # noqa: F401
 
-__all__ = [f"{op}{lvl}" for op in _lib.OPERATIONS for lvl in _lib.LEVELS] + ["MopsError",
-                                                                             "HostQueue"]
+__all__ = [f"{op}{lvl}" for op in _lib.OPERATIONS for lvl in _lib.LEVELS] + [
+    "MopsError", "HostQueue", "Plan"]
 
 
 def _torch():
@@ -77,6 +78,51 @@ def _check(array, ndim, kind, operation, name):
 def _check_scalar(value, operation, name):
     if not isinstance(value, (int, np.integer)) or isinstance(value, bool):
         raise TypeError(f"`{name}` must be a scalar in {operation}, got {type(value)}")
+
+
+class Plan:
+    """Device tables built once and reused (``mops_b200_plan_*`` of the C ABI).
+
+    Inside ``with plan:`` every operation called on CUDA tensors builds the table it derives
+    from its index (and coefficient) arrays only the first time it sees those arrays (same
+    device addresses and sizes) and reuses it afterwards: the segment offsets of a sorted
+    scatter index are shared by the forward and the VJP of one graph, HPE / SAP / SASAW
+    coupling tables are not rebuilt, and sorted scatter calls no longer stop mid-way to ask
+    the device whether the index was sorted. The caller must keep the index tensors alive and
+    unchanged while the plan holds tables for them. Binding is per thread: operations that
+    run on another thread (torch's autograd engine) do not see it."""
+
+    def __init__(self):
+        handle = ctypes.c_void_p()
+        _lib.check_status(_lib.library().mops_b200_plan_create(ctypes.byref(handle)))
+        self._handle = handle
+        self._previous = None
+
+    def __enter__(self):
+        lib = _lib.library()
+        self._previous = lib.mops_b200_plan_bound()
+        lib.mops_b200_plan_bind(self._handle)
+        return self
+
+    def __exit__(self, *exc):
+        _lib.library().mops_b200_plan_bind(self._previous)
+        return False
+
+    @property
+    def tables(self):
+        """Number of tables the plan holds."""
+        return int(_lib.library().mops_b200_plan_tables(self._handle))
+
+    def close(self):
+        if self._handle is not None:
+            _lib.library().mops_b200_plan_destroy(self._handle)
+            self._handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 class HostQueue:

@@ -30,6 +30,8 @@ def abi_symbols():
 
 EXTENSION_SYMBOLS = ("mops_b200_set_stream", "mops_b200_get_stream", "mops_b200_set_wait",
                      "mops_b200_get_wait", "mops_b200_version", "mops_b200_last_kernels",
+                     "mops_b200_plan_create", "mops_b200_plan_destroy", "mops_b200_plan_bind",
+                     "mops_b200_plan_bound", "mops_b200_plan_tables",
                      "mops_b200_cuda_sparse_accumulation_scatter_add_with_weights_noalloc_f64")
 
 
@@ -58,6 +60,12 @@ def library():
         lib.mops_get_last_error_message.restype = ctypes.c_char_p
         lib.mops_b200_version.restype = ctypes.c_char_p
         lib.mops_b200_last_kernels.restype = ctypes.c_char_p
+        lib.mops_b200_plan_create.argtypes = [ctypes.POINTER(ctypes.c_void_p)]
+        lib.mops_b200_plan_destroy.argtypes = [ctypes.c_void_p]
+        lib.mops_b200_plan_bind.argtypes = [ctypes.c_void_p]
+        lib.mops_b200_plan_bind.restype = None
+        lib.mops_b200_plan_bound.restype = ctypes.c_void_p
+        lib.mops_b200_plan_tables.argtypes = [ctypes.c_void_p]
         lib.mops_b200_set_stream.argtypes = [ctypes.c_void_p]
         lib.mops_b200_get_stream.restype = ctypes.c_void_p
         lib.mops_b200_set_wait.argtypes = [ctypes.c_int]

@@ -156,5 +156,24 @@ extern "C" void mops_b200_set_stream(void* stream) { mops_b200::set_stream(strea
 extern "C" void* mops_b200_get_stream(void) { return mops_b200::get_stream(); }
 extern "C" void mops_b200_set_wait(int wait) { mops_b200::set_wait(wait != 0); }
 extern "C" int mops_b200_get_wait(void) { return mops_b200::get_wait() ? 1 : 0; }
+extern "C" int mops_b200_plan_create(mops_b200_plan_t** plan) {
+    return guarded([&] {
+        if (plan == nullptr) throw std::runtime_error("mops_b200_plan_create: plan is NULL");
+        *plan = reinterpret_cast<mops_b200_plan_t*>(mops_b200::plan_create());
+    });
+}
+extern "C" int mops_b200_plan_destroy(mops_b200_plan_t* plan) {
+    return guarded([&] { mops_b200::plan_destroy(reinterpret_cast<mops_b200::TablePlan*>(plan)); });
+}
+extern "C" void mops_b200_plan_bind(mops_b200_plan_t* plan) {
+    mops_b200::plan_bind(reinterpret_cast<mops_b200::TablePlan*>(plan));
+}
+extern "C" mops_b200_plan_t* mops_b200_plan_bound(void) {
+    return reinterpret_cast<mops_b200_plan_t*>(mops_b200::plan_bound());
+}
+extern "C" int mops_b200_plan_tables(const mops_b200_plan_t* plan) {
+    return mops_b200::plan_table_count(reinterpret_cast<const mops_b200::TablePlan*>(plan));
+}
+
 extern "C" const char* mops_b200_last_kernels(void) { return mops_b200::last_kernels(); }
 extern "C" const char* mops_b200_version(void) { return "mops-b200 0.1 (sm_100a)"; }

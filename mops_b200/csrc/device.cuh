@@ -11,6 +11,7 @@
 #ifndef MOPS_B200_DEVICE_CUH
 #define MOPS_B200_DEVICE_CUH
 
+#include <algorithm>
 #include <cstdint>
 
 #include "runtime.hpp"
@@ -69,6 +70,51 @@ __device__ __forceinline__ int64_t warp_lower_bound(const int32_t* __restrict__ 
         hi = new_hi;
     }
     return lo;
+}
+
+// Number of i in [0, n) with t[i] + row_weight * i <= x, for an ascending table t, found by
+// the whole warp with 32-way probes (as warp_lower_bound). All lanes call it with the same
+// arguments.
+__device__ __forceinline__ int64_t warp_count_weighted_le(const int64_t* __restrict__ t, int64_t n,
+                                                          int64_t row_weight, int64_t x, int lane) {
+    int64_t lo = 0, hi = n;
+    while (hi > lo) {
+        const int64_t len = hi - lo;
+        const int64_t chunk = (len + 31) / 32; // >= 1
+        const int64_t probe = lo + (lane + 1) * chunk - 1;
+        const bool le = (probe < hi) && (t[probe] + row_weight * probe <= x);
+        const int c = __popc(__ballot_sync(kFullMask, le));
+        const int64_t new_lo = lo + c * chunk;
+        if (new_lo >= hi) {
+            lo = hi;
+            break;
+        }
+        int64_t new_hi = new_lo + chunk - 1;
+        if (new_hi > hi) new_hi = hi;
+        lo = new_lo;
+        hi = new_hi;
+    }
+    return lo;
+}
+
+// Splits the rows of a segment table among `parts` workers so that every worker gets whole
+// rows and about the same amount of work, counted as entries + kRowWeight per row: not the
+// same number of rows (the rows of a shard of a larger problem, or of an uneven graph, can be
+// mostly empty), and not entries alone either (a long run of empty rows still has to be
+// written). offsets[0 .. n_rows] ascending, offsets[n_rows] = number of entries. Returns the
+// first row of worker `part`, who owns rows [split(part), split(part + 1)). All lanes of a
+// warp call it together.
+constexpr int64_t kRowWeight = 4;
+__device__ __forceinline__ int64_t balanced_row_split(const int64_t* __restrict__ offsets,
+                                                      int64_t n_rows, int64_t part, int64_t parts,
+                                                      int lane) {
+    if (part <= 0) return 0;
+    if (part >= parts) return n_rows;
+    const int64_t total = offsets[n_rows] + kRowWeight * n_rows;
+    const int64_t target = total / parts * part + total % parts * part / parts;
+    // the last row whose weighted start is <= target
+    const int64_t r = warp_count_weighted_le(offsets, n_rows + 1, kRowWeight, target, lane) - 1;
+    return r < 0 ? 0 : (r > n_rows ? n_rows : r);
 }
 
 // Bounds [begin, end) of the entries whose (sorted) index equals r.
@@ -199,6 +245,37 @@ static __global__ void segment_offsets(const int32_t* __restrict__ P, int64_t J,
 }
 
 __host__ __device__ constexpr int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// The segment table of a scatter index for one call: taken from the calling thread's plan when
+// it has one for this index (then the index is known to be sorted and nothing is launched),
+// else built on the call's stream into call-scoped (or, for a plan's first use, plan-owned)
+// memory. release_table(call, t.ref) when the kernels that read it are enqueued.
+struct SegmentTable {
+    int64_t* offsets;
+    TableRef ref;
+    bool known_sorted; // no need to ask the device, no fallback kernels
+};
+
+inline SegmentTable segment_table(const Call& call, const int32_t* P, int64_t J, int64_t n_rows) {
+    TableKey key{};
+    key.kind = kSegmentTable;
+    key.ptr[0] = P;
+    key.n[0] = J;
+    key.n[1] = n_rows;
+    SegmentTable t;
+    t.ref = acquire_table(call, key, static_cast<size_t>(n_rows + 1) * sizeof(int64_t));
+    t.offsets = static_cast<int64_t*>(t.ref.ptr);
+    if (t.ref.fresh) {
+        const int64_t blocks =
+            std::min<int64_t>(ceil_div(J + 1, 256), static_cast<int64_t>(sm_count(call.device)) * 32);
+        segment_offsets<<<static_cast<unsigned>(blocks > 0 ? blocks : 1), 256, 0, call.stream>>>(
+            P, J, n_rows, t.offsets, call.status);
+        MOPS_CUDA_OK(cudaGetLastError());
+        commit_table(call, t.ref);
+    }
+    t.known_sorted = t.ref.owned_by_plan && t.ref.sorted;
+    return t;
+}
 
 } // namespace mops_b200
 

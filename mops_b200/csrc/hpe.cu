@@ -497,7 +497,7 @@ template <typename T, int K> size_t vjp_smem(int N, int rows_per_lane = 1) {
 
 // Allocates the call-scoped tables and runs the plan kernel.
 template <typename T>
-HpePlan make_plan(const Call& call, void** scratch, const T* C, const int32_t* P, int64_t J,
+HpePlan make_plan(const Call& call, TableRef* scratch, const T* C, const int32_t* P, int64_t J,
                   int K, int N, bool want_fwd, bool want_vjp, int pad = kPad) {
     auto up = [](size_t n) { return (n + 255) / 256 * 256; };
     const size_t M = static_cast<size_t>(J) * K;
@@ -505,9 +505,14 @@ HpePlan make_plan(const Call& call, void** scratch, const T* C, const int32_t* P
     const size_t b_vjp = want_vjp ? up(M * record_bytes(sizeof(T), K - 1)) : 0;
     const size_t b_n = up((static_cast<size_t>(N) + 1) * sizeof(int32_t));
     const size_t b_cur = up((kPlanThreads / 32) * (static_cast<size_t>(N) + 1) * sizeof(int32_t));
-    unsigned char* p =
-        static_cast<unsigned char*>(scratch_alloc(call, b_fwd + b_vjp + b_n + b_cur + 256));
-    *scratch = p;
+    TableKey key{};
+    key.kind = kHpeTable;
+    key.scalar_bytes = static_cast<int>(sizeof(T));
+    key.ptr[0] = C, key.ptr[1] = P;
+    key.n[0] = J, key.n[1] = K, key.n[2] = N, key.n[3] = want_fwd ? 1 : 0;
+    key.n[4] = want_vjp ? 1 : 0, key.n[5] = pad;
+    *scratch = acquire_table(call, key, b_fwd + b_vjp + b_n + b_cur + 256);
+    unsigned char* p = static_cast<unsigned char*>(scratch->ptr);
     HpePlan plan;
     plan.fwd_rec = p;
     p += b_fwd;
@@ -518,9 +523,12 @@ HpePlan make_plan(const Call& call, void** scratch, const T* C, const int32_t* P
     plan.cursor = reinterpret_cast<int32_t*>(p);
     p += b_cur;
     plan.split = reinterpret_cast<int32_t*>(p);
-    hpe_plan<T><<<1, kPlanThreads, 0, call.stream>>>(plan, C, P, static_cast<int>(J), K, N,
-                                                     want_fwd, want_vjp, pad, call.status);
-    MOPS_CUDA_OK(cudaGetLastError());
+    if (scratch->fresh) {
+        hpe_plan<T><<<1, kPlanThreads, 0, call.stream>>>(plan, C, P, static_cast<int>(J), K, N,
+                                                         want_fwd, want_vjp, pad, call.status);
+        MOPS_CUDA_OK(cudaGetLastError());
+        commit_table(call, *scratch);
+    }
     return plan;
 }
 
@@ -532,7 +540,7 @@ void launch_fwd(const Call& call, T* O, const T* A, const T* C, const int32_t* P
     const bool two = I >= static_cast<int64_t>(sm_count(call.device)) * 64 * 8 &&
                      smem2 <= 75 * 1024 && static_cast<int64_t>(N) * 65 <= 65535;
     const size_t smem = two ? smem2 : fwd_smem<T, K>(N);
-    void* scratch = nullptr;
+    TableRef scratch{};
     HpePlan plan = make_plan<T>(call, &scratch, C, P, J, K, N, true, false, two ? 65 : kPad);
     note_kernel_f("hpe_fwd_rows<%s,K=%d,R=%d>", scalar_name<T>(), K, two ? 2 : 1);
     if (two) {
@@ -551,7 +559,7 @@ void launch_fwd(const Call& call, T* O, const T* A, const T* C, const int32_t* P
             O, A, plan.fwd_rec, I, N, static_cast<int>(J));
     }
     MOPS_CUDA_OK(cudaGetLastError());
-    scratch_free(call, scratch);
+    release_table(call, scratch);
 }
 
 template <typename T, int K>
@@ -572,7 +580,7 @@ void launch_vjp(const Call& call, T* gA, const T* gO, const T* A, const T* C, co
         }
     }
     const size_t smem = vjp_smem<T, K>(N, rpl);
-    void* scratch = nullptr;
+    TableRef scratch{};
     HpePlan plan = make_plan<T>(call, &scratch, C, P, J, K, N, false, true, 32 * rpl + 1);
     auto launch = [&](auto kernel) {
         if (smem > 48 * 1024)
@@ -589,7 +597,7 @@ void launch_vjp(const Call& call, T* gA, const T* gO, const T* A, const T* C, co
     else
         launch(hpe_vjp_rows<T, K, 1>);
     MOPS_CUDA_OK(cudaGetLastError());
-    scratch_free(call, scratch);
+    release_table(call, scratch);
 }
 
 #define MOPS_B200_ORDER_SWITCH(K, CALL)                                                            \
@@ -794,6 +802,9 @@ void mops::cuda::homogeneous_polynomial_evaluation_vjp_vjp(
     const size_t b_c2 = up(static_cast<size_t>(J2) * sizeof(scalar_t));
     const size_t b_p2 = up(static_cast<size_t>(J2) * K * sizeof(int32_t));
     const size_t b_g2 = grad_A_2.data != nullptr ? b_a2 : 0;
+    // The augmented coefficient and index arrays below are temporaries whose addresses repeat
+    // from call to call: tables derived from them must not be kept by a plan.
+    PlanSuspended no_plan;
     unsigned char* base = static_cast<unsigned char*>(scratch_alloc(call, b_a2 + b_c2 + b_p2 + b_g2));
     scalar_t* A2 = reinterpret_cast<scalar_t*>(base);
     scalar_t* C2 = reinterpret_cast<scalar_t*>(base + b_a2);

@@ -636,12 +636,8 @@ void forward(const Call& call, T* O, const T* A, const T* B, const T* W, const i
 
     if (segmented) {
         // Segment table: call-scoped scratch, (nO + 1) offsets.
-        int64_t* offsets =
-            static_cast<int64_t*>(scratch_alloc(call, (nO + 1) * sizeof(int64_t)));
-        const int64_t pre_blocks = std::min<int64_t>(ceil_div(J + 1, 256), grid_generic * 4);
-        segment_offsets<<<static_cast<unsigned>(pre_blocks), 256, 0, call.stream>>>(
-            P, J, nO, offsets, call.status);
-        MOPS_CUDA_OK(cudaGetLastError());
+        SegmentTable seg = segment_table(call, P, J, nO);
+        const int64_t* offsets = seg.offsets;
         constexpr int widest = 16 / static_cast<int>(sizeof(T));
         bool on_tensor_cores = forward_pipe<T, WEIGHTED>(call, O, A, B, W, PW, offsets, J, K, L, nO);
         if constexpr (sizeof(T) == 8 && WEIGHTED) {
@@ -669,9 +665,9 @@ void forward(const Call& call, T* O, const T* A, const T* B, const T* W, const i
             dispatch_nv<T, 1, WEIGHTED>(plan.NV, plan.TK, call, plan, O, A, B, W, PW, offsets, K,
                                         L, nO);
         MOPS_CUDA_OK(cudaGetLastError());
-        scratch_free(call, offsets);
-        bool need_fallback = true; // asynchronous calls cannot look: always enqueue
-        if (call.wait) {
+        release_table(call, seg.ref);
+        bool need_fallback = !seg.known_sorted; // asynchronous calls cannot look: always enqueue
+        if (need_fallback && call.wait) {
             wait_stream(call);
             need_fallback = host_saw_unsorted(call);
         }
@@ -1183,10 +1179,8 @@ void backward(const Call& call, T* gA, T* gB, T* gW, const T* gO, const T* A, co
     const bool streaming = pipe_usable<T, WEIGHTED>(A, B, W, gO, K, L, true);
     if (K <= 16 && L <= 32 && (streaming || sizeof(T) == 8)) {
         const int sms = sm_count(call.device);
-        int64_t* offsets = static_cast<int64_t*>(scratch_alloc(call, (nO + 1) * sizeof(int64_t)));
-        const int64_t pre_blocks = std::min<int64_t>(ceil_div(J + 1, 256), sms * 32);
-        segment_offsets<<<static_cast<unsigned>(pre_blocks), 256, 0, call.stream>>>(
-            P, J, nO, offsets, call.status);
+        SegmentTable seg = segment_table(call, P, J, nO);
+        const int64_t* offsets = seg.offsets;
         bool launched = streaming && backward_pipe<T, WEIGHTED>(call, gA, gB, gW, gO, A, B, W, PW,
                                                                 offsets, J, K, L, nO);
         if constexpr (sizeof(T) == 8) {
@@ -1201,8 +1195,9 @@ void backward(const Call& call, T* gA, T* gB, T* gW, const T* gO, const T* A, co
             }
         }
         MOPS_CUDA_OK(cudaGetLastError());
-        scratch_free(call, offsets);
+        release_table(call, seg.ref);
         if (launched) {
+            if (seg.known_sorted) return;
             if (call.wait) {
                 wait_stream(call);
                 if (!host_saw_unsorted(call)) return;

@@ -113,11 +113,11 @@ struct PipeWarp {
 __device__ __forceinline__ PipeWarp pipe_partition(const int64_t* __restrict__ offsets, int64_t nO,
                                                    int ch, int warp) {
     PipeWarp w;
+    const int lane = threadIdx.x & 31;
     const int64_t total = static_cast<int64_t>(gridDim.x) * kPipeWarps;
     const int64_t gwarp = static_cast<int64_t>(blockIdx.x) * kPipeWarps + warp;
-    const int64_t per = (nO + total - 1) / total;
-    w.r0 = gwarp * per < nO ? gwarp * per : nO;
-    w.r1 = w.r0 + per < nO ? w.r0 + per : nO;
+    w.r0 = balanced_row_split(offsets, nO, gwarp, total, lane);
+    w.r1 = balanced_row_split(offsets, nO, gwarp + 1, total, lane);
     w.e_begin = offsets[w.r0];
     w.e_last = offsets[w.r1];
     w.e_first = w.e_begin & ~static_cast<int64_t>(3);

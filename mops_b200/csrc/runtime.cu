@@ -1,5 +1,7 @@
 #include <cstdarg>
 #include <cstdio>
+#include <cstring>
+#include <vector>
 #include <map>
 #include <mutex>
 #include <unordered_map>
@@ -163,6 +165,120 @@ cudaMemPool_t scratch_pool(int device) {
     return it->second;
 }
 } // namespace
+
+// ---- plans
+class TablePlan {
+  public:
+    struct Entry {
+        TableKey key;
+        int device;
+        void* ptr;
+        size_t bytes;
+        bool ready;  // built and committed
+        bool usable; // false: the index was unsorted or held bad values (rebuild per call)
+    };
+    std::mutex mutex;
+    std::vector<Entry> entries;
+};
+
+namespace {
+thread_local TablePlan* g_bound_plan = nullptr;
+bool same_key(const TableKey& a, const TableKey& b) { return std::memcmp(&a, &b, sizeof(TableKey)) == 0; }
+} // namespace
+
+TablePlan* plan_create() { return new TablePlan(); }
+
+void plan_destroy(TablePlan* plan) {
+    if (plan == nullptr) return;
+    if (g_bound_plan == plan) g_bound_plan = nullptr;
+    for (auto& e : plan->entries) {
+        if (e.ptr != nullptr) {
+            int previous = 0;
+            if (cudaGetDevice(&previous) == cudaSuccess && cudaSetDevice(e.device) == cudaSuccess) {
+                (void)cudaFree(e.ptr);
+                (void)cudaSetDevice(previous);
+            }
+        }
+    }
+    delete plan;
+}
+
+void plan_bind(TablePlan* plan) { g_bound_plan = plan; }
+TablePlan* plan_bound() { return g_bound_plan; }
+
+int plan_table_count(const TablePlan* plan) {
+    if (plan == nullptr) return 0;
+    std::lock_guard<std::mutex> lock(const_cast<TablePlan*>(plan)->mutex);
+    int n = 0;
+    for (const auto& e : plan->entries) n += e.ready && e.usable ? 1 : 0;
+    return n;
+}
+
+TableRef acquire_table(const Call& call, const TableKey& key_in, size_t bytes) {
+    TableRef ref{nullptr, true, false, false, -1};
+    TablePlan* plan = g_bound_plan;
+    if (plan != nullptr) {
+        TableKey key;
+        std::memset(&key, 0, sizeof(key)); // padding bytes take part in the comparison
+        key.kind = key_in.kind;
+        key.scalar_bytes = key_in.scalar_bytes;
+        for (int i = 0; i < 5; i++) key.ptr[i] = key_in.ptr[i];
+        for (int i = 0; i < 10; i++) key.n[i] = key_in.n[i];
+        std::lock_guard<std::mutex> lock(plan->mutex);
+        for (size_t i = 0; i < plan->entries.size(); i++) {
+            TablePlan::Entry& e = plan->entries[i];
+            if (e.device != call.device || !same_key(e.key, key)) continue;
+            if (e.ready && e.usable) {
+                ref.ptr = e.ptr;
+                ref.fresh = false;
+                ref.owned_by_plan = true;
+                ref.sorted = true;
+                ref.slot = static_cast<int>(i);
+                return ref;
+            }
+            // known to be unusable (or being built by another thread): per-call scratch
+            ref.ptr = scratch_alloc(call, bytes);
+            return ref;
+        }
+        TablePlan::Entry e{};
+        e.key = key;
+        e.device = call.device;
+        e.bytes = bytes;
+        e.ready = false;
+        e.usable = false;
+        // plain cudaMalloc: the table outlives the call and is used from any stream
+        MOPS_CUDA_OK(cudaMalloc(&e.ptr, bytes > 0 ? bytes : 1));
+        plan->entries.push_back(e);
+        ref.ptr = e.ptr;
+        ref.owned_by_plan = true;
+        ref.slot = static_cast<int>(plan->entries.size() - 1);
+        return ref;
+    }
+    ref.ptr = scratch_alloc(call, bytes);
+    return ref;
+}
+
+void commit_table(const Call& call, TableRef& ref) {
+    if (!ref.owned_by_plan || !ref.fresh) return;
+    TablePlan* plan = g_bound_plan;
+    // The table must be complete before another stream may use it, and what its builder
+    // reported decides whether it can be kept.
+    MOPS_CUDA_OK(cudaStreamSynchronize(call.stream));
+    volatile uint32_t* host = call.status.host;
+    bool clean = true;
+    for (int w = 0; w < kStatusWords; w++) clean = clean && host[w] != call.status.epoch;
+    ref.sorted = clean;
+    if (plan == nullptr) return;
+    std::lock_guard<std::mutex> lock(plan->mutex);
+    if (ref.slot >= 0 && ref.slot < static_cast<int>(plan->entries.size())) {
+        plan->entries[ref.slot].ready = true;
+        plan->entries[ref.slot].usable = clean;
+    }
+}
+
+void release_table(const Call& call, const TableRef& ref) {
+    if (!ref.owned_by_plan) scratch_free(call, ref.ptr);
+}
 
 void* scratch_alloc(const Call& call, size_t bytes) {
     void* ptr = nullptr;

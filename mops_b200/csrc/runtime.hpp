@@ -89,6 +89,65 @@ bool get_wait();
 void* scratch_alloc(const Call& call, size_t bytes);
 void scratch_free(const Call& call, void* ptr);
 
+// ---- reusable device tables ("plans")
+// Every operation first turns its index (and coefficient) arrays into a device table: the
+// segment offsets of a scatter index, HPE's packed monomial records, SAP's sorted triplets,
+// SASAW's grouped coupling table. Without a plan these tables are call-scoped scratch and are
+// rebuilt by every call (as the reference rebuilds its first-occurrence table,
+// mops/src/internal/cuda_first_occurences.cu:82-117). With a plan bound to the calling thread
+// a table is built by the first call that needs it and kept: later calls with the same arrays
+// (same addresses and sizes: the caller promises not to change their contents) reuse it, so the
+// forward and the VJP of one graph share one segment table, nothing is rebuilt, and a scatter
+// call knows without asking the device that its index is sorted.
+enum TableKind : int {
+    kSegmentTable = 1,
+    kSasawCouplingTable = 2,
+    kHpeTable = 3,
+    kSapTable = 4,
+    kSapSmallTable = 5
+};
+
+struct TableKey {
+    int kind;
+    int scalar_bytes;
+    const void* ptr[5]; // the arrays the table is derived from
+    int64_t n[10];      // their sizes and the layout parameters of the table
+};
+
+struct TableRef {
+    void* ptr;          // device memory of `bytes` bytes
+    bool fresh;         // the caller must fill it (launch the builder), then commit_table()
+    bool owned_by_plan; // kept by the bound plan (else call-scoped scratch: release_table frees)
+    bool sorted;        // segment tables from a plan: the index is known to be sorted
+    int slot;           // position in the plan
+};
+
+class TablePlan;
+TablePlan* plan_create();
+void plan_destroy(TablePlan* plan);
+void plan_bind(TablePlan* plan); // nullptr unbinds; per thread
+TablePlan* plan_bound();
+int plan_table_count(const TablePlan* plan);
+
+// Unbinds the calling thread's plan for the lifetime of the object (for internal calls whose
+// index arrays are temporaries).
+struct PlanSuspended {
+    TablePlan* saved;
+    PlanSuspended() : saved(plan_bound()) { plan_bind(nullptr); }
+    ~PlanSuspended() { plan_bind(saved); }
+    PlanSuspended(const PlanSuspended&) = delete;
+    PlanSuspended& operator=(const PlanSuspended&) = delete;
+};
+
+// Looks `key` up in the bound plan; without a plan (or when the plan knows that this index is
+// not sorted or held bad values) returns call-scoped scratch that the caller fills as before.
+TableRef acquire_table(const Call& call, const TableKey& key, size_t bytes);
+// To be called once the builder of a fresh table is enqueued. For a plan-owned table this
+// waits for the stream (once per table) and records whether the builder found the scatter
+// index sorted; a table whose builder reported bad indices is not kept.
+void commit_table(const Call& call, TableRef& ref);
+void release_table(const Call& call, const TableRef& ref);
+
 int sm_count(int device);
 int max_optin_smem(int device);
 

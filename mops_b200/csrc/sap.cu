@@ -485,7 +485,7 @@ template <typename Kernel> void allow_smem(Kernel kernel, size_t smem) {
 
 // Allocates the call-scoped plan tables and runs the plan kernel.
 template <typename T>
-Plan<T> make_plan(const Call& call, void** scratch, const T* C, const int32_t* PA,
+Plan<T> make_plan(const Call& call, TableRef* scratch, const T* C, const int32_t* PA,
                   const int32_t* PB, const int32_t* PO, int64_t K, int nA, int nB, int nO,
                   int stride, bool want_runs, bool want_groups) {
     const size_t table = up16(static_cast<size_t>(K) * sizeof(Entry<T>));
@@ -495,8 +495,14 @@ Plan<T> make_plan(const Call& call, void** scratch, const T* C, const int32_t* P
     const size_t ints_b = up16((static_cast<size_t>(nB) + 1) * sizeof(int32_t));
     const size_t total = 3 * table + 2 * ints_k + 2 * ints_o + 2 * ints_a + 2 * ints_b + 16 +
                          std::max(ints_a, ints_b);
-    unsigned char* p = static_cast<unsigned char*>(scratch_alloc(call, total));
-    *scratch = p;
+    TableKey key{};
+    key.kind = kSapTable;
+    key.scalar_bytes = static_cast<int>(sizeof(T));
+    key.ptr[0] = C, key.ptr[1] = PA, key.ptr[2] = PB, key.ptr[3] = PO;
+    key.n[0] = K, key.n[1] = nA, key.n[2] = nB, key.n[3] = nO, key.n[4] = stride;
+    key.n[5] = want_runs ? 1 : 0, key.n[6] = want_groups ? 1 : 0;
+    *scratch = acquire_table(call, key, total);
+    unsigned char* p = static_cast<unsigned char*>(scratch->ptr);
     Plan<T> plan;
     auto take = [&](size_t bytes) {
         unsigned char* q = p;
@@ -514,10 +520,13 @@ Plan<T> make_plan(const Call& call, void** scratch, const T* C, const int32_t* P
     plan.b_start = reinterpret_cast<int32_t*>(take(ints_b));
     plan.counts = reinterpret_cast<int32_t*>(take(16));
     plan.cursor = reinterpret_cast<int32_t*>(take(std::max(ints_a, ints_b)));
-    sap_plan<T><<<1, kPlanThreads, 0, call.stream>>>(plan, C, PA, PB, PO, static_cast<int>(K), nA,
-                                                     nB, nO, stride, want_runs, want_groups,
-                                                     call.status);
-    MOPS_CUDA_OK(cudaGetLastError());
+    if (scratch->fresh) {
+        sap_plan<T><<<1, kPlanThreads, 0, call.stream>>>(plan, C, PA, PB, PO, static_cast<int>(K),
+                                                         nA, nB, nO, stride, want_runs,
+                                                         want_groups, call.status);
+        MOPS_CUDA_OK(cudaGetLastError());
+        commit_table(call, *scratch);
+    }
     return plan;
 }
 
@@ -767,22 +776,31 @@ int rows_small(const Call& call, const void* kernel, int cols, int64_t K, int nb
 }
 
 template <typename T>
-SmallPlan<T> make_small_plan(const Call& call, void** scratch, const T* C, const int32_t* PS,
+SmallPlan<T> make_small_plan(const Call& call, TableRef* scratch, const T* C, const int32_t* PS,
                              const int32_t* PT, const int32_t* PO, int64_t K, int nS, int nT,
                              int nO, int NS, int stride, int mode, int bit_s, int bit_t) {
     const size_t nbins = static_cast<size_t>(mode == 0 ? nO : nT) * NS;
     const size_t table = up16(static_cast<size_t>(K + kSmallPad) * sizeof(Entry<T>));
     const size_t ints = up16((nbins + 1) * sizeof(int32_t));
-    unsigned char* p = static_cast<unsigned char*>(scratch_alloc(call, table + 2 * ints));
-    *scratch = p;
+    TableKey key{};
+    key.kind = kSapSmallTable;
+    key.scalar_bytes = static_cast<int>(sizeof(T));
+    key.ptr[0] = C, key.ptr[1] = PS, key.ptr[2] = PT, key.ptr[3] = PO;
+    key.n[0] = K, key.n[1] = nS, key.n[2] = nT, key.n[3] = nO, key.n[4] = NS, key.n[5] = stride;
+    key.n[6] = mode, key.n[7] = bit_s, key.n[8] = bit_t;
+    *scratch = acquire_table(call, key, table + 2 * ints);
+    unsigned char* p = static_cast<unsigned char*>(scratch->ptr);
     SmallPlan<T> plan;
     plan.table = reinterpret_cast<Entry<T>*>(p);
     plan.start = reinterpret_cast<int32_t*>(p + table);
     plan.cursor = reinterpret_cast<int32_t*>(p + table + ints);
-    sap_plan_small<T><<<1, kPlanThreads, 0, call.stream>>>(plan, C, PS, PT, PO,
-                                                           static_cast<int>(K), nS, nT, nO, NS,
-                                                           stride, mode, bit_s, bit_t, call.status);
-    MOPS_CUDA_OK(cudaGetLastError());
+    if (scratch->fresh) {
+        sap_plan_small<T><<<1, kPlanThreads, 0, call.stream>>>(
+            plan, C, PS, PT, PO, static_cast<int>(K), nS, nT, nO, NS, stride, mode, bit_s, bit_t,
+            call.status);
+        MOPS_CUDA_OK(cudaGetLastError());
+        commit_table(call, *scratch);
+    }
     return plan;
 }
 
@@ -803,7 +821,7 @@ bool forward_small(const Call& call, T* O, const T* A, const T* B, const T* C, c
                                    : reinterpret_cast<const void*>(sap_fwd_small<T, 16>);
     const int R = rows_small<T>(call, kernel, nT, K, nO * NS, &smem);
     if (R == 0) return false;
-    void* scratch = nullptr;
+    TableRef scratch{};
     SmallPlan<T> plan = make_small_plan<T>(call, &scratch, C, PS, PT, PO, K, nS, nT, nO, NS, R + 1,
                                            0, b_small ? 1 : 0, b_small ? 0 : 1);
     const unsigned blocks = static_cast<unsigned>(ceil_div(I, R));
@@ -817,7 +835,7 @@ bool forward_small(const Call& call, T* O, const T* A, const T* B, const T* C, c
     if (NS == 4) MOPS_B200_LAUNCH(4) else if (NS == 8) MOPS_B200_LAUNCH(8) else MOPS_B200_LAUNCH(16)
 #undef MOPS_B200_LAUNCH
     MOPS_CUDA_OK(cudaGetLastError());
-    scratch_free(call, scratch);
+    release_table(call, scratch);
     return true;
 }
 
@@ -839,7 +857,7 @@ bool backward_small(const Call& call, T* gA, T* gB, const T* gO, const T* A, con
                                    : reinterpret_cast<const void*>(sap_vjp_small<T, 16>);
     const int R = rows_small<T>(call, kernel, nO, K, nT * NS, &smem);
     if (R == 0) return false;
-    void* scratch = nullptr;
+    TableRef scratch{};
     SmallPlan<T> plan = make_small_plan<T>(call, &scratch, C, PS, PT, PO, K, nS, nT, nO, NS, R + 1,
                                            1, b_small ? 1 : 0, b_small ? 0 : 1);
     const unsigned blocks = static_cast<unsigned>(ceil_div(I, R));
@@ -853,7 +871,7 @@ bool backward_small(const Call& call, T* gA, T* gB, const T* gO, const T* A, con
     if (NS == 4) MOPS_B200_LAUNCH(4) else if (NS == 8) MOPS_B200_LAUNCH(8) else MOPS_B200_LAUNCH(16)
 #undef MOPS_B200_LAUNCH
     MOPS_CUDA_OK(cudaGetLastError());
-    scratch_free(call, scratch);
+    release_table(call, scratch);
     return true;
 }
 
@@ -911,7 +929,7 @@ void mops::cuda::sparse_accumulation_of_products(Tensor<scalar_t, 2> output, Ten
     bool in_smem = false;
     const int R = rows_per_block<scalar_t>(call, nA + nB, 1, K, &smem, &in_smem);
     if (R > 0) {
-        void* scratch = nullptr;
+        TableRef scratch{};
         Plan<scalar_t> plan = make_plan<scalar_t>(call, &scratch, C.data, indices_A.data,
                                                   indices_B.data, indices_output.data, K, nA, nB,
                                                   nO, R + 1, true, false);
@@ -921,7 +939,7 @@ void mops::cuda::sparse_accumulation_of_products(Tensor<scalar_t, 2> output, Ten
         kernel<<<static_cast<unsigned>(ceil_div(I, R)), R, smem, call.stream>>>(
             output.data, A.data, B.data, plan, I, nA, nB, nO, static_cast<int>(K));
         MOPS_CUDA_OK(cudaGetLastError());
-        scratch_free(call, scratch);
+        release_table(call, scratch);
     } else {
         sap_wide<scalar_t><<<static_cast<unsigned>(ceil_div(I, 128)), 128, 0, call.stream>>>(
             0, output.data, nullptr, nullptr, nullptr, nullptr, nullptr, A.data, B.data, C.data,
@@ -967,7 +985,7 @@ void mops::cuda::sparse_accumulation_of_products_vjp(
     bool in_smem = false;
     const int R = rows_per_block<scalar_t>(call, nA + nB + nO, 2, K, &smem, &in_smem);
     if (R > 0) {
-        void* scratch = nullptr;
+        TableRef scratch{};
         Plan<scalar_t> plan = make_plan<scalar_t>(call, &scratch, C.data, indices_A.data,
                                                   indices_B.data, indices_output.data, K, nA, nB,
                                                   nO, R + 1, false, true);
@@ -977,7 +995,7 @@ void mops::cuda::sparse_accumulation_of_products_vjp(
             grad_A.data, grad_B.data, grad_output.data, A.data, B.data, plan, I, nA, nB, nO,
             static_cast<int>(K));
         MOPS_CUDA_OK(cudaGetLastError());
-        scratch_free(call, scratch);
+        release_table(call, scratch);
     } else {
         sap_wide<scalar_t><<<static_cast<unsigned>(ceil_div(I, 128)), 128, 0, call.stream>>>(
             1, grad_A.data, grad_B.data, nullptr, nullptr, nullptr, grad_output.data, A.data,
@@ -1026,7 +1044,7 @@ void mops::cuda::sparse_accumulation_of_products_vjp_vjp(
     bool in_smem = false;
     const int R = rows_per_block<scalar_t>(call, 2 * nA + 2 * nB + nO, 3, K, &smem, &in_smem);
     if (R > 0) {
-        void* scratch = nullptr;
+        TableRef scratch{};
         Plan<scalar_t> plan = make_plan<scalar_t>(call, &scratch, C.data, indices_A.data,
                                                   indices_B.data, indices_output.data, K, nA, nB,
                                                   nO, R + 1, true, true);
@@ -1038,7 +1056,7 @@ void mops::cuda::sparse_accumulation_of_products_vjp_vjp(
             grad_grad_B.data, grad_output.data, A.data, B.data, plan, I, nA, nB, nO,
             static_cast<int>(K));
         MOPS_CUDA_OK(cudaGetLastError());
-        scratch_free(call, scratch);
+        release_table(call, scratch);
     } else {
         sap_wide<scalar_t><<<static_cast<unsigned>(ceil_div(I, 128)), 128, 0, call.stream>>>(
             2, grad_grad_output.data, grad_A_2.data, grad_B_2.data, grad_grad_A.data,

@@ -1348,9 +1348,8 @@ sasaw_fwd_quad(double* __restrict__ O, const double* __restrict__ A, const doubl
 
     const int64_t total_warps = static_cast<int64_t>(gridDim.x) * warps;
     const int64_t gwarp = static_cast<int64_t>(blockIdx.x) * warps + warp;
-    const int64_t per = (nW0 + total_warps - 1) / total_warps;
-    const int64_t r0 = gwarp * per < nW0 ? gwarp * per : nW0;
-    const int64_t r1 = r0 + per < nW0 ? r0 + per : nW0;
+    const int64_t r0 = balanced_row_split(offsets, nW0, gwarp, total_warps, lane);
+    const int64_t r1 = balanced_row_split(offsets, nW0, gwarp + 1, total_warps, lane);
     if (r0 >= r1) return;
     const int nrows = static_cast<int>(r1 - r0);
     // this warp's edges, operands and output, rebased to its first edge / row
@@ -1645,9 +1644,8 @@ sasaw_vjp_quad(double* __restrict__ gA, double* __restrict__ gB, double* __restr
 
     const int64_t total_warps = static_cast<int64_t>(gridDim.x) * warps;
     const int64_t gwarp = static_cast<int64_t>(blockIdx.x) * warps + warp;
-    const int64_t per = (nW0 + total_warps - 1) / total_warps;
-    const int64_t r0 = gwarp * per < nW0 ? gwarp * per : nW0;
-    const int64_t r1 = r0 + per < nW0 ? r0 + per : nW0;
+    const int64_t r0 = balanced_row_split(offsets, nW0, gwarp, total_warps, lane);
+    const int64_t r1 = balanced_row_split(offsets, nW0, gwarp + 1, total_warps, lane);
     if (r0 >= r1) return;
     const int nrows = static_cast<int>(r1 - r0);
     const int64_t e_base = offsets[r0];
@@ -2060,7 +2058,7 @@ template <typename T> struct Problem {
 // Allocates and fills the grouped coupling table; returns false when the grouped kernels
 // cannot be used (cell grid too large for one block's shared memory).
 template <typename T>
-bool build_coupling(const Call& call, const Problem<T>& p, Coupling<T>& cp, void** scratch,
+bool build_coupling(const Call& call, const Problem<T>& p, Coupling<T>& cp, TableRef* table,
                     int cell_stride = 0, int d_stride = 0, bool d_padded = false) {
     if (cell_stride == 0) cell_stride = p.nW1;
     const int64_t ncell64 = static_cast<int64_t>(p.nO1) * cell_stride;
@@ -2073,8 +2071,14 @@ bool build_coupling(const Call& call, const Problem<T>& p, Coupling<T>& cp, void
     const size_t nD =
         static_cast<size_t>(d_stride) * p.nO1 * (d_padded ? cell_stride : p.nW1) * sizeof(T);
     const size_t bytes = nT + 3 * nI + nStart + 16 + nD;
-    unsigned char* base = static_cast<unsigned char*>(scratch_alloc(call, bytes));
-    *scratch = base;
+    TableKey key{};
+    key.kind = kSasawCouplingTable;
+    key.scalar_bytes = static_cast<int>(sizeof(T));
+    key.ptr[0] = p.C, key.ptr[1] = p.M1, key.ptr[2] = p.M2, key.ptr[3] = p.M3;
+    key.n[0] = p.N, key.n[1] = p.nA, key.n[2] = p.nW1, key.n[3] = p.nO1;
+    key.n[4] = cell_stride, key.n[5] = d_stride, key.n[6] = d_padded ? 1 : 0;
+    *table = acquire_table(call, key, bytes);
+    unsigned char* base = static_cast<unsigned char*>(table->ptr);
     cp.d_stride = d_stride;
     cp.d_padded = d_padded;
     cp.D = d_stride > 0
@@ -2085,9 +2089,12 @@ bool build_coupling(const Call& call, const Problem<T>& p, Coupling<T>& cp, void
     cp.cell = cp.M1 + p.N;
     cp.order = cp.cell + p.N;
     cp.start = cp.order + p.N;
-    sasaw_group_coupling<T><<<1, kBuildThreads, cp.ncell * sizeof(int32_t), call.stream>>>(
-        cp, p.C, p.M1, p.M2, p.M3, p.nA, p.nW1, p.nO1, call.status);
-    MOPS_CUDA_OK(cudaGetLastError());
+    if (table->fresh) {
+        sasaw_group_coupling<T><<<1, kBuildThreads, cp.ncell * sizeof(int32_t), call.stream>>>(
+            cp, p.C, p.M1, p.M2, p.M3, p.nA, p.nW1, p.nO1, call.status);
+        MOPS_CUDA_OK(cudaGetLastError());
+        commit_table(call, *table);
+    }
     return true;
 }
 
@@ -2148,12 +2155,10 @@ bool forward_fast(const Call& call, T* O, const Problem<T>& p) {
     const int warps_edge = pick_warps_fast<T>(call, ncc, ds, tsize, &smem_edge);
     if (warps_seg == 0 || warps_edge == 0) return false;
     Coupling<T> cp{};
-    void* scratch = nullptr;
+    TableRef scratch{};
     if (!build_coupling(call, p, cp, &scratch, TP, ds)) return false;
-    int64_t* offsets = static_cast<int64_t*>(scratch_alloc(call, (p.nW0 + 1) * sizeof(int64_t)));
-    const int64_t pre_blocks = std::min<int64_t>(ceil_div(p.E + 1, 256), grid_generic * 4);
-    segment_offsets<<<static_cast<unsigned>(pre_blocks), 256, 0, call.stream>>>(
-        p.Io, p.E, p.nW0, offsets, call.status);
+    SegmentTable seg = segment_table(call, p.Io, p.E, p.nW0);
+    const int64_t* offsets = seg.offsets;
     allow_smem(sasaw_fwd_fast<T, TP, NAP, true>, smem_seg);
     note_kernel_f("sasaw_fwd_fast<%s,TP=%d,NAP=%d>", scalar_name<T>(), TP, NAP);
     sasaw_fwd_fast<T, TP, NAP, true><<<static_cast<unsigned>(ceil_div(p.nW0, warps_seg)),
@@ -2161,9 +2166,9 @@ bool forward_fast(const Call& call, T* O, const Problem<T>& p) {
         O, p.A, p.B, p.W, p.Jw, p.Io, offsets, cp, p.E, p.nA, p.L, p.nW0, p.nW1, p.nO1, false,
         call.status);
     MOPS_CUDA_OK(cudaGetLastError());
-    scratch_free(call, offsets);
-    bool need_fallback = true; // asynchronous calls cannot look: always enqueue
-    if (call.wait) {
+    release_table(call, seg.ref);
+    bool need_fallback = !seg.known_sorted; // asynchronous calls cannot look: always enqueue
+    if (need_fallback && call.wait) {
         wait_stream(call);
         need_fallback = host_saw_unsorted(call);
     }
@@ -2177,7 +2182,7 @@ bool forward_fast(const Call& call, T* O, const Problem<T>& p) {
             call.status);
     }
     MOPS_CUDA_OK(cudaGetLastError());
-    scratch_free(call, scratch);
+    release_table(call, scratch);
     return true;
 }
 
@@ -2190,7 +2195,7 @@ bool backward_fast(const Call& call, T* gA, T* gB, T* gW, const T* gO, const Pro
         pick_warps_fast<T>(call, ncc, ds, 2 * round4(static_cast<size_t>(p.nO1) * TP), &smem);
     if (warps == 0) return false;
     Coupling<T> cp{};
-    void* scratch = nullptr;
+    TableRef scratch{};
     if (!build_coupling(call, p, cp, &scratch, TP, ds)) return false;
     allow_smem(sasaw_vjp_fast<T, TP, NAP>, smem);
     note_kernel_f("sasaw_vjp_fast<%s,TP=%d,NAP=%d>", scalar_name<T>(), TP, NAP);
@@ -2200,7 +2205,7 @@ bool backward_fast(const Call& call, T* gA, T* gB, T* gW, const T* gO, const Pro
         gA, gB, gW, gO, p.A, p.B, p.W, p.Jw, p.Io, cp, p.E, p.nA, p.L, p.nW0, p.nW1, p.nO1,
         call.status);
     MOPS_CUDA_OK(cudaGetLastError());
-    scratch_free(call, scratch);
+    release_table(call, scratch);
     return true;
 }
 
@@ -2217,17 +2222,16 @@ bool forward_mma_launch(const Call& call, T* O, const Problem<T>& p, bool segmen
     const int64_t rowsize = static_cast<int64_t>(p.nO1) * p.L;
     const int sms = sm_count(call.device);
     Coupling<T> cp{};
-    void* scratch = nullptr;
+    TableRef scratch{};
     if (!build_coupling(call, p, cp, &scratch, Lay::TS, Lay::d_stride(p.nA), true)) return false;
     const bool wide_copies = p.L % 2 == 0 && reinterpret_cast<uintptr_t>(p.W) % 16 == 0 &&
                              reinterpret_cast<uintptr_t>(p.B) % 16 == 0 &&
                              reinterpret_cast<uintptr_t>(O) % 16 == 0;
+    bool known_sorted = false;
     if (!segmented_done) {
-        int64_t* offsets =
-            static_cast<int64_t*>(scratch_alloc(call, (p.nW0 + 1) * sizeof(int64_t)));
-        const int64_t pre_blocks = std::min<int64_t>(ceil_div(p.E + 1, 256), sms * 32);
-        segment_offsets<<<static_cast<unsigned>(pre_blocks), 256, 0, call.stream>>>(
-            p.Io, p.E, p.nW0, offsets, call.status);
+        SegmentTable seg = segment_table(call, p.Io, p.E, p.nW0);
+        const int64_t* offsets = seg.offsets;
+        known_sorted = seg.known_sorted;
         allow_smem(sasaw_fwd_mma<TP, true>, smem);
         note_kernel_f("sasaw_fwd_mma<TP=%d,SEG=1>", TP);
         const int64_t seg_blocks = std::min<int64_t>(ceil_div(p.nW0, warps), sms * 3);
@@ -2236,10 +2240,10 @@ bool forward_mma_launch(const Call& call, T* O, const Problem<T>& p, bool segmen
                                                  p.nA, p.L, p.nW0, p.nW1, p.nO1, wide_copies,
                                                  call.status);
         MOPS_CUDA_OK(cudaGetLastError());
-        scratch_free(call, offsets);
+        release_table(call, seg.ref);
     }
-    bool need_fallback = true; // asynchronous calls cannot look: always enqueue
-    if (call.wait && !segmented_done) {
+    bool need_fallback = !known_sorted; // asynchronous calls cannot look: always enqueue
+    if (need_fallback && call.wait && !segmented_done) {
         wait_stream(call);
         need_fallback = host_saw_unsorted(call);
     }
@@ -2252,7 +2256,7 @@ bool forward_mma_launch(const Call& call, T* O, const Problem<T>& p, bool segmen
             wide_copies, call.status);
     }
     MOPS_CUDA_OK(cudaGetLastError());
-    scratch_free(call, scratch);
+    release_table(call, scratch);
     return true;
 }
 
@@ -2282,13 +2286,10 @@ template <typename T> int forward_quad(const Call& call, T* O, const Problem<T>&
         const size_t smem = d_bytes + warps * warp_bytes;
         const int sms = sm_count(call.device);
         Coupling<T> cp{};
-        void* scratch = nullptr;
+        TableRef scratch{};
         if (!build_coupling(call, p, cp, &scratch, p.nW1, q.DS, false)) return 0;
-        int64_t* offsets =
-            static_cast<int64_t*>(scratch_alloc(call, (p.nW0 + 1) * sizeof(int64_t)));
-        const int64_t pre_blocks = std::min<int64_t>(ceil_div(p.E + 1, 256), sms * 32);
-        segment_offsets<<<static_cast<unsigned>(pre_blocks), 256, 0, call.stream>>>(
-            p.Io, p.E, p.nW0, offsets, call.status);
+        SegmentTable seg = segment_table(call, p.Io, p.E, p.nW0);
+    const int64_t* offsets = seg.offsets;
         const int mode = p.nO1 <= 8 ? 0 : (p.nO1 == 9 ? 1 : 2);
         const unsigned blocks = static_cast<unsigned>(std::min<int64_t>(ceil_div(p.nW0, warps), sms));
         const bool fixed = p.nA == p.nW1 && p.nA == p.nO1 && (p.nA == 4 || p.nA == 9 || p.nA == 16);
@@ -2308,8 +2309,9 @@ template <typename T> int forward_quad(const Call& call, T* O, const Problem<T>&
         else MOPS_B200_CASE(2, 0, 0, 0)
 #undef MOPS_B200_CASE
         MOPS_CUDA_OK(cudaGetLastError());
-        scratch_free(call, offsets);
-        scratch_free(call, scratch);
+        release_table(call, seg.ref);
+        release_table(call, scratch);
+        if (seg.known_sorted) return 1;
         if (call.wait) {
             wait_stream(call);
             if (!host_saw_unsorted(call)) return 1;
@@ -2345,7 +2347,7 @@ bool backward_mma_launch(const Call& call, T* gA, T* gB, T* gW, const T* gO, con
         (Lay::d_scalars(p.nO1, p.nA) + Lay::per_warp(p.nO1, p.nW1) * warps) * sizeof(T);
     if (smem > 74 * 1024) return false; // three blocks per SM
     Coupling<T> cp{};
-    void* scratch = nullptr;
+    TableRef scratch{};
     if (!build_coupling(call, p, cp, &scratch, Lay::TS, Lay::d_stride(p.nA), true)) return false;
     allow_smem(sasaw_vjp_mma<TP, KS3>, smem);
     if (!only_if_unsorted) note_kernel_f("sasaw_vjp_mma<TP=%d,KS3=%d>", TP, KS3);
@@ -2357,7 +2359,7 @@ bool backward_mma_launch(const Call& call, T* gA, T* gB, T* gW, const T* gO, con
         gA, gB, gW, gO, p.A, p.B, p.W, p.Jw, p.Io, cp, p.E, p.nA, p.L, p.nW0, p.nW1, p.nO1,
         wide_copies, only_if_unsorted, call.status);
     MOPS_CUDA_OK(cudaGetLastError());
-    scratch_free(call, scratch);
+    release_table(call, scratch);
     return true;
 }
 
@@ -2382,13 +2384,10 @@ int backward_quad(const Call& call, T* gA, T* gB, T* gW, const T* gO, const Prob
         const size_t smem = d_bytes + warps * warp_bytes;
         const int sms = sm_count(call.device);
         Coupling<T> cp{};
-        void* scratch = nullptr;
+        TableRef scratch{};
         if (!build_coupling(call, p, cp, &scratch, p.nW1, q.DS, false)) return 0;
-        int64_t* offsets =
-            static_cast<int64_t*>(scratch_alloc(call, (p.nW0 + 1) * sizeof(int64_t)));
-        const int64_t pre_blocks = std::min<int64_t>(ceil_div(p.E + 1, 256), sms * 32);
-        segment_offsets<<<static_cast<unsigned>(pre_blocks), 256, 0, call.stream>>>(
-            p.Io, p.E, p.nW0, offsets, call.status);
+        SegmentTable seg = segment_table(call, p.Io, p.E, p.nW0);
+    const int64_t* offsets = seg.offsets;
         const unsigned blocks = static_cast<unsigned>(std::min<int64_t>(ceil_div(p.nW0, warps), sms));
         note_kernel_f("sasaw_vjp_quad<9,9,9,L=%d> warps=%d", p.L == 32 ? 32 : 0, warps);
         if (p.L == 32) {
@@ -2401,8 +2400,9 @@ int backward_quad(const Call& call, T* gA, T* gB, T* gW, const T* gO, const Prob
                 gA, gB, gW, gO, p.A, p.B, p.W, p.Jw, offsets, cp, p.L, p.nW0, call.status);
         }
         MOPS_CUDA_OK(cudaGetLastError());
-        scratch_free(call, offsets);
-        scratch_free(call, scratch);
+        release_table(call, seg.ref);
+        release_table(call, scratch);
+        if (seg.known_sorted) return 1;
         if (call.wait) {
             wait_stream(call);
             if (!host_saw_unsorted(call)) return 1;
@@ -2472,7 +2472,7 @@ template <typename T> void forward(const Call& call, T* O, const Problem<T>& p) 
     if (MOPS_B200_SASAW_FAST(forward_fast, call, O, p)) return;
     const int grid_generic = sm_count(call.device) * 8;
     Coupling<T> cp{};
-    void* scratch = nullptr;
+    TableRef scratch{};
     const bool grouped = build_coupling(call, p, cp, &scratch);
     size_t smem_seg = 0, smem_edge = 0;
     int warps_seg = 0, warps_edge = 0;
@@ -2508,7 +2508,7 @@ template <typename T> void forward(const Call& call, T* O, const Problem<T>& p) 
             p.nO1, call.status);
     }
     MOPS_CUDA_OK(cudaGetLastError());
-    scratch_free(call, scratch);
+    release_table(call, scratch);
 }
 
 template <typename T>
@@ -2522,7 +2522,7 @@ void backward(const Call& call, T* gA, T* gB, T* gW, const T* gO, const Problem<
     if (!empty && backward_mma(call, gA, gB, gW, gO, p)) return;
     if (!empty && MOPS_B200_SASAW_FAST(backward_fast, call, gA, gB, gW, gO, p)) return;
     Coupling<T> cp{};
-    void* scratch = nullptr;
+    TableRef scratch{};
     const bool grouped = !empty && build_coupling(call, p, cp, &scratch);
     size_t smem = 0;
     int warps = 0;
@@ -2549,7 +2549,7 @@ void backward(const Call& call, T* gA, T* gB, T* gW, const T* gO, const Problem<
             p.nW0, p.nW1, p.nO1, call.status);
     }
     MOPS_CUDA_OK(cudaGetLastError());
-    scratch_free(call, scratch);
+    release_table(call, scratch);
 }
 
 template <typename scalar_t>

@@ -434,3 +434,72 @@ def test_full_size_properties():
     sub = M.sparse_accumulation_of_products(A[1000:1100].contiguous(), B[1000:1100].contiguous(),
                                             C, *idx, 50)
     assert torch.equal(sub, O[1000:1100])
+
+
+# ---------------------------------------------------------------- plans
+def test_plan_reuses_tables_and_results_do_not_change(oracle):
+    """With a plan bound, the first call of every kind builds its table and later calls reuse
+    it (forward and VJP of a scatter op share the segment table); results equal the oracle's
+    and, bit for bit, those of the same calls without a plan."""
+    import mops_b200 as M
+    for op in ("hpe", "sap", "opsa", "opsaw", "sasaw"):
+        d = workloads.GENERATORS[op]()
+        t = to_dev(d, np.float64)
+        plain = run_library(op, t)
+        want = run_checker(oracle, op, d, np.float64)
+        plan = M.Plan()
+        with plan:
+            first = run_library(op, t)
+            held = plan.tables
+            assert held >= 1, op
+            again = run_library(op, t)
+            assert plan.tables == held, f"{op}: a repeated call built another table"
+        for k in want:
+            assert_parity(first[k], want[k], f"plan/{op}/{k}")
+            if not (op in ("opsaw", "sasaw") and k == "grad_W"):  # RED order is free
+                assert np.array_equal(first[k], plain[k]), f"plan/{op}/{k} differs from no plan"
+                assert np.array_equal(again[k], plain[k]), f"plan/{op}/{k} differs on reuse"
+        if op in ("opsa", "opsaw"):
+            assert held == 1, f"{op}: forward and VJP must share one segment table, got {held}"
+        plan.close()
+    # outside the block nothing is bound
+    assert M._lib.library().mops_b200_plan_bound() is None
+
+
+def test_plan_does_not_keep_tables_of_bad_or_unsorted_indices(oracle):
+    import mops_b200 as M
+    d = workloads.opsa(J=3000, nO=40)
+    d["indices_output"] = np.random.default_rng(2).permutation(d["indices_output"])
+    t = to_dev(d, np.float64)
+    want = run_checker(oracle, "opsa", d, np.float64)
+    with M.Plan() as plan:
+        for _ in range(2):
+            got = run_library("opsa", t)
+            for k in want:
+                assert_parity(got[k], want[k], f"unsorted with plan/{k}")
+        assert plan.tables == 0
+    d = workloads.hpe(I=64, N=10, J=20)
+    d["indices_A"][7, 2] = 12
+    t = to_dev(d, np.float64)
+    with M.Plan() as plan:
+        for _ in range(2):
+            with pytest.raises(M.MopsError, match="Index array indices_A"):
+                M.homogeneous_polynomial_evaluation(t["A"], t["C"], t["indices_A"])
+        assert plan.tables == 0
+
+
+def test_plan_second_order_calls_are_not_cached_from_temporaries(oracle):
+    """HPE's second-order path derives tables from temporaries; a bound plan must not keep
+    them (two different problems in a row would otherwise share a stale table)."""
+    import mops_b200 as M
+    r = np.random.default_rng(5)
+    alive = []  # the contract: arrays a plan has seen stay alive and unchanged
+    with M.Plan():
+        for seed in (1, 2):
+            d = workloads.hpe(I=80, N=9, J=30, K=3, seed=seed)
+            d["grad_grad_A"] = r.standard_normal(d["A"].shape)
+            alive.append(to_dev(d, np.float64))
+            got = run_library("hpe", alive[-1], second_order=True)
+            want = run_checker(oracle, "hpe", d, np.float64, second_order=True)
+            for k in want:
+                assert_parity(got[k], want[k], f"hpe second order with plan/{k}")
