@@ -216,6 +216,18 @@ MOPS_EXPORT mops_b200_plan_t* mops_b200_plan_bound(void);
 /* Number of tables the plan currently holds. */
 MOPS_EXPORT int mops_b200_plan_tables(const mops_b200_plan_t* plan);
 
+/* Stable sort of a scatter index on the device (no counterpart in the reference, whose callers
+ * sort on the host before the call, python/mops/tests/opsa.py:96): on return sorted[i] =
+ * indices[permutation[i]] is ascending and entries with equal values keep their input order.
+ * All three are device arrays of the same length (< 2^31); values must lie in [0, n_rows).
+ * Apply `permutation` to the rows of A, B (and indices_W) to obtain the sorted problem the
+ * scatter operations run fastest on; applied to indices_W / indices_W_1 it groups the grad_W
+ * contributions by row of W. Same status convention, stream and completion rules as the
+ * mops_cuda_* entry points. */
+MOPS_EXPORT int mops_b200_cuda_sort_index(mops_tensor_1d_i32_t sorted,
+                                          mops_tensor_1d_i32_t permutation,
+                                          mops_tensor_1d_i32_t indices, int64_t n_rows);
+
 /* Names (with template arguments) of the main kernels the calling thread's last mops_cuda_*
  * call dispatched to, "; "-separated; valid until that thread's next call. For tools that
  * pair a timing with the profile of the same kernel instantiation. */

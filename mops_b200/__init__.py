@@ -30,7 +30,7 @@ from . import _lib
 from ._lib import MopsError  # noqa: F401
 
 __all__ = [f"{op}{lvl}" for op in _lib.OPERATIONS for lvl in _lib.LEVELS] + [
-    "MopsError", "HostQueue", "Plan"]
+    "MopsError", "HostQueue", "Plan", "sort_indices"]
 
 
 def _torch():
@@ -78,6 +78,41 @@ def _check(array, ndim, kind, operation, name):
 def _check_scalar(value, operation, name):
     if not isinstance(value, (int, np.integer)) or isinstance(value, bool):
         raise TypeError(f"`{name}` must be a scalar in {operation}, got {type(value)}")
+
+
+def sort_indices(indices, n_rows):
+    """Stable sort of a scatter index on the GPU: returns ``(sorted, permutation)`` with
+    ``sorted == indices[permutation]`` ascending and equal values in input order, as int32
+    arrays of the kind given (CUDA tensor in, CUDA tensors out; host arrays are staged through
+    the current device). Permute the rows of ``A``, ``B`` (and ``indices_W``) with
+    ``permutation`` to get the sorted problem the scatter operations run fastest on."""
+    op = "sort_indices"
+    _check(indices, 1, "i", op, "indices")
+    _check_scalar(n_rows, op, "n_rows")
+    torch = _torch()
+    numpy_in = isinstance(indices, np.ndarray)
+    t = torch.from_numpy(np.ascontiguousarray(indices)) if numpy_in else indices
+    was_cuda = t.is_cuda
+    if not torch.cuda.is_available():
+        raise MopsError("no CUDA device available")
+    dev = t.device if was_cuda else torch.device("cuda", torch.cuda.current_device())
+    t = t.to(dev).to(torch.int32).contiguous()
+    out, perm = torch.empty_like(t), torch.empty_like(t)
+    lib = _lib.library()
+    fn = lib.mops_b200_cuda_sort_index
+    structs = [_lib.make_struct(x.data_ptr(), x.shape) for x in (out, perm, t)]
+    fn.restype, fn.argtypes = ctypes.c_int, [type(s) for s in structs] + [ctypes.c_int64]
+    with torch.cuda.device(dev):
+        previous = lib.mops_b200_get_stream()
+        lib.mops_b200_set_stream(torch.cuda.current_stream().cuda_stream)
+        try:
+            _lib.check_status(fn(*structs, int(n_rows)))
+        finally:
+            lib.mops_b200_set_stream(previous)
+    if was_cuda:
+        return out, perm
+    out, perm = out.cpu(), perm.cpu()
+    return (out.numpy(), perm.numpy()) if numpy_in else (out, perm)
 
 
 class Plan:

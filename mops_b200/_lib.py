@@ -31,7 +31,7 @@ def abi_symbols():
 EXTENSION_SYMBOLS = ("mops_b200_set_stream", "mops_b200_get_stream", "mops_b200_set_wait",
                      "mops_b200_get_wait", "mops_b200_version", "mops_b200_last_kernels",
                      "mops_b200_plan_create", "mops_b200_plan_destroy", "mops_b200_plan_bind",
-                     "mops_b200_plan_bound", "mops_b200_plan_tables",
+                     "mops_b200_plan_bound", "mops_b200_plan_tables", "mops_b200_cuda_sort_index",
                      "mops_b200_cuda_sparse_accumulation_scatter_add_with_weights_noalloc_f64")
 
 

@@ -27,7 +27,7 @@ ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ARCH + ["-lineinfo", "-O3", "-std=c++17", "-ccbin", HOST_CXX, "-Xcompiler",
                      "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr"]
 
-KERNEL_SOURCES = ["runtime.cu", "hpe.cu", "sap.cu", "opsa.cu", "sasaw.cu", "capi.cu",
+KERNEL_SOURCES = ["runtime.cu", "hpe.cu", "sap.cu", "opsa.cu", "sasaw.cu", "sort.cu", "capi.cu",
                   "host_stubs.cpp"]
 
 

@@ -156,6 +156,15 @@ extern "C" void mops_b200_set_stream(void* stream) { mops_b200::set_stream(strea
 extern "C" void* mops_b200_get_stream(void) { return mops_b200::get_stream(); }
 extern "C" void mops_b200_set_wait(int wait) { mops_b200::set_wait(wait != 0); }
 extern "C" int mops_b200_get_wait(void) { return mops_b200::get_wait() ? 1 : 0; }
+namespace mops_b200 {
+void sort_index(mops::Tensor<int32_t, 1>, mops::Tensor<int32_t, 1>, mops::Tensor<int32_t, 1>, int64_t);
+}
+extern "C" int mops_b200_cuda_sort_index(mops_tensor_1d_i32_t sorted,
+                                         mops_tensor_1d_i32_t permutation,
+                                         mops_tensor_1d_i32_t indices, int64_t n_rows) {
+    return guarded([&] { mops_b200::sort_index(cpp(sorted), cpp(permutation), cpp(indices), n_rows); });
+}
+
 extern "C" int mops_b200_plan_create(mops_b200_plan_t** plan) {
     return guarded([&] {
         if (plan == nullptr) throw std::runtime_error("mops_b200_plan_create: plan is NULL");

@@ -532,9 +532,103 @@ HpePlan make_plan(const Call& call, TableRef* scratch, const T* C, const int32_t
     return plan;
 }
 
+// ---------------------------------------------------------------- small batches
+// With one lane per batch row, a batch of a thousand rows is 32 blocks and most of the GPU
+// idles while every block walks the whole table. For small batches the roles are swapped: one
+// warp per batch row (its A row in shared memory, record offsets = column numbers), lanes over
+// the monomials (forward) or over the incidences of one factor (VJP), one shuffle reduction per
+// result. A thousand rows are then a thousand warps.
+constexpr int kSmallWarps = 8;
+constexpr int64_t kSmallBatch = 8192; // rows up to which the warp-per-row kernels are used
+
+template <typename T, int K>
+__global__ void __launch_bounds__(kSmallWarps * 32)
+hpe_fwd_warp(T* __restrict__ O, const T* __restrict__ A, const unsigned char* __restrict__ rec,
+             int64_t I, int N, int J) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    constexpr int RB = record_bytes(sizeof(T), K);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * kSmallWarps + warp;
+    if (i >= I) return;
+    T* row = reinterpret_cast<T*>(smem_raw) + static_cast<size_t>(warp) * N;
+    for (int n = lane; n < N; n += 32) row[n] = A[i * N + n];
+    __syncwarp();
+    T acc = T(0);
+    for (int j = lane; j < J; j += 32) {
+        int o[K > 0 ? K : 1];
+        T term = read_record<T, K>(rec + static_cast<size_t>(j) * RB, o);
+#pragma unroll
+        for (int k = 0; k < K; k++) term *= row[o[k]];
+        acc += term;
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) O[i] = acc;
+}
+
+template <typename T, int K>
+__global__ void __launch_bounds__(kSmallWarps * 32)
+hpe_vjp_warp(T* __restrict__ gA, const T* __restrict__ gO, const T* __restrict__ A, HpePlan plan,
+             int64_t I, int N) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    constexpr int NF = K - 1;
+    constexpr int RB = record_bytes(sizeof(T), NF);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * kSmallWarps + warp;
+    int32_t* starts = reinterpret_cast<int32_t*>(
+        smem_raw + static_cast<size_t>(N) * kSmallWarps * sizeof(T)); // [N + 1]
+    for (int n = threadIdx.x; n <= N; n += blockDim.x) starts[n] = plan.n_start[n];
+    __syncthreads();
+    if (i >= I) return;
+    T* row = reinterpret_cast<T*>(smem_raw) + static_cast<size_t>(warp) * N;
+    for (int n = lane; n < N; n += 32) row[n] = A[i * N + n];
+    __syncwarp();
+    const T g = gO[i];
+    T mine = T(0); // lane (n & 31) keeps the result of factor n until 32 of them go out together
+    // four factors at a time, so that their shuffle reductions overlap
+    for (int n0 = 0; n0 < N; n0 += 4) {
+        T acc[4];
+#pragma unroll
+        for (int f = 0; f < 4; f++) {
+            acc[f] = T(0);
+            const int n = n0 + f < N ? n0 + f : N - 1;
+            const int lo = starts[n], hi = n0 + f < N ? starts[n + 1] : lo;
+            for (int x = lo + lane; x < hi; x += 32) {
+                int o[NF > 0 ? NF : 1];
+                T term = read_record<T, NF>(plan.vjp_rec + static_cast<size_t>(x) * RB, o);
+#pragma unroll
+                for (int k = 0; k < NF; k++) term *= row[o[k]];
+                acc[f] += term;
+            }
+        }
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1)
+#pragma unroll
+            for (int f = 0; f < 4; f++) acc[f] += __shfl_xor_sync(kFullMask, acc[f], d);
+#pragma unroll
+        for (int f = 0; f < 4; f++)
+            if (lane == ((n0 + f) & 31)) mine = g * acc[f];
+        const int last = n0 + 3 < N ? n0 + 3 : N - 1;
+        if ((last & 31) == 31 || last == N - 1) {
+            const int col = (last & ~31) + lane;
+            if (col <= last) gA[i * N + col] = mine;
+        }
+    }
+}
+
 template <typename T, int K>
 void launch_fwd(const Call& call, T* O, const T* A, const T* C, const int32_t* P, int64_t I,
                 int N, int64_t J) {
+    if (I <= kSmallBatch && static_cast<size_t>(N) * kSmallWarps * sizeof(T) <= 48 * 1024) {
+        TableRef scratch{};
+        HpePlan plan = make_plan<T>(call, &scratch, C, P, J, K, N, true, false, 1);
+        note_kernel_f("hpe_fwd_warp<%s,K=%d>", scalar_name<T>(), K);
+        hpe_fwd_warp<T, K><<<static_cast<unsigned>(ceil_div(I, kSmallWarps)), kSmallWarps * 32,
+                             static_cast<size_t>(N) * kSmallWarps * sizeof(T), call.stream>>>(
+            O, A, plan.fwd_rec, I, N, static_cast<int>(J));
+        MOPS_CUDA_OK(cudaGetLastError());
+        release_table(call, scratch);
+        return;
+    }
     // Two rows per lane when the batch still fills the GPU that way and the wider tile fits.
     const size_t smem2 = fwd_smem<T, K>(N, 2);
     const bool two = I >= static_cast<int64_t>(sm_count(call.device)) * 64 * 8 &&
@@ -567,6 +661,19 @@ void launch_vjp(const Call& call, T* gA, const T* gO, const T* A, const T* C, co
                 int64_t I, int N, int64_t J) {
     if (K == 0 || J == 0) { // no factor depends on A
         MOPS_CUDA_OK(cudaMemsetAsync(gA, 0, I * N * sizeof(T), call.stream));
+        return;
+    }
+    if (I <= kSmallBatch && static_cast<size_t>(N) * kSmallWarps * sizeof(T) <= 48 * 1024) {
+        TableRef scratch{};
+        HpePlan plan = make_plan<T>(call, &scratch, C, P, J, K, N, false, true, 1);
+        note_kernel_f("hpe_vjp_warp<%s,K=%d>", scalar_name<T>(), K);
+        hpe_vjp_warp<T, K><<<static_cast<unsigned>(ceil_div(I, kSmallWarps)), kSmallWarps * 32,
+                             static_cast<size_t>(N) * kSmallWarps * sizeof(T) +
+                                 (static_cast<size_t>(N) + 1) * sizeof(int32_t),
+                             call.stream>>>(
+            gA, gO, A, plan, I, N);
+        MOPS_CUDA_OK(cudaGetLastError());
+        release_table(call, scratch);
         return;
     }
     // Several rows per lane when the batch still fills the GPU that way and the wider tile fits.

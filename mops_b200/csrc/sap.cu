@@ -661,11 +661,14 @@ __global__ void sap_fwd_small(T* __restrict__ O, const T* __restrict__ S, const 
     T* o = O + i * nO;
     // The triplets are one stream across all groups, read two ahead: (c0, v0) is triplet k with
     // its operand already loaded, e1 is triplet k + 1.
-    int k = 0;
-    Entry<T> e1 = fetch_shared(table);
+    // (small batches: gridDim.y blocks share a block of rows, each takes a range of columns)
+    const int col_lo = static_cast<int>(static_cast<int64_t>(nO) * blockIdx.y / gridDim.y);
+    const int col_hi = static_cast<int>(static_cast<int64_t>(nO) * (blockIdx.y + 1) / gridDim.y);
+    int k = start[col_lo * NS];
+    Entry<T> e1 = fetch_shared(table + k);
     T c0 = e1.c, v0 = t[e1.o1];
-    e1 = fetch_shared(table + 1);
-    for (int col = 0; col < nO; col++) {
+    e1 = fetch_shared(table + k + 1);
+    for (int col = col_lo; col < col_hi; col++) {
         const int32_t* bounds = start + col * NS + 1;
         T acc = T(0);
 #pragma unroll
@@ -751,7 +754,7 @@ inline int small_width(int nA, int nB) {
 // block, the tiles per row); 0 if 32 rows do not fit.
 template <typename T>
 int rows_small(const Call& call, const void* kernel, int cols, int64_t K, int nbins,
-               size_t* smem) {
+               size_t* smem, int64_t batch) {
     cudaFuncAttributes attr{};
     MOPS_CUDA_OK(cudaFuncGetAttributes(&attr, kernel));
     const int regs = std::max(attr.numRegs, 1);
@@ -771,6 +774,9 @@ int rows_small(const Call& call, const void* kernel, int cols, int64_t K, int nb
             best_r = R;
             *smem = total;
         }
+        // A batch too small to give every SM a block of this size: the smallest block spreads
+        // the rows over the most SMs (the work per row does not depend on the block size).
+        if (R == 32 && batch <= static_cast<int64_t>(sm_count(call.device)) * 64) return R;
     }
     return best_r;
 }
@@ -819,12 +825,16 @@ bool forward_small(const Call& call, T* O, const T* A, const T* B, const T* C, c
     const void* kernel = NS == 4   ? reinterpret_cast<const void*>(sap_fwd_small<T, 4>)
                          : NS == 8 ? reinterpret_cast<const void*>(sap_fwd_small<T, 8>)
                                    : reinterpret_cast<const void*>(sap_fwd_small<T, 16>);
-    const int R = rows_small<T>(call, kernel, nT, K, nO * NS, &smem);
+    const int R = rows_small<T>(call, kernel, nT, K, nO * NS, &smem, I);
     if (R == 0) return false;
     TableRef scratch{};
     SmallPlan<T> plan = make_small_plan<T>(call, &scratch, C, PS, PT, PO, K, nS, nT, nO, NS, R + 1,
                                            0, b_small ? 1 : 0, b_small ? 0 : 1);
-    const unsigned blocks = static_cast<unsigned>(ceil_div(I, R));
+    const int64_t row_blocks = ceil_div(I, R);
+    // few row blocks: split the output columns over up to eight blocks per block of rows
+    const int col_parts = static_cast<int>(std::max<int64_t>(
+        1, std::min<int64_t>(std::min(nO, 8), 2 * sm_count(call.device) / row_blocks)));
+    const dim3 blocks(static_cast<unsigned>(row_blocks), static_cast<unsigned>(col_parts));
     note_kernel_f("sap_fwd_small<%s,NS=%d> rows/block=%d", scalar_name<T>(), NS, R);
 #define MOPS_B200_LAUNCH(NS_)                                                                      \
     {                                                                                              \
@@ -855,7 +865,7 @@ bool backward_small(const Call& call, T* gA, T* gB, const T* gO, const T* A, con
     const void* kernel = NS == 4   ? reinterpret_cast<const void*>(sap_vjp_small<T, 4>)
                          : NS == 8 ? reinterpret_cast<const void*>(sap_vjp_small<T, 8>)
                                    : reinterpret_cast<const void*>(sap_vjp_small<T, 16>);
-    const int R = rows_small<T>(call, kernel, nO, K, nT * NS, &smem);
+    const int R = rows_small<T>(call, kernel, nO, K, nT * NS, &smem, I);
     if (R == 0) return false;
     TableRef scratch{};
     SmallPlan<T> plan = make_small_plan<T>(call, &scratch, C, PS, PT, PO, K, nS, nT, nO, NS, R + 1,

@@ -503,3 +503,54 @@ def test_plan_second_order_calls_are_not_cached_from_temporaries(oracle):
             want = run_checker(oracle, "hpe", d, np.float64, second_order=True)
             for k in want:
                 assert_parity(got[k], want[k], f"hpe second order with plan/{k}")
+
+
+# ---------------------------------------------------------------- sorting the scatter index
+@pytest.mark.parametrize("n,n_rows", [(1, 1), (33, 7), (5000, 300), (70001, 1 << 16),
+                                      (300000, 70000), (1 << 20, 1 << 18), (4097, 1 << 24)])
+def test_sort_indices_is_a_stable_sort(n, n_rows):
+    import torch
+    import mops_b200 as M
+    r = np.random.default_rng(n)
+    idx = r.integers(0, n_rows, n, dtype=np.int32)
+    got, perm = M.sort_indices(torch.from_numpy(idx).cuda(), n_rows)
+    want_perm = np.argsort(idx, kind="stable").astype(np.int32)
+    assert np.array_equal(perm.cpu().numpy(), want_perm)
+    assert np.array_equal(got.cpu().numpy(), idx[want_perm])
+    # host arrays are staged
+    got_h, perm_h = M.sort_indices(idx, n_rows)
+    assert isinstance(got_h, np.ndarray) and np.array_equal(perm_h, want_perm)
+
+
+def test_sort_indices_then_scatter_matches_the_oracle_on_unsorted_input(oracle):
+    """The intended use: sort once on the device, permute the rows, run the segmented kernels
+    (a plan then knows the index is sorted); same result as the oracle on the unsorted input."""
+    import torch
+    import mops_b200 as M
+    d = workloads.opsaw(E=20000, n=300)
+    shuffle = np.random.default_rng(9).permutation(20000)
+    for k in ("A", "B", "indices_W", "indices_output"):
+        d[k] = d[k][shuffle]
+    want = run_checker(oracle, "opsaw", d, np.float64)
+    t = to_dev(d, np.float64)
+    PO, perm = M.sort_indices(t["indices_output"], 300)
+    perm = perm.long()
+    A, B, PW = t["A"][perm].contiguous(), t["B"][perm].contiguous(), t["indices_W"][perm].contiguous()
+    with M.Plan() as plan:
+        O = M.outer_product_scatter_add_with_weights(A, B, t["W"], PW, PO)
+        gA, gB, gW = M.outer_product_scatter_add_with_weights_vjp(t["grad_output"], A, B, t["W"], PW, PO)
+        assert plan.tables == 1
+    inverse = torch.empty_like(perm)
+    inverse[perm] = torch.arange(perm.numel(), device=perm.device)
+    assert_parity(O.cpu().numpy(), want["output"], "sorted opsaw output")
+    assert_parity(gA[inverse].cpu().numpy(), want["grad_A"], "sorted opsaw grad_A")
+    assert_parity(gB[inverse].cpu().numpy(), want["grad_B"], "sorted opsaw grad_B")
+    assert_parity(gW.cpu().numpy(), want["grad_W"], "sorted opsaw grad_W")
+
+
+def test_sort_indices_reports_values_out_of_range():
+    import torch
+    import mops_b200 as M
+    idx = torch.tensor([3, 1, 9, 2], dtype=torch.int32, device="cuda")
+    with pytest.raises(M.MopsError, match="Index array indices in operation cuda_sort_index"):
+        M.sort_indices(idx, 9)
