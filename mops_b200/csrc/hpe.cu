@@ -663,7 +663,8 @@ void launch_vjp(const Call& call, T* gA, const T* gO, const T* A, const T* C, co
         MOPS_CUDA_OK(cudaMemsetAsync(gA, 0, I * N * sizeof(T), call.stream));
         return;
     }
-    if (I <= kSmallBatch && static_cast<size_t>(N) * kSmallWarps * sizeof(T) <= 48 * 1024) {
+    if (I <= kSmallBatch && static_cast<size_t>(N) * kSmallWarps * sizeof(T) +
+                                    (static_cast<size_t>(N) + 1) * sizeof(int32_t) <= 48 * 1024) {
         TableRef scratch{};
         HpePlan plan = make_plan<T>(call, &scratch, C, P, J, K, N, false, true, 1);
         note_kernel_f("hpe_vjp_warp<%s,K=%d>", scalar_name<T>(), K);

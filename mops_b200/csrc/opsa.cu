@@ -27,6 +27,7 @@
 // staged back in place and written with coalesced stores; gW is accumulated with RED.
 #include <algorithm>
 #include <cstdlib>
+#include <type_traits>
 
 #include "bulk.cuh"
 #include "checks.hpp"
@@ -528,7 +529,7 @@ template <typename T, bool WEIGHTED> PipeLayout choose_pipe_layout(int K, int L,
     // 0.59 ms, VJP 1.12 ms against 0.92 / 1.63 with chunks of 32).
     int ch = env_int("MOPS_B200_PIPE_CH", WEIGHTED ? 8 : 32);
     int stages = env_int("MOPS_B200_PIPE_STAGES", 2);
-    ch = std::max(4, std::min(32, ch / 4 * 4));
+    ch = std::max(4, std::min(WEIGHTED ? 32 : 128, ch / 4 * 4)); // weighted: one lane per entry
     stages = std::max(2, std::min(8, stages));
     return pipe_layout(sizeof(T), K, L, WEIGHTED, vjp, ch, stages);
 }
@@ -572,6 +573,31 @@ bool forward_pipe(const Call& call, T* O, const T* A, const T* B, const T* W, co
     const PipeLayout lay = choose_pipe_layout<T, WEIGHTED>(K, L, false);
     if (static_cast<size_t>(lay.warp_bytes) * kPipeWarps > static_cast<size_t>(max_optin_smem(call.device)))
         return false;
+    if constexpr (std::is_same<T, float>::value && !WEIGHTED) {
+        // f32 without weights: the TF32 tensor path (MOPS_B200_TF32=0: development switch back
+        // to the FP64 MMA route)
+        if (env_int("MOPS_B200_TF32", 1) != 0) {
+            const size_t smem = static_cast<size_t>(lay.warp_bytes) * kPipeWarps;
+            note_kernel_f("opsa_fwd_pipe_tf32<NT=%d> ch=%d stages=%d", (L + 7) / 8, lay.ch,
+                          lay.stages);
+#define MOPS_B200_CASE(NT_)                                                                        \
+    {                                                                                              \
+        auto kernel = opsa_fwd_pipe_tf32<NT_>;                                                     \
+        const unsigned blocks = pipe_grid(call, kernel, smem, nO);                                 \
+        kernel<<<blocks, kPipeWarps * 32, smem, call.stream>>>(O, A, B, offsets, J, nO, lay,       \
+                                                               call.status);                      \
+    }
+            switch ((L + 7) / 8) {
+            case 1: MOPS_B200_CASE(1) break;
+            case 2: MOPS_B200_CASE(2) break;
+            case 3: MOPS_B200_CASE(3) break;
+            default: MOPS_B200_CASE(4) break;
+            }
+#undef MOPS_B200_CASE
+            MOPS_CUDA_OK(cudaGetLastError());
+            return true;
+        }
+    }
     note_kernel_f("opsa_fwd_pipe<%s,MT=%d,NT=%d,W=%d> ch=%d stages=%d", scalar_name<T>(),
                   K <= 8 ? 1 : 2, (L + 7) / 8, WEIGHTED ? 1 : 0, lay.ch, lay.stages);
     if (K <= 8)
@@ -607,6 +633,33 @@ bool backward_pipe(const Call& call, T* gA, T* gB, T* gW, const T* gO, const T* 
     const PipeLayout lay = choose_pipe_layout<T, WEIGHTED>(K, L, true);
     if (static_cast<size_t>(lay.warp_bytes) * kPipeWarps > static_cast<size_t>(max_optin_smem(call.device)))
         return false;
+    if constexpr (std::is_same<T, float>::value && !WEIGHTED) {
+        if (env_int("MOPS_B200_TF32", 1) != 0) {
+            const size_t smem = static_cast<size_t>(lay.warp_bytes) * kPipeWarps;
+            note_kernel_f("opsa_vjp_pipe_tf32<KS=%d,LS=%d> ch=%d stages=%d", (K + 7) / 8,
+                          (L + 7) / 8, lay.ch, lay.stages);
+#define MOPS_B200_CASE(KS_, LS_)                                                                   \
+    {                                                                                              \
+        auto kernel = opsa_vjp_pipe_tf32<KS_, LS_>;                                                \
+        const unsigned blocks = pipe_grid(call, kernel, smem, nO);                                 \
+        kernel<<<blocks, kPipeWarps * 32, smem, call.stream>>>(gA, gB, gO, A, B, offsets, J, nO,   \
+                                                               lay, call.status);                 \
+    }
+            switch (((K + 7) / 8) * 10 + (L + 7) / 8) {
+            case 11: MOPS_B200_CASE(1, 1) break;
+            case 12: MOPS_B200_CASE(1, 2) break;
+            case 13: MOPS_B200_CASE(1, 3) break;
+            case 14: MOPS_B200_CASE(1, 4) break;
+            case 21: MOPS_B200_CASE(2, 1) break;
+            case 22: MOPS_B200_CASE(2, 2) break;
+            case 23: MOPS_B200_CASE(2, 3) break;
+            default: MOPS_B200_CASE(2, 4) break;
+            }
+#undef MOPS_B200_CASE
+            MOPS_CUDA_OK(cudaGetLastError());
+            return true;
+        }
+    }
     note_kernel_f("opsa_vjp_pipe<%s,KT=%d,LT8=%d,W=%d> ch=%d stages=%d", scalar_name<T>(),
                   (K + 3) / 4, (L + 7) / 8, WEIGHTED ? 1 : 0, lay.ch, lay.stages);
     switch ((K + 3) / 4) {

@@ -22,7 +22,7 @@ struct PipeLayout {
                   // piece, L + 4 when rows are copied one by one (weighted: conflict-free)
     int row_pieces;      // weighted: 16-byte pieces of one B / W row
     int row_pieces_log2; // its log2 when it is a power of two, else -1
-    int ch;       // entries per chunk: a multiple of 4, at most 32
+    int ch;       // entries per chunk: a multiple of 4 (at most 32 with weights: a lane per entry)
     int stages;   // chunks in flight per warp + 1
     int a_off, b_off, w_off, pw_off; // byte offsets inside a stage (16-byte aligned)
     int stage_bytes;
@@ -525,5 +525,401 @@ opsa_vjp_pipe(S* __restrict__ gA, S* __restrict__ gB, S* __restrict__ gW,
     }
     // Rows after the last entry have no gradients to produce, but their grad_output copies
     // may still be in flight into this block's shared memory: wait for them before leaving.
+    next_rows();
+}
+
+// ------------------------------------------------------------- f32 on the TF32 tensor path
+// For f32 operands the FP64 MMA route above is bound by the FP64 tensor pipe (63 % busy at
+// 57 % of the HBM peak): f32 moves half the bytes but needs the same number of FP64 MMAs. The
+// kernels below run the same streaming structure on mma.sync m16n8k8 TF32 with the
+// three-product split: every f32 operand x is taken as hi + lo with hi = tf32(x), lo =
+// tf32(x - hi), and a product a*b as a_hi*b_hi + a_hi*b_lo + a_lo*b_hi (the dropped a_lo*b_lo
+// is below 2^-22 |ab|), accumulated in f32. The result is f32-accurate (the parity tests hold
+// it to 1e-5 of the largest output, like every f32 path). In the forward, where one output
+// row sums over arbitrarily many entries, only the small correction products are chained
+// through the tensor core's accumulator (which may round towards zero); the main products of
+// every 8-entry step start from zero and are added to the running sums by ordinary f32
+// additions.
+__device__ __forceinline__ void tf32_split(float x, unsigned& hi, unsigned& lo) {
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(x));
+    const float rest = x - __uint_as_float(hi);
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo) : "f"(rest));
+}
+
+// d += a b for one m16n8k8 tile. Fragments (g = lane / 4, t = lane % 4):
+// a0 (g, t) a1 (g + 8, t) a2 (g, t + 4) a3 (g + 8, t + 4); b0 (k = t, n = g) b1 (k = t + 4,
+// n = g); d0 (g, 2 t) d1 (g, 2 t + 1) d2 (g + 8, 2 t) d3 (g + 8, 2 t + 1).
+__device__ __forceinline__ void mma_tf32(float (&d)[4], const unsigned (&a)[4], const unsigned (&b)[2]) {
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+                 "{%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+// Forward, f32, K <= 16, L <= 32, no weights: O[r] = A[seg]^T B[seg], eight entries per step
+// (the entries are the MMA's k dimension). NT = ceil(L / 8).
+template <int NT>
+__global__ void __launch_bounds__(kPipeWarps * 32, 4)
+opsa_fwd_pipe_tf32(float* __restrict__ O, const float* __restrict__ A, const float* __restrict__ B,
+                   const int64_t* __restrict__ offsets, int64_t J, int64_t nO, PipeLayout lay,
+                   Status st) {
+    extern __shared__ __align__(128) unsigned char pipe_smem[];
+    if (saw_unsorted(st)) return; // the atomic kernel of the same call does the work
+    const int lane = threadIdx.x & 31;
+    const int warp = __shfl_sync(kFullMask, threadIdx.x >> 5, 0);
+    const int g = lane >> 2, t = lane & 3;
+    const int K = lay.K, L = lay.L, CH = lay.ch, NS = lay.stages;
+    unsigned char* area = pipe_smem + static_cast<size_t>(warp) * lay.warp_bytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(area + lay.bar_off);
+    if (lane == 0) {
+        for (int s = 0; s < NS; s++) mbarrier_init(bars + s, 1);
+        mbarrier_init_fence();
+    }
+    __syncwarp();
+    const PipeWarp w = pipe_partition(offsets, nO, CH, warp);
+    if (w.r0 >= w.r1) return;
+
+    int issued = 0;
+    auto issue_next = [&]() {
+        if (issued < w.nchunks) {
+            const int s = issued % NS;
+            pipe_issue_chunk<float, false>(lay, area + s * lay.stage_bytes, bars + s, A, B, nullptr,
+                                           w.e_first + static_cast<int64_t>(issued) * CH, J, 0, lane);
+            issued++;
+        }
+    };
+    for (int i = 0; i < NS - 1; i++) issue_next();
+
+    int64_t wbase = w.r0;
+    auto load_window = [&](int64_t base) {
+        const int64_t i = base + 1 + lane;
+        return offsets[i < nO ? i : nO];
+    };
+    int64_t win = load_window(wbase);
+    auto row_end = [&](int64_t r) -> int64_t {
+        if (r - wbase >= 32) {
+            wbase = r;
+            win = load_window(wbase);
+        }
+        return __shfl_sync(kFullMask, win, static_cast<int>(r - wbase));
+    };
+
+    float sum[NT][4], corr[NT][4]; // running sums of the main products / chained corrections
+    auto clear = [&] {
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) sum[nt][i] = corr[nt][i] = 0.0f;
+    };
+    const int64_t rowsize = static_cast<int64_t>(K) * L;
+    const bool pair_ok = L % 2 == 0 && reinterpret_cast<uintptr_t>(O) % 8 == 0;
+    // element (nt, 2 h + i) is O[r, k = g + 8 h, l = 8 nt + 2 t + i]
+    auto flush = [&](int64_t r) {
+        float* dst = O + r * rowsize;
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int k = g + 8 * h;
+            if (k >= K) continue;
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                const int l = 8 * nt + 2 * t;
+                if (l >= L) continue;
+                const float v0 = sum[nt][2 * h] + corr[nt][2 * h];
+                const float v1 = sum[nt][2 * h + 1] + corr[nt][2 * h + 1];
+                float* d2 = dst + k * L + l;
+                if (pair_ok) {
+                    *reinterpret_cast<float2*>(d2) = make_float2(v0, v1);
+                } else {
+                    d2[0] = v0;
+                    if (l + 1 < L) d2[1] = v1;
+                }
+            }
+        }
+    };
+
+    clear();
+    int64_t e = w.e_begin, row = w.r0;
+    int64_t hi = row_end(row);
+    auto finish_rows = [&] {
+        while (row < w.r1 && e == hi) {
+            flush(row);
+            clear();
+            row++;
+            if (row < w.r1) hi = row_end(row);
+        }
+    };
+
+    for (int c = 0; c < w.nchunks; c++) {
+        issue_next();
+        const int s = c % NS;
+        if (!mbarrier_wait(bars + s, (c / NS) & 1)) {
+            if (lane == 0) report_stalled(st);
+            return;
+        }
+        __syncwarp();
+        const unsigned char* stage = area + s * lay.stage_bytes;
+        const float* As = reinterpret_cast<const float*>(stage + lay.a_off);
+        const float* Bs = reinterpret_cast<const float*>(stage + lay.b_off);
+        const int64_t c_lo = w.e_first + static_cast<int64_t>(c) * CH;
+        const int64_t c_hi = c_lo + CH < w.e_last ? c_lo + CH : w.e_last;
+        while (true) {
+            finish_rows();
+            if (row >= w.r1 || e >= c_hi) break;
+            const int64_t seg_end = hi < c_hi ? hi : c_hi;
+            const int first = static_cast<int>(e - c_lo), last = static_cast<int>(seg_end - c_lo);
+            for (int s0 = first; s0 < last; s0 += 8) {
+                // A^T fragment: (row k, column entry); B fragment: (row entry, column l)
+                const int e0 = s0 + t, e1 = s0 + t + 4;
+                const bool v0 = e0 < last, v1 = e1 < last;
+                unsigned ah[4], al[4];
+                tf32_split((v0 && g < K) ? As[e0 * K + g] : 0.0f, ah[0], al[0]);
+                tf32_split((v0 && g + 8 < K) ? As[e0 * K + g + 8] : 0.0f, ah[1], al[1]);
+                tf32_split((v1 && g < K) ? As[e1 * K + g] : 0.0f, ah[2], al[2]);
+                tf32_split((v1 && g + 8 < K) ? As[e1 * K + g + 8] : 0.0f, ah[3], al[3]);
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) {
+                    const int l = 8 * nt + g;
+                    unsigned bh[2], bl[2];
+                    tf32_split((v0 && l < L) ? Bs[e0 * L + l] : 0.0f, bh[0], bl[0]);
+                    tf32_split((v1 && l < L) ? Bs[e1 * L + l] : 0.0f, bh[1], bl[1]);
+                    float main_[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                    mma_tf32(main_, ah, bh);
+                    mma_tf32(corr[nt], ah, bl);
+                    mma_tf32(corr[nt], al, bh);
+#pragma unroll
+                    for (int i = 0; i < 4; i++) sum[nt][i] += main_[i];
+                }
+            }
+            e = seg_end;
+        }
+        __syncwarp();
+    }
+    finish_rows();
+}
+
+// VJP, f32, K <= 16, L <= 32, no weights: for the entries of one output row grad_A[seg] =
+// B[seg] gO[r]^T and grad_B[seg] = A[seg] gO[r], sixteen entries per tile (the entries are the
+// MMA's m dimension), gO[r] split once per row and kept in registers. KS = ceil(K / 8),
+// LS = ceil(L / 8).
+template <int KS, int LS>
+__global__ void __launch_bounds__(kPipeWarps * 32, 3)
+opsa_vjp_pipe_tf32(float* __restrict__ gA, float* __restrict__ gB, const float* __restrict__ gO,
+                   const float* __restrict__ A, const float* __restrict__ B,
+                   const int64_t* __restrict__ offsets, int64_t J, int64_t nO, PipeLayout lay,
+                   Status st) {
+    extern __shared__ __align__(128) unsigned char pipe_smem[];
+    if (saw_unsorted(st)) return; // the entry-per-lane kernel of the same call does the work
+    const int lane = threadIdx.x & 31;
+    const int warp = __shfl_sync(kFullMask, threadIdx.x >> 5, 0);
+    const int g = lane >> 2, t = lane & 3;
+    const int K = lay.K, L = lay.L, CH = lay.ch, NS = lay.stages;
+    unsigned char* area = pipe_smem + static_cast<size_t>(warp) * lay.warp_bytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(area + lay.bar_off);
+    uint64_t* gbars = bars + NS;
+    if (lane == 0) {
+        for (int s = 0; s < NS + 2; s++) mbarrier_init(bars + s, 1);
+        mbarrier_init_fence();
+    }
+    __syncwarp();
+    const PipeWarp w = pipe_partition(offsets, nO, CH, warp);
+    if (w.r0 >= w.r1 || w.nchunks == 0) return;
+    const bool want_a = gA != nullptr, want_b = gB != nullptr;
+    const int64_t rowsize = static_cast<int64_t>(K) * L;
+    const int g_slot_bytes = (lay.g_bytes + 15) / 16 * 16;
+    const bool pair_a = K % 2 == 0 && reinterpret_cast<uintptr_t>(gA) % 8 == 0;
+    const bool pair_b = L % 2 == 0 && reinterpret_cast<uintptr_t>(gB) % 8 == 0;
+
+    int issued = 0;
+    auto issue_next = [&]() {
+        if (issued < w.nchunks) {
+            const int s = issued % NS;
+            pipe_issue_chunk<float, false>(lay, area + s * lay.stage_bytes, bars + s, A, B, nullptr,
+                                           w.e_first + static_cast<int64_t>(issued) * CH, J, 0, lane);
+            issued++;
+        }
+    };
+    auto issue_g = [&](int64_t r) {
+        if (r < w.r1 && lane == 0) {
+            const int slot = static_cast<int>(r - w.r0) & 1;
+            mbarrier_arrive_expect(gbars + slot, static_cast<unsigned>(lay.g_bytes));
+            bulk_copy_in(area + lay.g_off + slot * g_slot_bytes, gO + r * rowsize,
+                         static_cast<unsigned>(lay.g_bytes), gbars + slot);
+        }
+    };
+    issue_g(w.r0);
+    issue_g(w.r0 + 1);
+    for (int i = 0; i < NS - 1; i++) issue_next();
+
+    int64_t wbase = w.r0;
+    auto load_window = [&](int64_t base) {
+        const int64_t i = base + 1 + lane;
+        return offsets[i < nO ? i : nO];
+    };
+    int64_t win = load_window(wbase);
+    auto row_end = [&](int64_t r) -> int64_t {
+        if (r - wbase >= 32) {
+            wbase = r;
+            win = load_window(wbase);
+        }
+        return __shfl_sync(kFullMask, win, static_cast<int>(r - wbase));
+    };
+
+    // gO[r] as the B operand of both products, split into hi and lo:
+    // ga: [k-step over l][tile over k]: b0 = gO[k = 8 nt + g][l = 8 ks + t], b1 = ... l + 4
+    // gb: [k-step over k][tile over l]: b0 = gO[k = 8 ks + t][l = 8 nt + g], b1 = ... k + 4
+    unsigned ga_h[LS][KS][2], ga_l[LS][KS][2], gb_h[KS][LS][2], gb_l[KS][LS][2];
+    bool stalled = false;
+    auto enter_row = [&](int64_t r, bool has_entries) {
+        const int use = static_cast<int>(r - w.r0);
+        if (!mbarrier_wait(gbars + (use & 1), (use >> 1) & 1)) {
+            stalled = true;
+            return;
+        }
+        if (has_entries) {
+            const float* gs = reinterpret_cast<const float*>(area + lay.g_off + (use & 1) * g_slot_bytes);
+#pragma unroll
+            for (int ks = 0; ks < LS; ks++)
+#pragma unroll
+                for (int nt = 0; nt < KS; nt++)
+#pragma unroll
+                    for (int i = 0; i < 2; i++) {
+                        const int k = 8 * nt + g, l = 8 * ks + t + 4 * i;
+                        tf32_split((want_a && k < K && l < L) ? gs[k * L + l] : 0.0f, ga_h[ks][nt][i],
+                                   ga_l[ks][nt][i]);
+                    }
+#pragma unroll
+            for (int ks = 0; ks < KS; ks++)
+#pragma unroll
+                for (int nt = 0; nt < LS; nt++)
+#pragma unroll
+                    for (int i = 0; i < 2; i++) {
+                        const int k = 8 * ks + t + 4 * i, l = 8 * nt + g;
+                        tf32_split((want_b && k < K && l < L) ? gs[k * L + l] : 0.0f, gb_h[ks][nt][i],
+                                   gb_l[ks][nt][i]);
+                    }
+        }
+        __syncwarp();
+        issue_g(r + 2);
+    };
+
+    int64_t e = w.e_begin, row = w.r0;
+    int64_t hi = row_end(row);
+    enter_row(row, hi > e);
+    auto next_rows = [&] {
+        while (row < w.r1 && e == hi && !stalled) {
+            row++;
+            if (row < w.r1) {
+                hi = row_end(row);
+                enter_row(row, hi > e);
+            }
+        }
+    };
+
+    for (int c = 0; c < w.nchunks && !stalled; c++) {
+        issue_next();
+        const int s = c % NS;
+        if (!mbarrier_wait(bars + s, (c / NS) & 1)) {
+            stalled = true;
+            break;
+        }
+        __syncwarp();
+        const unsigned char* stage = area + s * lay.stage_bytes;
+        const float* As = reinterpret_cast<const float*>(stage + lay.a_off);
+        const float* Bs = reinterpret_cast<const float*>(stage + lay.b_off);
+        const int64_t c_lo = w.e_first + static_cast<int64_t>(c) * CH;
+        const int64_t c_hi = c_lo + CH < w.e_last ? c_lo + CH : w.e_last;
+        while (true) {
+            next_rows();
+            if (stalled || row >= w.r1 || e >= c_hi) break;
+            const int64_t seg_end = hi < c_hi ? hi : c_hi;
+            const int first = static_cast<int>(e - c_lo), last = static_cast<int>(seg_end - c_lo);
+            for (int t0 = first; t0 < last; t0 += 16) {
+                const int i0 = t0 + g, i1 = t0 + g + 8; // this lane's two entries (fragment rows)
+                const bool v0 = i0 < last, v1 = i1 < last;
+                const int64_t eg0 = c_lo + i0, eg1 = c_lo + i1;
+                if (want_a) {
+                    float acc[KS][4];
+#pragma unroll
+                    for (int nt = 0; nt < KS; nt++)
+#pragma unroll
+                        for (int i = 0; i < 4; i++) acc[nt][i] = 0.0f;
+#pragma unroll
+                    for (int ks = 0; ks < LS; ks++) {
+                        const int l0 = 8 * ks + t, l1 = l0 + 4;
+                        unsigned bh[4], bl[4];
+                        tf32_split((v0 && l0 < L) ? Bs[i0 * L + l0] : 0.0f, bh[0], bl[0]);
+                        tf32_split((v1 && l0 < L) ? Bs[i1 * L + l0] : 0.0f, bh[1], bl[1]);
+                        tf32_split((v0 && l1 < L) ? Bs[i0 * L + l1] : 0.0f, bh[2], bl[2]);
+                        tf32_split((v1 && l1 < L) ? Bs[i1 * L + l1] : 0.0f, bh[3], bl[3]);
+#pragma unroll
+                        for (int nt = 0; nt < KS; nt++) {
+                            mma_tf32(acc[nt], bl, ga_h[ks][nt]);
+                            mma_tf32(acc[nt], bh, ga_l[ks][nt]);
+                            mma_tf32(acc[nt], bh, ga_h[ks][nt]);
+                        }
+                    }
+                    // acc[nt] = grad_A[entry g (+8)][k = 8 nt + 2 t (+1)]
+#pragma unroll
+                    for (int nt = 0; nt < KS; nt++) {
+                        const int k = 8 * nt + 2 * t;
+#pragma unroll
+                        for (int h = 0; h < 2; h++) {
+                            if (!(h ? v1 : v0) || k >= K) continue;
+                            float* dst = gA + (h ? eg1 : eg0) * K + k;
+                            if (pair_a) {
+                                *reinterpret_cast<float2*>(dst) = make_float2(acc[nt][2 * h], acc[nt][2 * h + 1]);
+                            } else {
+                                dst[0] = acc[nt][2 * h];
+                                if (k + 1 < K) dst[1] = acc[nt][2 * h + 1];
+                            }
+                        }
+                    }
+                }
+                if (want_b) {
+                    float acc[LS][4];
+#pragma unroll
+                    for (int nt = 0; nt < LS; nt++)
+#pragma unroll
+                        for (int i = 0; i < 4; i++) acc[nt][i] = 0.0f;
+#pragma unroll
+                    for (int ks = 0; ks < KS; ks++) {
+                        const int k0 = 8 * ks + t, k1 = k0 + 4;
+                        unsigned ah[4], al[4];
+                        tf32_split((v0 && k0 < K) ? As[i0 * K + k0] : 0.0f, ah[0], al[0]);
+                        tf32_split((v1 && k0 < K) ? As[i1 * K + k0] : 0.0f, ah[1], al[1]);
+                        tf32_split((v0 && k1 < K) ? As[i0 * K + k1] : 0.0f, ah[2], al[2]);
+                        tf32_split((v1 && k1 < K) ? As[i1 * K + k1] : 0.0f, ah[3], al[3]);
+#pragma unroll
+                        for (int nt = 0; nt < LS; nt++) {
+                            mma_tf32(acc[nt], al, gb_h[ks][nt]);
+                            mma_tf32(acc[nt], ah, gb_l[ks][nt]);
+                            mma_tf32(acc[nt], ah, gb_h[ks][nt]);
+                        }
+                    }
+#pragma unroll
+                    for (int nt = 0; nt < LS; nt++) {
+                        const int l = 8 * nt + 2 * t;
+#pragma unroll
+                        for (int h = 0; h < 2; h++) {
+                            if (!(h ? v1 : v0) || l >= L) continue;
+                            float* dst = gB + (h ? eg1 : eg0) * L + l;
+                            if (pair_b) {
+                                *reinterpret_cast<float2*>(dst) = make_float2(acc[nt][2 * h], acc[nt][2 * h + 1]);
+                            } else {
+                                dst[0] = acc[nt][2 * h];
+                                if (l + 1 < L) dst[1] = acc[nt][2 * h + 1];
+                            }
+                        }
+                    }
+                }
+            }
+            e = seg_end;
+        }
+        __syncwarp();
+    }
+    if (stalled) {
+        if (lane == 0) report_stalled(st);
+        return;
+    }
     next_rows();
 }
