@@ -527,7 +527,7 @@ template <typename T, bool WEIGHTED> PipeLayout choose_pipe_layout(int K, int L,
     // already keeps about 100 KB per SM in flight. With weights a stage also holds the padded
     // B and W rows (680 bytes per entry), so chunks of 8 keep the warp count up (forward
     // 0.59 ms, VJP 1.12 ms against 0.92 / 1.63 with chunks of 32).
-    int ch = env_int("MOPS_B200_PIPE_CH", WEIGHTED ? 8 : 32);
+    int ch = env_int("MOPS_B200_PIPE_CH", WEIGHTED ? 8 : sizeof(T) == 4 ? 64 : 32);
     int stages = env_int("MOPS_B200_PIPE_STAGES", 2);
     ch = std::max(4, std::min(WEIGHTED ? 32 : 128, ch / 4 * 4)); // weighted: one lane per entry
     stages = std::max(2, std::min(8, stages));

@@ -23,7 +23,8 @@ struct PipeLayout {
     int row_pieces;      // weighted: 16-byte pieces of one B / W row
     int row_pieces_log2; // its log2 when it is a power of two, else -1
     int ch;       // entries per chunk: a multiple of 4 (at most 32 with weights: a lane per entry)
-    int stages;   // chunks in flight per warp + 1
+    int stages;   // chunks in flight per warp + 1: a power of two
+    int stages_log2;
     int a_off, b_off, w_off, pw_off; // byte offsets inside a stage (16-byte aligned)
     int stage_bytes;
     int g_off;    // grad_output ring (VJP): two rows of g_bytes each; unused in the forward
@@ -40,7 +41,9 @@ inline PipeLayout pipe_layout(size_t s, int K, int L, bool weighted, bool vjp, i
     PipeLayout p{};
     p.K = K, p.L = L;
     p.LP = weighted ? L + 4 : L;
-    p.ch = ch, p.stages = stages;
+    p.ch = ch;
+    p.stages_log2 = stages >= 8 ? 3 : stages >= 4 ? 2 : 1;
+    p.stages = 1 << p.stages_log2;
     p.row_pieces = static_cast<int>(L * s / 16);
     p.row_pieces_log2 = -1;
     for (int b = 0; b < 6; b++)
@@ -51,9 +54,9 @@ inline PipeLayout pipe_layout(size_t s, int K, int L, bool weighted, bool vjp, i
     p.pw_off = weighted ? p.w_off + round16(static_cast<size_t>(ch) * p.LP * s) : p.w_off;
     p.stage_bytes = weighted ? p.pw_off + round16(static_cast<size_t>(ch) * 4) : p.pw_off;
     p.g_bytes = static_cast<int>(static_cast<size_t>(K) * L * s);
-    p.g_off = stages * p.stage_bytes;
+    p.g_off = p.stages * p.stage_bytes;
     p.bar_off = p.g_off + (vjp ? 2 * round16(p.g_bytes) : 0);
-    p.warp_bytes = (p.bar_off + 8 * (stages + 2) + 127) / 128 * 128;
+    p.warp_bytes = (p.bar_off + 8 * (p.stages + 2) + 127) / 128 * 128;
     return p;
 }
 
@@ -84,12 +87,27 @@ __device__ __forceinline__ void pipe_issue_chunk(const PipeLayout& lay, unsigned
         if (lane < n) pws[lane] = pw_lane;
         __syncwarp();
         constexpr int kPer = 16 / static_cast<int>(sizeof(S)); // scalars per piece
-        const int pieces = n * lay.row_pieces;
-        for (int i = lane; i < pieces; i += 32) {
-            const int r = lay.row_pieces_log2 >= 0 ? i >> lay.row_pieces_log2 : i / lay.row_pieces;
-            const int c = (i - r * lay.row_pieces) * kPer;
-            lane_copy16(Bs + r * lay.LP + c, B + (e0 + r) * L + c);
-            lane_copy16(Ws + r * lay.LP + c, W + static_cast<int64_t>(pws[r]) * L + c);
+        if (lay.row_pieces_log2 >= 0 && lay.row_pieces <= 32) {
+            // a lane keeps its piece column and walks down the rows, 32 / row_pieces at a time
+            const int per_round = 32 >> lay.row_pieces_log2;
+            const int c = (lane & (lay.row_pieces - 1)) * kPer;
+            int r = lane >> lay.row_pieces_log2;
+            S* bd = Bs + r * lay.LP + c;
+            S* wd = Ws + r * lay.LP + c;
+            const S* bsrc = B + (e0 + r) * L + c;
+            for (; r < n; r += per_round) {
+                lane_copy16(bd, bsrc);
+                lane_copy16(wd, W + static_cast<int64_t>(pws[r]) * L + c);
+                bd += per_round * lay.LP, wd += per_round * lay.LP, bsrc += per_round * L;
+            }
+        } else {
+            const int pieces = n * lay.row_pieces;
+            for (int i = lane; i < pieces; i += 32) {
+                const int r = i / lay.row_pieces;
+                const int c = (i - r * lay.row_pieces) * kPer;
+                lane_copy16(Bs + r * lay.LP + c, B + (e0 + r) * L + c);
+                lane_copy16(Ws + r * lay.LP + c, W + static_cast<int64_t>(pws[r]) * L + c);
+            }
         }
         lane_copies_arrive(bar);
     }
@@ -164,7 +182,7 @@ opsa_fwd_pipe(S* __restrict__ O, const S* __restrict__ A, const S* __restrict__ 
     int32_t pw_reg = load_pw(0);
     auto issue_next = [&]() {
         if (issued < w.nchunks) {
-            const int s = issued % NS;
+            const int s = issued & (NS - 1);
             pipe_issue_chunk<S, WEIGHTED>(lay, area + s * lay.stage_bytes, bars + s, A, B, W,
                                           w.e_first + static_cast<int64_t>(issued) * CH, J, pw_reg,
                                           lane);
@@ -223,22 +241,32 @@ opsa_fwd_pipe(S* __restrict__ O, const S* __restrict__ A, const S* __restrict__ 
     };
 
     clear();
-    int64_t e = w.e_begin, row = w.r0;
-    int64_t hi = row_end(row);
+    // positions of entries below are relative to e_first (the warp's range fits an int)
+    int64_t row = w.r0;
+    int e = static_cast<int>(w.e_begin - w.e_first);
+    const int e_stop = static_cast<int>(w.e_last - w.e_first);
+    int hi = static_cast<int>(row_end(row) - w.e_first);
     // Rows whose last entry has been consumed (and rows without entries) are written out.
     auto finish_rows = [&] {
         while (row < w.r1 && e == hi) {
             flush(row);
             clear();
             row++;
-            if (row < w.r1) hi = row_end(row);
+            if (row < w.r1) hi = static_cast<int>(row_end(row) - w.e_first);
         }
     };
+    // which fragment rows (k) and columns (l) of this lane exist
+    bool ka[MT], la[NT];
+#pragma unroll
+    for (int mt = 0; mt < MT; mt++) ka[mt] = 8 * mt + qr < K;
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) la[nt] = 8 * nt + qr < L;
 
-    for (int c = 0; c < w.nchunks; c++) {
+    int c_lo = 0;
+    for (int c = 0; c < w.nchunks; c++, c_lo += CH) {
         issue_next(); // into the stage that the previous iteration released
-        const int s = c % NS;
-        if (!mbarrier_wait(bars + s, (c / NS) & 1)) {
+        const int s = c & (NS - 1);
+        if (!mbarrier_wait(bars + s, (c >> lay.stages_log2) & 1)) {
             if (lane == 0) report_stalled(st);
             return;
         }
@@ -247,38 +275,42 @@ opsa_fwd_pipe(S* __restrict__ O, const S* __restrict__ A, const S* __restrict__ 
         const S* As = reinterpret_cast<const S*>(stage + lay.a_off);
         const S* Bs = reinterpret_cast<const S*>(stage + lay.b_off);
         const S* Ws = reinterpret_cast<const S*>(stage + lay.w_off);
-        const int64_t c_lo = w.e_first + static_cast<int64_t>(c) * CH;
-        const int64_t c_hi = c_lo + CH < w.e_last ? c_lo + CH : w.e_last;
+        const int c_hi = c_lo + CH < e_stop ? c_lo + CH : e_stop;
         while (true) {
             finish_rows();
             if (row >= w.r1 || e >= c_hi) break;
-            const int64_t seg_end = hi < c_hi ? hi : c_hi;
+            const int seg_end = hi < c_hi ? hi : c_hi;
             // entries [e, seg_end) of the current row, four per MMA step: fragment
-            // A^T[k = 8 mt + qr][entry qc], (B*W)[entry qc][l = 8 nt + qr]
-            const int first = static_cast<int>(e - c_lo), last = static_cast<int>(seg_end - c_lo);
-#pragma unroll 2
-            for (int s0 = first; s0 < last; s0 += 4) {
+            // A^T[k = 8 mt + qr][entry qc], (B*W)[entry qc][l = 8 nt + qr]. Whole steps need no
+            // test per entry, the last one of a segment may.
+            const int first = e - c_lo, last = seg_end - c_lo;
+            auto step = [&](int s0, auto ragged) {
+                constexpr bool kRagged = decltype(ragged)::value;
                 const int idx = s0 + qc;
-                const bool valid = idx < last;
+                const bool valid = !kRagged || idx < last;
+                const S* ap = As + idx * K + qr;
+                const S* bp = Bs + idx * LP + qr;
+                const S* wp = Ws + idx * LP + qr;
                 T af[MT], bf[NT];
 #pragma unroll
-                for (int mt = 0; mt < MT; mt++) {
-                    const int k = 8 * mt + qr;
-                    af[mt] = (valid && k < K) ? static_cast<T>(As[idx * K + k]) : T(0);
-                }
+                for (int mt = 0; mt < MT; mt++)
+                    af[mt] = (valid && ka[mt]) ? static_cast<T>(ap[8 * mt]) : T(0);
 #pragma unroll
                 for (int nt = 0; nt < NT; nt++) {
-                    const int l = 8 * nt + qr;
-                    const bool in = valid && l < L;
-                    T v = in ? static_cast<T>(Bs[idx * LP + l]) : T(0);
-                    if (WEIGHTED && in) v *= static_cast<T>(Ws[idx * LP + l]);
+                    const bool in = valid && la[nt];
+                    T v = in ? static_cast<T>(bp[8 * nt]) : T(0);
+                    if (WEIGHTED && in) v *= static_cast<T>(wp[8 * nt]);
                     bf[nt] = v;
                 }
 #pragma unroll
                 for (int mt = 0; mt < MT; mt++)
 #pragma unroll
                     for (int nt = 0; nt < NT; nt++) dmma(acc[mt][nt], af[mt], bf[nt]);
-            }
+            };
+            int s0 = first;
+#pragma unroll 2
+            for (; s0 + 4 <= last; s0 += 4) step(s0, std::false_type{});
+            if (s0 < last) step(s0, std::true_type{});
             e = seg_end;
         }
         __syncwarp(); // the stage may be refilled by the copies issued next
@@ -341,7 +373,7 @@ opsa_vjp_pipe(S* __restrict__ gA, S* __restrict__ gB, S* __restrict__ gW,
     int32_t pw_reg = load_pw(0);
     auto issue_next = [&]() {
         if (issued < w.nchunks) {
-            const int s = issued % NS;
+            const int s = issued & (NS - 1);
             pipe_issue_chunk<S, WEIGHTED>(lay, area + s * lay.stage_bytes, bars + s, A, B, W,
                                           w.e_first + static_cast<int64_t>(issued) * CH, J, pw_reg,
                                           lane);
@@ -409,23 +441,27 @@ opsa_vjp_pipe(S* __restrict__ gA, S* __restrict__ gB, S* __restrict__ gW,
         issue_g(r + 2);
     };
 
-    int64_t e = w.e_begin, row = w.r0;
-    int64_t hi = row_end(row);
+    // positions of entries below are relative to e_first (the warp's range fits an int)
+    int64_t row = w.r0;
+    int e = static_cast<int>(w.e_begin - w.e_first);
+    const int e_stop = static_cast<int>(w.e_last - w.e_first);
+    int hi = static_cast<int>(row_end(row) - w.e_first);
     enter_row(row, hi > e);
     auto next_rows = [&] {
         while (row < w.r1 && e == hi && !stalled) {
             row++;
             if (row < w.r1) {
-                hi = row_end(row);
+                hi = static_cast<int>(row_end(row) - w.e_first);
                 enter_row(row, hi > e);
             }
         }
     };
 
-    for (int c = 0; c < w.nchunks && !stalled; c++) {
+    int c_lo = 0;
+    for (int c = 0; c < w.nchunks && !stalled; c++, c_lo += CH) {
         issue_next();
-        const int s = c % NS;
-        if (!mbarrier_wait(bars + s, (c / NS) & 1)) {
+        const int s = c & (NS - 1);
+        if (!mbarrier_wait(bars + s, (c >> lay.stages_log2) & 1)) {
             stalled = true;
             break;
         }
@@ -435,28 +471,33 @@ opsa_vjp_pipe(S* __restrict__ gA, S* __restrict__ gB, S* __restrict__ gW,
         const S* Bs = reinterpret_cast<const S*>(stage + lay.b_off);
         const S* Ws = reinterpret_cast<const S*>(stage + lay.w_off);
         const int32_t* pws = reinterpret_cast<const int32_t*>(stage + lay.pw_off);
-        const int64_t c_lo = w.e_first + static_cast<int64_t>(c) * CH;
-        const int64_t c_hi = c_lo + CH < w.e_last ? c_lo + CH : w.e_last;
+        const int c_hi = c_lo + CH < e_stop ? c_lo + CH : e_stop;
         while (true) {
             next_rows();
             if (stalled || row >= w.r1 || e >= c_hi) break;
-            const int64_t seg_end = hi < c_hi ? hi : c_hi;
-            const int first = static_cast<int>(e - c_lo), last = static_cast<int>(seg_end - c_lo);
-            for (int t0 = first; t0 < last; t0 += 8) {
+            const int seg_end = hi < c_hi ? hi : c_hi;
+            const int first = e - c_lo, last = seg_end - c_lo;
+            // eight entries per tile: whole tiles need no test per entry, the last one may
+            auto tile = [&](int t0, auto ragged) {
+                constexpr bool kRagged = decltype(ragged)::value;
                 const int idx = t0 + qr; // this lane's entry of the tile, within the chunk
-                const bool valid = idx < last;
-                const int64_t eg = c_lo + idx;
+                const bool valid = !kRagged || idx < last;
+                const int64_t eg = w.e_first + c_lo + idx;
+                const S* brow = Bs + idx * LP;
+                const S* wrow_s = Ws + idx * LP;
                 if (want_a) {
                     // grad_A[entry qr][k = 8 nt + 2 qc + {0,1}] = sum_l (B*W)[entry][l] gO[k][l]
                     T bf[KSL];
+                    const S* bp = brow + qc;
+                    const S* wp = wrow_s + qc;
 #pragma unroll
                     for (int ks = 0; ks < KSL; ks++) {
-                        const int l = 4 * ks + qc;
-                        const bool in = valid && l < L;
-                        T v = in ? static_cast<T>(Bs[idx * LP + l]) : T(0);
-                        if (WEIGHTED && in) v *= static_cast<T>(Ws[idx * LP + l]);
+                        const bool in = valid && 4 * ks + qc < L;
+                        T v = in ? static_cast<T>(bp[4 * ks]) : T(0);
+                        if (WEIGHTED && in) v *= static_cast<T>(wp[4 * ks]);
                         bf[ks] = v;
                     }
+                    S* dst = gA + eg * K + 2 * qc;
 #pragma unroll
                     for (int nt = 0; nt < NTK; nt++) {
                         T cfrag[2];
@@ -464,20 +505,22 @@ opsa_vjp_pipe(S* __restrict__ gA, S* __restrict__ gB, S* __restrict__ gW,
 #pragma unroll
                         for (int ks = 1; ks < KSL; ks++) dmma(cfrag, bf[ks], ga_k[nt][ks]);
                         const int k = 8 * nt + 2 * qc;
-                        S* dst = gA + eg * K + k;
-                        if (valid && k < K) dst[0] = static_cast<S>(cfrag[0]);
-                        if (valid && k + 1 < K) dst[1] = static_cast<S>(cfrag[1]);
+                        if (valid && k < K) dst[8 * nt] = static_cast<S>(cfrag[0]);
+                        if (valid && k + 1 < K) dst[8 * nt + 1] = static_cast<S>(cfrag[1]);
                     }
                 }
                 if (want_b) {
                     // X[entry qr][l = 8 nt + 2 qc + {0,1}] = sum_k A[entry][k] gO[k][l]
                     T af[KSK];
+                    const S* ap = As + idx * K + qc;
 #pragma unroll
-                    for (int ks = 0; ks < KSK; ks++) {
-                        const int k = 4 * ks + qc;
-                        af[ks] = (valid && k < K) ? static_cast<T>(As[idx * K + k]) : T(0);
-                    }
+                    for (int ks = 0; ks < KSK; ks++)
+                        af[ks] = (valid && 4 * ks + qc < K) ? static_cast<T>(ap[4 * ks]) : T(0);
                     const int32_t wrow = (WEIGHTED && valid) ? pws[idx] : 0;
+                    const S* wp = wrow_s + 2 * qc;
+                    const S* bp = brow + 2 * qc;
+                    S* gw = WEIGHTED && gW != nullptr ? gW + static_cast<int64_t>(wrow) * L + 2 * qc : nullptr;
+                    S* dst = gB != nullptr ? gB + eg * L + 2 * qc : nullptr;
 #pragma unroll
                     for (int nt = 0; nt < NTL; nt++) {
                         T cfrag[2];
@@ -488,33 +531,39 @@ opsa_vjp_pipe(S* __restrict__ gA, S* __restrict__ gB, S* __restrict__ gW,
                         if (!valid || l >= L) continue;
                         const bool two = l + 1 < L;
                         if (WEIGHTED) {
-                            const S* wp = Ws + idx * LP + l;
-                            const S* bp = Bs + idx * LP + l;
-                            const T w0 = wp[0], b0 = bp[0];
-                            const T w1 = two ? static_cast<T>(wp[1]) : T(0);
-                            const T b1 = two ? static_cast<T>(bp[1]) : T(0);
-                            if (gW != nullptr) {
-                                S* gw = gW + static_cast<int64_t>(wrow) * L + l;
-                                red_add(gw, static_cast<S>(cfrag[0] * b0));
-                                if (two) red_add(gw + 1, static_cast<S>(cfrag[1] * b1));
+                            T w0, w1, b0, b1;
+                            if (pair_ok) { // L even: both columns exist, 16-byte aligned pairs
+                                const S2 w2 = *reinterpret_cast<const S2*>(wp + 8 * nt);
+                                const S2 b2 = *reinterpret_cast<const S2*>(bp + 8 * nt);
+                                w0 = w2.x, w1 = w2.y, b0 = b2.x, b1 = b2.y;
+                            } else {
+                                w0 = wp[8 * nt], b0 = bp[8 * nt];
+                                w1 = two ? static_cast<T>(wp[8 * nt + 1]) : T(0);
+                                b1 = two ? static_cast<T>(bp[8 * nt + 1]) : T(0);
+                            }
+                            if (gw != nullptr) {
+                                red_add(gw + 8 * nt, static_cast<S>(cfrag[0] * b0));
+                                if (two) red_add(gw + 8 * nt + 1, static_cast<S>(cfrag[1] * b1));
                             }
                             cfrag[0] *= w0;
                             cfrag[1] *= w1;
                         }
-                        if (gB != nullptr) {
-                            S* dst = gB + eg * L + l;
+                        if (dst != nullptr) {
                             if (pair_ok) {
                                 S2 v2;
                                 v2.x = static_cast<S>(cfrag[0]), v2.y = static_cast<S>(cfrag[1]);
-                                *reinterpret_cast<S2*>(dst) = v2;
+                                *reinterpret_cast<S2*>(dst + 8 * nt) = v2;
                             } else {
-                                dst[0] = static_cast<S>(cfrag[0]);
-                                if (two) dst[1] = static_cast<S>(cfrag[1]);
+                                dst[8 * nt] = static_cast<S>(cfrag[0]);
+                                if (two) dst[8 * nt + 1] = static_cast<S>(cfrag[1]);
                             }
                         }
                     }
                 }
-            }
+            };
+            int t0 = first;
+            for (; t0 + 8 <= last; t0 += 8) tile(t0, std::false_type{});
+            if (t0 < last) tile(t0, std::true_type{});
             e = seg_end;
         }
         __syncwarp(); // the stage may be refilled by the copies issued next
@@ -532,18 +581,21 @@ opsa_vjp_pipe(S* __restrict__ gA, S* __restrict__ gB, S* __restrict__ gW,
 // For f32 operands the FP64 MMA route above is bound by the FP64 tensor pipe (63 % busy at
 // 57 % of the HBM peak): f32 moves half the bytes but needs the same number of FP64 MMAs. The
 // kernels below run the same streaming structure on mma.sync m16n8k8 TF32 with the
-// three-product split: every f32 operand x is taken as hi + lo with hi = tf32(x), lo =
-// tf32(x - hi), and a product a*b as a_hi*b_hi + a_hi*b_lo + a_lo*b_hi (the dropped a_lo*b_lo
-// is below 2^-22 |ab|), accumulated in f32. The result is f32-accurate (the parity tests hold
+// three-product split: every f32 operand x is taken as hi + lo with hi = the TF32 part of x,
+// lo = the TF32 part of x - hi, and a product a*b as a_hi*b_hi + a_hi*b_lo + a_lo*b_hi (the
+// dropped a_lo*b_lo is below 2^-20 |ab|), accumulated in f32. The result is f32-accurate (the parity tests hold
 // it to 1e-5 of the largest output, like every f32 path). In the forward, where one output
 // row sums over arbitrarily many entries, only the small correction products are chained
 // through the tensor core's accumulator (which may round towards zero); the main products of
 // every 8-entry step start from zero and are added to the running sums by ordinary f32
 // additions.
 __device__ __forceinline__ void tf32_split(float x, unsigned& hi, unsigned& lo) {
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(x));
-    const float rest = x - __uint_as_float(hi);
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo) : "f"(rest));
+    // hi = the upper 19 bits of x (what the tensor core reads of an f32 register anyway), lo =
+    // x - hi, exact in f32, of which the tensor core again reads the upper 19 bits. Dropping
+    // bits instead of rounding (cvt.rna.tf32.f32, about five instructions here) leaves
+    // |x - hi - lo'| < 2^-20 |x|, well inside the f32 tolerance, at two instructions.
+    hi = __float_as_uint(x) & 0xffffe000u;
+    lo = __float_as_uint(x - __uint_as_float(hi));
 }
 
 // d += a b for one m16n8k8 tile. Fragments (g = lane / 4, t = lane % 4):
@@ -582,7 +634,7 @@ opsa_fwd_pipe_tf32(float* __restrict__ O, const float* __restrict__ A, const flo
     int issued = 0;
     auto issue_next = [&]() {
         if (issued < w.nchunks) {
-            const int s = issued % NS;
+            const int s = issued & (NS - 1);
             pipe_issue_chunk<float, false>(lay, area + s * lay.stage_bytes, bars + s, A, B, nullptr,
                                            w.e_first + static_cast<int64_t>(issued) * CH, J, 0, lane);
             issued++;
@@ -613,6 +665,7 @@ opsa_fwd_pipe_tf32(float* __restrict__ O, const float* __restrict__ A, const flo
     };
     const int64_t rowsize = static_cast<int64_t>(K) * L;
     const bool pair_ok = L % 2 == 0 && reinterpret_cast<uintptr_t>(O) % 8 == 0;
+    const bool ka0 = g < K, ka1 = g + 8 < K; // which of the lane's two A^T rows exist
     // element (nt, 2 h + i) is O[r, k = g + 8 h, l = 8 nt + 2 t + i]
     auto flush = [&](int64_t r) {
         float* dst = O + r * rowsize;
@@ -651,8 +704,8 @@ opsa_fwd_pipe_tf32(float* __restrict__ O, const float* __restrict__ A, const flo
 
     for (int c = 0; c < w.nchunks; c++) {
         issue_next();
-        const int s = c % NS;
-        if (!mbarrier_wait(bars + s, (c / NS) & 1)) {
+        const int s = c & (NS - 1);
+        if (!mbarrier_wait(bars + s, (c >> lay.stages_log2) & 1)) {
             if (lane == 0) report_stalled(st);
             return;
         }
@@ -667,21 +720,27 @@ opsa_fwd_pipe_tf32(float* __restrict__ O, const float* __restrict__ A, const flo
             if (row >= w.r1 || e >= c_hi) break;
             const int64_t seg_end = hi < c_hi ? hi : c_hi;
             const int first = static_cast<int>(e - c_lo), last = static_cast<int>(seg_end - c_lo);
-            for (int s0 = first; s0 < last; s0 += 8) {
-                // A^T fragment: (row k, column entry); B fragment: (row entry, column l)
-                const int e0 = s0 + t, e1 = s0 + t + 4;
-                const bool v0 = e0 < last, v1 = e1 < last;
+            // A^T fragment: (row k, column entry); B fragment: (row entry, column l). Whole
+            // steps of eight entries need no per-entry test; the last, ragged one does.
+            auto step = [&](int s0, auto ragged) {
+                constexpr bool kRagged = decltype(ragged)::value;
+                const int e0 = s0 + t, e1 = e0 + 4;
+                const bool v0 = !kRagged || e0 < last, v1 = !kRagged || e1 < last;
+                const float* a0 = As + e0 * K + g;
+                const float* a1 = As + e1 * K + g;
                 unsigned ah[4], al[4];
-                tf32_split((v0 && g < K) ? As[e0 * K + g] : 0.0f, ah[0], al[0]);
-                tf32_split((v0 && g + 8 < K) ? As[e0 * K + g + 8] : 0.0f, ah[1], al[1]);
-                tf32_split((v1 && g < K) ? As[e1 * K + g] : 0.0f, ah[2], al[2]);
-                tf32_split((v1 && g + 8 < K) ? As[e1 * K + g + 8] : 0.0f, ah[3], al[3]);
+                tf32_split((v0 && ka0) ? a0[0] : 0.0f, ah[0], al[0]);
+                tf32_split((v0 && ka1) ? a0[8] : 0.0f, ah[1], al[1]);
+                tf32_split((v1 && ka0) ? a1[0] : 0.0f, ah[2], al[2]);
+                tf32_split((v1 && ka1) ? a1[8] : 0.0f, ah[3], al[3]);
+                const float* b0 = Bs + e0 * L + g;
+                const float* b1 = Bs + e1 * L + g;
 #pragma unroll
                 for (int nt = 0; nt < NT; nt++) {
-                    const int l = 8 * nt + g;
+                    const bool lb = 8 * nt + g < L;
                     unsigned bh[2], bl[2];
-                    tf32_split((v0 && l < L) ? Bs[e0 * L + l] : 0.0f, bh[0], bl[0]);
-                    tf32_split((v1 && l < L) ? Bs[e1 * L + l] : 0.0f, bh[1], bl[1]);
+                    tf32_split((v0 && lb) ? b0[8 * nt] : 0.0f, bh[0], bl[0]);
+                    tf32_split((v1 && lb) ? b1[8 * nt] : 0.0f, bh[1], bl[1]);
                     float main_[4] = {0.0f, 0.0f, 0.0f, 0.0f};
                     mma_tf32(main_, ah, bh);
                     mma_tf32(corr[nt], ah, bl);
@@ -689,7 +748,10 @@ opsa_fwd_pipe_tf32(float* __restrict__ O, const float* __restrict__ A, const flo
 #pragma unroll
                     for (int i = 0; i < 4; i++) sum[nt][i] += main_[i];
                 }
-            }
+            };
+            int s0 = first;
+            for (; s0 + 8 <= last; s0 += 8) step(s0, std::false_type{});
+            if (s0 < last) step(s0, std::true_type{});
             e = seg_end;
         }
         __syncwarp();
@@ -732,7 +794,7 @@ opsa_vjp_pipe_tf32(float* __restrict__ gA, float* __restrict__ gB, const float* 
     int issued = 0;
     auto issue_next = [&]() {
         if (issued < w.nchunks) {
-            const int s = issued % NS;
+            const int s = issued & (NS - 1);
             pipe_issue_chunk<float, false>(lay, area + s * lay.stage_bytes, bars + s, A, B, nullptr,
                                            w.e_first + static_cast<int64_t>(issued) * CH, J, 0, lane);
             issued++;
@@ -817,8 +879,8 @@ opsa_vjp_pipe_tf32(float* __restrict__ gA, float* __restrict__ gB, const float* 
 
     for (int c = 0; c < w.nchunks && !stalled; c++) {
         issue_next();
-        const int s = c % NS;
-        if (!mbarrier_wait(bars + s, (c / NS) & 1)) {
+        const int s = c & (NS - 1);
+        if (!mbarrier_wait(bars + s, (c >> lay.stages_log2) & 1)) {
             stalled = true;
             break;
         }
@@ -833,24 +895,28 @@ opsa_vjp_pipe_tf32(float* __restrict__ gA, float* __restrict__ gB, const float* 
             if (stalled || row >= w.r1 || e >= c_hi) break;
             const int64_t seg_end = hi < c_hi ? hi : c_hi;
             const int first = static_cast<int>(e - c_lo), last = static_cast<int>(seg_end - c_lo);
-            for (int t0 = first; t0 < last; t0 += 16) {
-                const int i0 = t0 + g, i1 = t0 + g + 8; // this lane's two entries (fragment rows)
-                const bool v0 = i0 < last, v1 = i1 < last;
-                const int64_t eg0 = c_lo + i0, eg1 = c_lo + i1;
+            // sixteen entries per tile; whole tiles need no per-entry test, the last one does
+            auto tile = [&](int t0, auto ragged) {
+                constexpr bool kRagged = decltype(ragged)::value;
+                const int i0 = t0 + g, i1 = i0 + 8; // this lane's two entries (fragment rows)
+                const bool v0 = !kRagged || i0 < last, v1 = !kRagged || i1 < last;
+                const int64_t eg0 = c_lo + i0;
                 if (want_a) {
                     float acc[KS][4];
 #pragma unroll
                     for (int nt = 0; nt < KS; nt++)
 #pragma unroll
                         for (int i = 0; i < 4; i++) acc[nt][i] = 0.0f;
+                    const float* b0 = Bs + i0 * L + t;
+                    const float* b1 = b0 + 8 * L;
 #pragma unroll
                     for (int ks = 0; ks < LS; ks++) {
-                        const int l0 = 8 * ks + t, l1 = l0 + 4;
+                        const bool c0 = 8 * ks + t < L, c1 = 8 * ks + t + 4 < L;
                         unsigned bh[4], bl[4];
-                        tf32_split((v0 && l0 < L) ? Bs[i0 * L + l0] : 0.0f, bh[0], bl[0]);
-                        tf32_split((v1 && l0 < L) ? Bs[i1 * L + l0] : 0.0f, bh[1], bl[1]);
-                        tf32_split((v0 && l1 < L) ? Bs[i0 * L + l1] : 0.0f, bh[2], bl[2]);
-                        tf32_split((v1 && l1 < L) ? Bs[i1 * L + l1] : 0.0f, bh[3], bl[3]);
+                        tf32_split((v0 && c0) ? b0[8 * ks] : 0.0f, bh[0], bl[0]);
+                        tf32_split((v1 && c0) ? b1[8 * ks] : 0.0f, bh[1], bl[1]);
+                        tf32_split((v0 && c1) ? b0[8 * ks + 4] : 0.0f, bh[2], bl[2]);
+                        tf32_split((v1 && c1) ? b1[8 * ks + 4] : 0.0f, bh[3], bl[3]);
 #pragma unroll
                         for (int nt = 0; nt < KS; nt++) {
                             mma_tf32(acc[nt], bl, ga_h[ks][nt]);
@@ -859,18 +925,19 @@ opsa_vjp_pipe_tf32(float* __restrict__ gA, float* __restrict__ gB, const float* 
                         }
                     }
                     // acc[nt] = grad_A[entry g (+8)][k = 8 nt + 2 t (+1)]
+                    float* dst = gA + eg0 * K + 2 * t;
 #pragma unroll
                     for (int nt = 0; nt < KS; nt++) {
                         const int k = 8 * nt + 2 * t;
 #pragma unroll
                         for (int h = 0; h < 2; h++) {
                             if (!(h ? v1 : v0) || k >= K) continue;
-                            float* dst = gA + (h ? eg1 : eg0) * K + k;
+                            float* d2 = dst + h * 8 * K + 8 * nt;
                             if (pair_a) {
-                                *reinterpret_cast<float2*>(dst) = make_float2(acc[nt][2 * h], acc[nt][2 * h + 1]);
+                                *reinterpret_cast<float2*>(d2) = make_float2(acc[nt][2 * h], acc[nt][2 * h + 1]);
                             } else {
-                                dst[0] = acc[nt][2 * h];
-                                if (k + 1 < K) dst[1] = acc[nt][2 * h + 1];
+                                d2[0] = acc[nt][2 * h];
+                                if (k + 1 < K) d2[1] = acc[nt][2 * h + 1];
                             }
                         }
                     }
@@ -881,14 +948,16 @@ opsa_vjp_pipe_tf32(float* __restrict__ gA, float* __restrict__ gB, const float* 
                     for (int nt = 0; nt < LS; nt++)
 #pragma unroll
                         for (int i = 0; i < 4; i++) acc[nt][i] = 0.0f;
+                    const float* a0 = As + i0 * K + t;
+                    const float* a1 = a0 + 8 * K;
 #pragma unroll
                     for (int ks = 0; ks < KS; ks++) {
-                        const int k0 = 8 * ks + t, k1 = k0 + 4;
+                        const bool c0 = 8 * ks + t < K, c1 = 8 * ks + t + 4 < K;
                         unsigned ah[4], al[4];
-                        tf32_split((v0 && k0 < K) ? As[i0 * K + k0] : 0.0f, ah[0], al[0]);
-                        tf32_split((v1 && k0 < K) ? As[i1 * K + k0] : 0.0f, ah[1], al[1]);
-                        tf32_split((v0 && k1 < K) ? As[i0 * K + k1] : 0.0f, ah[2], al[2]);
-                        tf32_split((v1 && k1 < K) ? As[i1 * K + k1] : 0.0f, ah[3], al[3]);
+                        tf32_split((v0 && c0) ? a0[8 * ks] : 0.0f, ah[0], al[0]);
+                        tf32_split((v1 && c0) ? a1[8 * ks] : 0.0f, ah[1], al[1]);
+                        tf32_split((v0 && c1) ? a0[8 * ks + 4] : 0.0f, ah[2], al[2]);
+                        tf32_split((v1 && c1) ? a1[8 * ks + 4] : 0.0f, ah[3], al[3]);
 #pragma unroll
                         for (int nt = 0; nt < LS; nt++) {
                             mma_tf32(acc[nt], al, gb_h[ks][nt]);
@@ -896,23 +965,27 @@ opsa_vjp_pipe_tf32(float* __restrict__ gA, float* __restrict__ gB, const float* 
                             mma_tf32(acc[nt], ah, gb_h[ks][nt]);
                         }
                     }
+                    float* dst = gB + eg0 * L + 2 * t;
 #pragma unroll
                     for (int nt = 0; nt < LS; nt++) {
                         const int l = 8 * nt + 2 * t;
 #pragma unroll
                         for (int h = 0; h < 2; h++) {
                             if (!(h ? v1 : v0) || l >= L) continue;
-                            float* dst = gB + (h ? eg1 : eg0) * L + l;
+                            float* d2 = dst + h * 8 * L + 8 * nt;
                             if (pair_b) {
-                                *reinterpret_cast<float2*>(dst) = make_float2(acc[nt][2 * h], acc[nt][2 * h + 1]);
+                                *reinterpret_cast<float2*>(d2) = make_float2(acc[nt][2 * h], acc[nt][2 * h + 1]);
                             } else {
-                                dst[0] = acc[nt][2 * h];
-                                if (l + 1 < L) dst[1] = acc[nt][2 * h + 1];
+                                d2[0] = acc[nt][2 * h];
+                                if (l + 1 < L) d2[1] = acc[nt][2 * h + 1];
                             }
                         }
                     }
                 }
-            }
+            };
+            int t0 = first;
+            for (; t0 + 16 <= last; t0 += 16) tile(t0, std::false_type{});
+            if (t0 < last) tile(t0, std::true_type{});
             e = seg_end;
         }
         __syncwarp();
