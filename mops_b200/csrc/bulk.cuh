@@ -80,12 +80,6 @@ __device__ __forceinline__ void lane_copy16(void* smem_dst, const void* global_s
                  : "memory");
 }
 
-// The same with the destination given as a shared-memory address.
-__device__ __forceinline__ void lane_copy16_to(unsigned smem_dst, const void* global_src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_dst), "l"(global_src)
-                 : "memory");
-}
-
 // The calling lane arrives on `bar` once all the lane copies it has issued so far are complete.
 // The barrier's arrival count must include this arrival (it does not raise the pending count).
 __device__ __forceinline__ void lane_copies_arrive(uint64_t* bar) {

@@ -69,7 +69,6 @@ template <typename T, int N> __device__ __forceinline__ void store_vec(T* p, con
 }
 
 #include "opsa_pipe.cuh"
-#include "opsaw_team.cuh"
 
 // ------------------------------------------------------------------------------ forward
 struct FwdPlan {
@@ -535,69 +534,16 @@ template <typename T, bool WEIGHTED> PipeLayout choose_pipe_layout(int K, int L,
     return pipe_layout(sizeof(T), K, L, WEIGHTED, vjp, ch, stages);
 }
 
-// Blocks that fill the GPU once (what the occupancy of `kernel` allows), at most one per
-// `rows_per_block` output rows.
 template <typename Kernel>
-unsigned resident_grid(const Call& call, Kernel kernel, int threads, size_t smem, int64_t nO,
-                       int rows_per_block) {
+unsigned pipe_grid(const Call& call, Kernel kernel, size_t smem, int64_t nO) {
     if (smem > 48 * 1024)
         MOPS_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           static_cast<int>(smem)));
     int per_sm = 0;
-    MOPS_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem));
+    MOPS_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kPipeWarps * 32, smem));
     per_sm = std::max(1, per_sm);
     return static_cast<unsigned>(std::min<int64_t>(
-        ceil_div(nO, rows_per_block), static_cast<int64_t>(sm_count(call.device)) * per_sm));
-}
-
-template <typename Kernel>
-unsigned pipe_grid(const Call& call, Kernel kernel, size_t smem, int64_t nO) {
-    return resident_grid(call, kernel, kPipeWarps * 32, smem, nO, kPipeWarps);
-}
-
-// Weighted kernels by teams of warps (opsaw_team.cuh): used when B has more than one tile of
-// eight columns. MOPS_B200_TEAM=0 (development switch) falls back to the per-warp kernels,
-// MOPS_B200_TEAM_CH changes the entries per chunk.
-inline bool team_layout_for(const Call& call, size_t scalar, int K, int L, bool vjp, PipeLayout& lay) {
-    if ((L + 7) / 8 < 2 || env_int("MOPS_B200_TEAM", 1) == 0) return false;
-    int ch = env_int("MOPS_B200_TEAM_CH", 32);
-    ch = std::max(4, std::min(32, ch / 4 * 4)); // one lane per entry holds its W row
-    lay = team_layout(scalar, K, L, vjp, ch);
-    return static_cast<size_t>(lay.warp_bytes) <= static_cast<size_t>(max_optin_smem(call.device));
-}
-
-template <typename T, int MT, typename... Args>
-void launch_fwd_team(const Call& call, const PipeLayout& lay, int64_t nO, Args... args) {
-    const size_t smem = static_cast<size_t>(lay.warp_bytes);
-#define MOPS_B200_CASE(NW_)                                                                        \
-    {                                                                                              \
-        auto kernel = opsaw_fwd_team<T, MT, NW_>;                                                  \
-        const unsigned blocks = resident_grid(call, kernel, NW_ * 32, smem, nO, 1);                \
-        kernel<<<blocks, NW_ * 32, smem, call.stream>>>(args..., lay, call.status);                \
-    }
-    switch ((lay.L + 7) / 8) {
-    case 2: MOPS_B200_CASE(2) break;
-    case 3: MOPS_B200_CASE(3) break;
-    default: MOPS_B200_CASE(4) break;
-    }
-#undef MOPS_B200_CASE
-}
-
-template <typename T, int KT, typename... Args>
-void launch_vjp_team(const Call& call, const PipeLayout& lay, int64_t nO, Args... args) {
-    const size_t smem = static_cast<size_t>(lay.warp_bytes);
-#define MOPS_B200_CASE(NW_)                                                                        \
-    {                                                                                              \
-        auto kernel = opsaw_vjp_team<T, KT, NW_>;                                                  \
-        const unsigned blocks = resident_grid(call, kernel, NW_ * 32, smem, nO, 1);                \
-        kernel<<<blocks, NW_ * 32, smem, call.stream>>>(args..., lay, call.status);                \
-    }
-    switch ((lay.L + 7) / 8) {
-    case 2: MOPS_B200_CASE(2) break;
-    case 3: MOPS_B200_CASE(3) break;
-    default: MOPS_B200_CASE(4) break;
-    }
-#undef MOPS_B200_CASE
+        ceil_div(nO, kPipeWarps), static_cast<int64_t>(sm_count(call.device)) * per_sm));
 }
 
 template <typename T, int MT, bool WEIGHTED, typename... Args>
@@ -624,19 +570,6 @@ template <typename T, bool WEIGHTED>
 bool forward_pipe(const Call& call, T* O, const T* A, const T* B, const T* W, const int32_t* PW,
                   const int64_t* offsets, int64_t J, int K, int L, int64_t nO) {
     if (!pipe_usable<T, WEIGHTED>(A, B, W, nullptr, K, L, false)) return false;
-    if constexpr (WEIGHTED) {
-        PipeLayout team;
-        if (team_layout_for(call, sizeof(T), K, L, false, team)) {
-            note_kernel_f("opsaw_fwd_team<%s,MT=%d,NW=%d> ch=%d", scalar_name<T>(), K <= 8 ? 1 : 2,
-                          (L + 7) / 8, team.ch);
-            if (K <= 8)
-                launch_fwd_team<T, 1>(call, team, nO, O, A, B, W, PW, offsets, J, nO, nO);
-            else
-                launch_fwd_team<T, 2>(call, team, nO, O, A, B, W, PW, offsets, J, nO, nO);
-            MOPS_CUDA_OK(cudaGetLastError());
-            return true;
-        }
-    }
     const PipeLayout lay = choose_pipe_layout<T, WEIGHTED>(K, L, false);
     if (static_cast<size_t>(lay.warp_bytes) * kPipeWarps > static_cast<size_t>(max_optin_smem(call.device)))
         return false;
@@ -697,21 +630,6 @@ template <typename T, bool WEIGHTED>
 bool backward_pipe(const Call& call, T* gA, T* gB, T* gW, const T* gO, const T* A, const T* B,
                    const T* W, const int32_t* PW, const int64_t* offsets, int64_t J, int K, int L,
                    int64_t nO) {
-    if constexpr (WEIGHTED) {
-        PipeLayout team;
-        if (team_layout_for(call, sizeof(T), K, L, true, team)) {
-            note_kernel_f("opsaw_vjp_team<%s,KT=%d,NW=%d> ch=%d", scalar_name<T>(), (K + 3) / 4,
-                          (L + 7) / 8, team.ch);
-            switch ((K + 3) / 4) {
-            case 1: launch_vjp_team<T, 1>(call, team, nO, gA, gB, gW, gO, A, B, W, PW, offsets, J, nO, nO); break;
-            case 2: launch_vjp_team<T, 2>(call, team, nO, gA, gB, gW, gO, A, B, W, PW, offsets, J, nO, nO); break;
-            case 3: launch_vjp_team<T, 3>(call, team, nO, gA, gB, gW, gO, A, B, W, PW, offsets, J, nO, nO); break;
-            default: launch_vjp_team<T, 4>(call, team, nO, gA, gB, gW, gO, A, B, W, PW, offsets, J, nO, nO); break;
-            }
-            MOPS_CUDA_OK(cudaGetLastError());
-            return true;
-        }
-    }
     const PipeLayout lay = choose_pipe_layout<T, WEIGHTED>(K, L, true);
     if (static_cast<size_t>(lay.warp_bytes) * kPipeWarps > static_cast<size_t>(max_optin_smem(call.device)))
         return false;
