@@ -520,6 +520,10 @@ bool pipe_usable(const T* A, const T* B, const T* W, const void* extra, int K, i
     return true;
 }
 
+// Shapes of the weighted operation that have kernels with K and L fixed at compile time:
+// L = 32 columns and K = 9, 13 or 16 (angular channels up to l = 4, 6, and (l + 1)^2 for l = 3).
+inline bool fixed_shape(int K, int L) { return L == 32 && (K == 9 || K == 13 || K == 16); }
+
 template <typename T, bool WEIGHTED> PipeLayout choose_pipe_layout(int K, int L, bool vjp) {
     // Measured on B200 (J = 2^24 / E = 2^22): without weights two stages of 32 entries per
     // warp are best (f64 forward 0.91 ms, VJP 1.64 ms against 0.97 / 1.85 with three stages
@@ -598,6 +602,30 @@ bool forward_pipe(const Call& call, T* O, const T* A, const T* B, const T* W, co
             return true;
         }
     }
+    if constexpr (WEIGHTED) {
+        // common shapes with K and L fixed at compile time (MOPS_B200_FIXED=0: development
+        // switch back to the run-time widths)
+        if (fixed_shape(K, L) && lay.ch == kFixedChunk<true> && lay.stages == 2 &&
+            env_int("MOPS_B200_FIXED", 1) != 0) {
+            const size_t smem = static_cast<size_t>(lay.warp_bytes) * kPipeWarps;
+            note_kernel_f("opsa_fwd_pipe<%s,W=1,K=%d,L=%d> ch=%d stages=2", scalar_name<T>(), K, L, lay.ch);
+#define MOPS_B200_CASE(K_)                                                                         \
+    {                                                                                              \
+        auto kernel = opsa_fwd_pipe<T, 2, 4, true, K_, 32>;                                        \
+        const unsigned blocks = pipe_grid(call, kernel, smem, nO);                                 \
+        kernel<<<blocks, kPipeWarps * 32, smem, call.stream>>>(O, A, B, W, PW, offsets, J, nO, nO, \
+                                                               lay, call.status);                 \
+    }
+            switch (K) {
+            case 9: MOPS_B200_CASE(9) break;
+            case 13: MOPS_B200_CASE(13) break;
+            default: MOPS_B200_CASE(16) break;
+            }
+#undef MOPS_B200_CASE
+            MOPS_CUDA_OK(cudaGetLastError());
+            return true;
+        }
+    }
     note_kernel_f("opsa_fwd_pipe<%s,MT=%d,NT=%d,W=%d> ch=%d stages=%d", scalar_name<T>(),
                   K <= 8 ? 1 : 2, (L + 7) / 8, WEIGHTED ? 1 : 0, lay.ch, lay.stages);
     if (K <= 8)
@@ -654,6 +682,29 @@ bool backward_pipe(const Call& call, T* gA, T* gB, T* gW, const T* gO, const T* 
             case 22: MOPS_B200_CASE(2, 2) break;
             case 23: MOPS_B200_CASE(2, 3) break;
             default: MOPS_B200_CASE(2, 4) break;
+            }
+#undef MOPS_B200_CASE
+            MOPS_CUDA_OK(cudaGetLastError());
+            return true;
+        }
+    }
+    if constexpr (WEIGHTED) {
+        if (fixed_shape(K, L) && lay.ch == kFixedChunk<true> && lay.stages == 2 &&
+            env_int("MOPS_B200_FIXED", 1) != 0) {
+            const size_t smem = static_cast<size_t>(lay.warp_bytes) * kPipeWarps;
+            note_kernel_f("opsa_vjp_pipe<%s,W=1,K=%d,L=%d> ch=%d stages=2", scalar_name<T>(), K, L, lay.ch);
+#define MOPS_B200_CASE(K_)                                                                         \
+    {                                                                                              \
+        auto kernel = opsa_vjp_pipe<T, (K_ + 3) / 4, 4, true, K_, 32>;                             \
+        const unsigned blocks = pipe_grid(call, kernel, smem, nO);                                 \
+        kernel<<<blocks, kPipeWarps * 32, smem, call.stream>>>(gA, gB, gW, gO, A, B, W, PW,        \
+                                                               offsets, J, nO, nO, lay,           \
+                                                               call.status);                      \
+    }
+            switch (K) {
+            case 9: MOPS_B200_CASE(9) break;
+            case 13: MOPS_B200_CASE(13) break;
+            default: MOPS_B200_CASE(16) break;
             }
 #undef MOPS_B200_CASE
             MOPS_CUDA_OK(cudaGetLastError());

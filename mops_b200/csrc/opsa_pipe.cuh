@@ -35,9 +35,10 @@ struct PipeLayout {
 
 constexpr int kPipeWarps = 4;
 
-inline int round16(size_t n) { return static_cast<int>((n + 15) / 16 * 16); }
+__host__ __device__ constexpr int round16(size_t n) { return static_cast<int>((n + 15) / 16 * 16); }
 
-inline PipeLayout pipe_layout(size_t s, int K, int L, bool weighted, bool vjp, int ch, int stages) {
+__host__ __device__ constexpr PipeLayout pipe_layout(size_t s, int K, int L, bool weighted, bool vjp, int ch,
+                                                     int stages) {
     PipeLayout p{};
     p.K = K, p.L = L;
     p.LP = weighted ? L + 4 : L;
@@ -146,13 +147,32 @@ __device__ __forceinline__ PipeWarp pipe_partition(const int64_t* __restrict__ o
 // ------------------------------------------------------------------------------- forward
 // O[r] = A[seg]^T (B[seg] * W[PW[seg]]) with the entries as the MMA's k dimension, four per
 // step. MT = ceil(K / 8), NT = ceil(L / 8).
-template <typename S, int MT, int NT, bool WEIGHTED>
+//
+// KC, LC > 0: K and L fixed at compile time (with the default ring: kFixedChunk entries per
+// chunk, two stages): every offset inside a stage and every stride becomes a constant, which
+// removes about a third of the instructions of the run-time-width kernel. The host picks such
+// an instantiation when the shapes match one of the common ones and the run-time layout equals
+// the fixed one; lay_rt is then ignored.
+template <bool WEIGHTED> constexpr int kFixedChunk = WEIGHTED ? 8 : 32;
+
+template <typename S, bool WEIGHTED, bool VJP, int KC, int LC>
+__device__ __forceinline__ PipeLayout fixed_layout_or(const PipeLayout& run_time) {
+    if constexpr (KC > 0) {
+        constexpr PipeLayout fixed = pipe_layout(sizeof(S), KC, LC, WEIGHTED, VJP, kFixedChunk<WEIGHTED>, 2);
+        return fixed;
+    } else {
+        return run_time;
+    }
+}
+
+template <typename S, int MT, int NT, bool WEIGHTED, int KC = 0, int LC = 0>
 __global__ void __launch_bounds__(kPipeWarps * 32, 4)
 opsa_fwd_pipe(S* __restrict__ O, const S* __restrict__ A, const S* __restrict__ B,
               const S* __restrict__ W, const int32_t* __restrict__ PW,
               const int64_t* __restrict__ offsets, int64_t J, int64_t nO, int64_t nW,
-              PipeLayout lay, Status st) {
+              PipeLayout lay_rt, Status st) {
     using T = double;
+    const PipeLayout lay = fixed_layout_or<S, WEIGHTED, false, KC, LC>(lay_rt);
     extern __shared__ __align__(128) unsigned char pipe_smem[];
     if (saw_unsorted(st)) return; // the atomic kernel of the same call does the work
     const int lane = threadIdx.x & 31;
@@ -323,14 +343,15 @@ opsa_fwd_pipe(S* __restrict__ O, const S* __restrict__ A, const S* __restrict__ 
 // (grad_B = X * W, grad_W[PW] += X * B) with gO[r] as the common factor, kept in registers as
 // MMA fragments while the row lasts; entries are the MMA's m dimension, eight per tile.
 // KT = ceil(K / 4), LT8 = ceil(L / 8).
-template <typename S, int KT, int LT8, bool WEIGHTED>
+template <typename S, int KT, int LT8, bool WEIGHTED, int KC = 0, int LC = 0>
 __global__ void __launch_bounds__(kPipeWarps * 32, 3)
 opsa_vjp_pipe(S* __restrict__ gA, S* __restrict__ gB, S* __restrict__ gW,
               const S* __restrict__ gO, const S* __restrict__ A, const S* __restrict__ B,
               const S* __restrict__ W, const int32_t* __restrict__ PW,
               const int64_t* __restrict__ offsets, int64_t J, int64_t nO, int64_t nW,
-              PipeLayout lay, Status st) {
+              PipeLayout lay_rt, Status st) {
     using T = double;
+    const PipeLayout lay = fixed_layout_or<S, WEIGHTED, true, KC, LC>(lay_rt);
     using S2 = typename VecOf<S, 2>::type;
     constexpr int NTK = (KT + 1) / 2; // 8-wide tiles over K
     constexpr int KSL = 2 * LT8;      // k-steps over L
