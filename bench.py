@@ -80,14 +80,18 @@ BATCH_KEYS = {"hpe": ("I",), "sap": ("I",), "opsa": ("J", "nO"), "opsaw": ("E", 
               "sasaw": ("E", "n")}
 ROW_KEYS = ("nO", "n")
 # what bounds each case on the SM: HBM bytes, shared-memory
-# wavefronts (every operand is a gather with a run-time index), or FP64 throughput
+# wavefronts (every operand is a gather with a run-time index), or FP64 throughput. SASAW also
+# reports the DRAM traffic it really causes (`*_traffic_frac_of_hbm`): its W table (151 MB at
+# the benchmark size) does not fit L2, so the gathered W rows and the grad_W additions of every
+# edge go to DRAM and the kernels move 4 to 7 times their algorithmic bytes.
 BOUND = {"hpe": "smem", "sap": "smem", "opsa": "hbm", "opsa_f32": "hbm", "opsaw": "hbm",
          "sasaw": "fp64"}
 # kernels of this library launched by one forward / one VJP call of every case (sorted input,
-# waiting calls): a table builder (plan, segment offsets, coupling) + the main kernel; the f32
-# OPSA VJP needs no table, the SASAW forward builds two
-LAUNCHES = {"hpe": (2, 2), "sap": (2, 2), "opsa": (2, 2), "opsa_f32": (2, 1), "opsaw": (2, 2),
-            "sasaw": (3, 2)}
+# waiting calls, no plan bound): a table builder (HPE / SAP plan, segment offsets) + the main
+# kernel; SASAW builds two tables (segment offsets and the grouped coupling) in either call.
+# profiles/launch_list_full_bench.md counts the same 26 launches per step.
+LAUNCHES = {"hpe": (2, 2), "sap": (2, 2), "opsa": (2, 2), "opsa_f32": (2, 2), "opsaw": (2, 2),
+            "sasaw": (3, 3)}
 
 OP_NAMES = {"hpe": "homogeneous_polynomial_evaluation", "sap": "sparse_accumulation_of_products",
             "opsa": "outer_product_scatter_add", "opsaw": "outer_product_scatter_add_with_weights",
@@ -829,6 +833,8 @@ def main():
             entry[f"{lvl}_traffic"] = dram
             if note:
                 entry[f"{lvl}_traffic_note"] = note
+            if dram is not None:
+                entry[f"{lvl}_traffic_frac_of_hbm"] = dram / ms / 1e6 / peak
             if BOUND[n] == "hbm":
                 entry[f"{lvl}_frac_of_bound"] = b / ms / 1e6 / peak
             elif BOUND[n] == "smem":

@@ -147,6 +147,21 @@ def test_outer_product_shapes(oracle, K, L, dtype):
     compare("opsaw", workloads.opsaw(E=700, K=K, L=L, n=23), dtype, oracle, what=f"opsaw {K}x{L}")
 
 
+@pytest.mark.parametrize("K", [9, 13, 16])
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_weighted_outer_product_fixed_shapes(oracle, K, dtype):
+    """The weighted kernels with K and L fixed at compile time (L = 32, K = 9, 13, 16): ragged
+    rows, empty rows, one row that spans many chunks, an entry count that is no multiple of
+    the chunk."""
+    d = workloads.opsaw(E=4999, K=K, L=32, n=211)
+    po = d["indices_output"]
+    po[po == 5] = 6          # row 5 is empty
+    po[1000:1900] = po[1000]  # a long row
+    po.sort()
+    compare("opsaw", d, dtype, oracle, what=f"opsaw fixed {K}x32")
+    compare("opsaw", workloads.opsaw(E=7, K=K, L=32, n=3), dtype, oracle, what=f"opsaw tiny {K}x32")
+
+
 @pytest.mark.parametrize("kw", [
     dict(I=100, nA=3, nB=20, nO=7, K=300),      # A is the register-resident operand
     dict(I=257, nA=20, nB=16, nO=50, K=1000),   # widest register-resident row
