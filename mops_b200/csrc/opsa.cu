@@ -526,11 +526,13 @@ inline bool fixed_shape(int K, int L) { return L == 32 && (K == 9 || K == 13 || 
 
 template <typename T, bool WEIGHTED> PipeLayout choose_pipe_layout(int K, int L, bool vjp) {
     // Measured on B200 (J = 2^24 / E = 2^22): without weights two stages of 32 entries per
-    // warp are best (f64 forward 0.91 ms, VJP 1.64 ms against 0.97 / 1.85 with three stages
+    // warp are best for f64 (forward 0.92 ms, VJP 1.60 ms against 0.97 / 1.84 with four stages
     // of 16): the smaller ring lets more warps share an SM, and one chunk in flight per warp
-    // already keeps about 100 KB per SM in flight. With weights a stage also holds the padded
-    // B and W rows (680 bytes per entry), so chunks of 8 keep the warp count up (forward
-    // 0.59 ms, VJP 1.12 ms against 0.92 / 1.63 with chunks of 32).
+    // already keeps about 100 KB per SM in flight; f32 takes 64 entries (the same bytes:
+    // forward 0.52 ms, VJP 0.95 ms against 0.56 / 1.09 with 32). With weights a stage also
+    // holds the padded B and W rows (680 bytes per entry), so chunks of 8 keep the warp count
+    // up (forward 0.49 ms, VJP 1.00 ms against 0.54 / 1.02 with 16; four stages of 4 or 8:
+    // 0.54 / 1.49 and 0.74 / 1.23). The stage count is rounded to a power of two.
     int ch = env_int("MOPS_B200_PIPE_CH", WEIGHTED ? 8 : sizeof(T) == 4 ? 64 : 32);
     int stages = env_int("MOPS_B200_PIPE_STAGES", 2);
     ch = std::max(4, std::min(WEIGHTED ? 32 : 128, ch / 4 * 4)); // weighted: one lane per entry

@@ -61,9 +61,16 @@ def shard_scatter(arrays, index_name, n_rows, world, rank, per_entry):
     local = dict(arrays)
     for name in per_entry:
         if name in arrays:
-            local[name] = arrays[name][lo:hi]
+            local[name] = _own(arrays[name][lo:hi])
     local[index_name] = arrays[index_name][lo:hi] - rho[rank]
     return local, (rho[rank], rho[rank + 1])
+
+
+def _own(view):
+    """A copy of a slice in storage of its own. A slice that starts in the middle of an array
+    is rarely aligned to 16 bytes, and the streaming kernels (bulk asynchronous copies) only
+    take aligned operands: a view would run on the slower general kernels."""
+    return view.clone() if hasattr(view, "clone") else view.copy()
 
 
 def all_reduce_sum(tensor):
