@@ -610,10 +610,19 @@ def main():
         if timers is not None:
             launched[(n, "vjp")] = _lib.last_kernels()
         if reduce and op in ("opsaw", "sasaw") and grads[2].is_cuda:
-            dist.all_reduce(grads[2])
+            # the one exchange step of the path: started here, joined at the end of the step,
+            # so that it overlaps the calls that follow (nothing in the step reads grad_W)
+            pending.append((dist.all_reduce(grads[2], async_op=True), grads[2]))
         if timers is not None:
             timers[2].record()
         return out, grads
+
+    pending = []
+
+    def join_reductions():
+        for work, _ in pending:
+            work.wait()
+        pending.clear()
 
     # ---- device-resident timing
     sampler = ClockSampler(physical_gpu_index(local))
@@ -621,6 +630,7 @@ def main():
     for _ in range(args.warmup):
         for n in names:
             run_case(n, devd[n])
+        join_reductions()
     barrier()
     events = [[[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in names]
               for _ in range(args.steps)]
@@ -631,6 +641,7 @@ def main():
     for s in range(args.steps):
         for i, n in enumerate(names):
             run_case(n, devd[n], events[s][i])
+        join_reductions()
     stop.record()
     barrier()
     sampler.enabled = False
