@@ -1070,7 +1070,10 @@ opsa_vjp_mma(S* __restrict__ gA, S* __restrict__ gB, S* __restrict__ gW,
     const int64_t nwarps = static_cast<int64_t>(gridDim.x) * warps;
     const int64_t rowsize = static_cast<int64_t>(K) * L;
     const bool want_a = gA != nullptr, want_b = gB != nullptr || (WEIGHTED && gW != nullptr);
-    const bool pair_ok = L % 2 == 0; // two-scalar accesses to rows of B, W, grad_B
+    // two-scalar accesses to rows of B, W, grad_B: rows of even length in 16-byte (8-byte for
+    // f32) aligned arrays; this kernel is the one that serves unaligned operands
+    auto pair_aligned = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % (2 * sizeof(S)) == 0; };
+    const bool pair_ok = L % 2 == 0 && pair_aligned(gB) && (!WEIGHTED || (pair_aligned(B) && pair_aligned(W)));
 
     for (int64_t r = static_cast<int64_t>(blockIdx.x) * warps + warp; r < nO; r += nwarps) {
         const int64_t lo = offsets[r], hi = offsets[r + 1];

@@ -12,7 +12,8 @@
 // Checks and error types follow mops-torch/src/utils.cpp:7-66 (same device, f32/f64 only and
 // all equal, int32 indices, number of dimensions) and the per-op rules: gradients with respect
 // to C are refused (mops-torch/src/hpe.cpp:85-91, sap.cpp:135-141, sasaw.cpp:158-164); second
-// derivatives exist for SAP only, as in the reference CUDA build.
+// derivatives exist for HPE, SAP and OPSA (the operations whose _vjp_vjp the reference declares);
+// OPSAW and SASAW refuse them, as the reference does.
 #include <string>
 #include <vector>
 

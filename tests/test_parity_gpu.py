@@ -162,6 +162,28 @@ def test_weighted_outer_product_fixed_shapes(oracle, K, dtype):
     compare("opsaw", workloads.opsaw(E=7, K=K, L=32, n=3), dtype, oracle, what=f"opsaw tiny {K}x32")
 
 
+@pytest.mark.parametrize("op", ["opsa", "opsaw", "sasaw"])
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_operands_that_are_views_at_odd_addresses(oracle, op, dtype):
+    """Per-entry operands that are views starting one scalar into a larger allocation (what a
+    slice of a bigger array looks like): not 16-byte aligned, so the streaming kernels do not
+    apply and the general kernels must give the same results."""
+    import torch
+    d = {"opsa": workloads.opsa(J=3001, K=13, L=20, nO=57),
+         "opsaw": workloads.opsaw(E=3001, K=13, L=32, n=57),
+         "sasaw": workloads.sasaw(E=1501, n=57)}[op]
+    t = to_dev(d, dtype)
+    for name in ("A", "B", "grad_output"):
+        flat = torch.empty(t[name].numel() + 1, dtype=t[name].dtype, device="cuda")
+        flat[1:] = t[name].reshape(-1)
+        t[name] = flat[1:].view(t[name].shape)
+        assert t[name].data_ptr() % 16 != 0 and t[name].is_contiguous()
+    got = run_library(op, t)
+    want = run_checker(oracle, op, d, dtype)
+    for k in want:
+        assert_parity(got[k], want[k], f"{op} unaligned views {k}")
+
+
 @pytest.mark.parametrize("kw", [
     dict(I=100, nA=3, nB=20, nO=7, K=300),      # A is the register-resident operand
     dict(I=257, nA=20, nB=16, nO=50, K=1000),   # widest register-resident row
