@@ -25,12 +25,13 @@ def batch_range(n_rows, world, rank):
     return start, start + base + (1 if rank < extra else 0)
 
 
-def segment_cuts(indices_output, n_rows, world):
+def segment_cuts(indices_output, n_rows, world, known_ascending=False):
     """Row cut points rho[0..world] (rho[0] = 0, rho[world] = n_rows) and the matching entry
     cut points eps[0..world] for an ascending scatter index, such that every rank gets whole
-    output rows and about the same number of entries."""
+    output rows and about the same number of entries. ``known_ascending``: the caller has
+    already looked (the check reads the whole index)."""
     idx = np.asarray(indices_output)
-    if idx.size and np.any(idx[1:] < idx[:-1]):
+    if not known_ascending and idx.size and np.any(idx[1:] < idx[:-1]):
         raise ValueError("segment sharding needs an ascending scatter index")
     n_entries = idx.shape[0]
     rho, eps = [0], [0]
@@ -38,10 +39,11 @@ def segment_cuts(indices_output, n_rows, world):
         target = (n_entries * r) // world
         # first row whose entries start at or after the target position
         row = int(idx[target]) if target < n_entries else n_rows
-        start_of_row = int(np.searchsorted(idx, row, side="left"))
+        # (the needle in the index's own dtype: NumPy would otherwise convert the whole index)
+        start_of_row = int(np.searchsorted(idx, idx.dtype.type(row), side="left"))
         if start_of_row < target:  # the target falls inside a row: cut after it
             row += 1
-            start_of_row = int(np.searchsorted(idx, row, side="left"))
+            start_of_row = int(np.searchsorted(idx, idx.dtype.type(row), side="left"))
         row = max(row, rho[-1])
         rho.append(min(row, n_rows))
         eps.append(max(start_of_row, eps[-1]))
