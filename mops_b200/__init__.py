@@ -183,8 +183,17 @@ class HostQueue:
             raise MopsError("no CUDA device available")
         index = torch.cuda.current_device() if device is None else torch.device(device).index
         self.device = torch.device("cuda", index)
-        self.copy_in, self.compute, self.copy_out = (torch.cuda.Stream(device=self.device)
-                                                     for _ in range(3))
+        # The three streams are made once per thread and device and shared by the queues that
+        # follow each other: torch's caching allocator keeps freed device memory per stream, so
+        # a queue on fresh streams could not reuse what the previous queue's arrays occupied
+        # (28 GB per step of the benchmark: the device filled up within a few steps and every
+        # so often a step stalled for half a second while the allocator emptied its cache).
+        streams = getattr(HostQueue._local, "streams", None)
+        if streams is None:
+            streams = HostQueue._local.streams = {}
+        if index not in streams:
+            streams[index] = tuple(torch.cuda.Stream(device=self.device) for _ in range(3))
+        self.copy_in, self.compute, self.copy_out = streams[index]
         self._operands = {}  # (address, bytes, dtype) -> (device tensor, event, host array)
         self._keep = []
 

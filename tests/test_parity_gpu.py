@@ -405,6 +405,25 @@ def test_host_queue_overlaps_calls_and_matches_the_oracle(oracle):
     assert_parity(out, w1["output"], "after the queue")
 
 
+def test_host_queues_in_a_row_reuse_device_memory():
+    """Queues that follow each other run on the same streams, so torch's caching allocator
+    hands the arrays of one queue to the next: the memory it has reserved does not grow."""
+    import torch
+    import mops_b200 as M
+    d = workloads.sap(I=200_000)
+    pin = {k: (torch.from_numpy(v).pin_memory() if isinstance(v, np.ndarray) else v)
+           for k, v in d.items()}
+    idx = (pin["indices_A"], pin["indices_B"], pin["indices_output"])
+    reserved = []
+    for _ in range(8):
+        with M.HostQueue():
+            M.sparse_accumulation_of_products(pin["A"], pin["B"], pin["C"], *idx, 50)
+            M.sparse_accumulation_of_products_vjp(pin["grad_output"], pin["A"], pin["B"],
+                                                  pin["C"], *idx)
+        reserved.append(torch.cuda.memory_reserved())
+    assert reserved[-1] == reserved[1], reserved
+
+
 # ---------------------------------------------------------------- the timed configurations
 @pytest.mark.parametrize("name", ["hpe", "sap", "opsa", "opsa_f32", "opsaw", "sasaw"])
 def test_timed_configurations_against_oracle_subranges(oracle, name):
