@@ -31,7 +31,8 @@ result back to pinned host memory on three streams, all inside the timed region.
 oracle on sub-ranges (tests/subrange.py), outside the timed region.
 
 ``small_configs``: call latency (median / p10 / p90 of >= 100 synchronous calls through the
-C ABI) at the five small configurations of BASELINE.json; no roofline for these.
+C ABI) at the five small configurations the reference's own benchmark programs run
+(mops/benchmarks/*.cpp: the generators' defaults); no roofline for these.
 
 With N > 1 every rank first runs its own problem of the full per-GPU size (weak scaling, the
 headline), then all ranks split rank 0's problem (``strong``: batch rows / output-segment
@@ -70,7 +71,8 @@ CASES = {
     "opsaw": ("opsaw", np.float64, dict(E=1 << 22, n=1 << 16), 8),
     "sasaw": ("sasaw", np.float64, dict(E=1 << 22, n=1 << 16), 64),
 }
-# the configurations BASELINE.json lists (the generators' defaults): latency cases
+# the configurations of the reference's benchmark programs (the generators' defaults):
+# latency cases
 SMALL_CASES = {
     "hpe": ("hpe", np.float64), "sap": ("sap", np.float64), "opsa": ("opsa", np.float64),
     "opsa_f32": ("opsa", np.float32), "opsaw": ("opsaw", np.float64),
@@ -358,7 +360,7 @@ def cpu_run(impl, kind, threads, names, steps, warmup, full):
 
 def cpu_small_configs(impl, kind, names):
     """Call latency of the CPU implementation at the small configurations (full config, as
-    listed in BASELINE.json), through the reference's C ABI on preallocated arrays;
+    of the reference's benchmark programs), through the reference's C ABI on preallocated arrays;
     repetitions sized to about two seconds per call kind."""
     out = {}
     for n in names:
