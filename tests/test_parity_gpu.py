@@ -162,6 +162,32 @@ def test_weighted_outer_product_fixed_shapes(oracle, K, dtype):
     compare("opsaw", workloads.opsaw(E=7, K=K, L=32, n=3), dtype, oracle, what=f"opsaw tiny {K}x32")
 
 
+@pytest.mark.parametrize("seed", list(range(16)))
+def test_outer_product_random_shapes_and_row_lengths(oracle, seed):
+    """Random widths within the streaming kernels' range (K <= 16, L <= 32), entry counts that
+    are no multiple of a chunk, and row lengths from empty to several chunks: the whole /
+    ragged step logic at every alignment, both dtypes, with and without weights."""
+    r = np.random.default_rng(9000 + seed)
+    K, L = int(r.integers(1, 17)), int(r.integers(1, 33))
+    if seed % 2:
+        L = int(r.choice([2, 4, 8, 12, 16, 20, 24, 28, 32]))  # weighted streaming needs 16-byte rows
+    nO = int(r.integers(1, 120))
+    J = int(r.integers(1, 2500))
+    # row lengths: a few long rows, many short ones, some empty
+    weights = r.random(nO) ** 4
+    weights[r.random(nO) < 0.3] = 0.0
+    if weights.sum() == 0:
+        weights[0] = 1.0
+    rows = np.sort(r.choice(nO, size=J, p=weights / weights.sum())).astype(np.int32)
+    for dtype in DTYPES:
+        d = workloads.opsa(J=J, K=K, L=L, nO=nO, seed=seed)
+        d["indices_output"] = rows
+        compare("opsa", d, dtype, oracle, what=f"opsa random {K}x{L} J={J} nO={nO}")
+        d = workloads.opsaw(E=J, K=K, L=L, n=nO, seed=seed)
+        d["indices_output"] = rows
+        compare("opsaw", d, dtype, oracle, what=f"opsaw random {K}x{L} E={J} n={nO}")
+
+
 @pytest.mark.parametrize("op", ["opsa", "opsaw", "sasaw"])
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_operands_that_are_views_at_odd_addresses(oracle, op, dtype):
