@@ -19,12 +19,12 @@ GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "golden.npz"))
 DTYPES = [np.float64, np.float32]
 
 
-def compare(op, d, dtype, checker, second_order=False, what=""):
+def compare(op, d, dtype, checker, second_order=False, what="", tol=None):
     got = run_library(op, to_dev(d, dtype), second_order)
     want = run_checker(checker, op, d, dtype, second_order)
     assert set(got) == set(want)
     for k in want:
-        assert_parity(got[k], want[k], f"{what or op}/{k}/{np.dtype(dtype).name}")
+        assert_parity(got[k], want[k], f"{what or op}/{k}/{np.dtype(dtype).name}", tol=tol)
 
 
 # ---------------------------------------------------------------- the reference's fixtures
@@ -186,6 +186,33 @@ def test_outer_product_random_shapes_and_row_lengths(oracle, seed):
         d = workloads.opsaw(E=J, K=K, L=L, n=nO, seed=seed)
         d["indices_output"] = rows
         compare("opsaw", d, dtype, oracle, what=f"opsaw random {K}x{L} E={J} n={nO}")
+
+
+@pytest.mark.parametrize("seed", list(range(10)))
+def test_sasaw_random_shapes_and_row_lengths(oracle, seed):
+    """SASAW with the compiled-in channel counts (4, 9, 16) and with arbitrary ones, several
+    widths of B, and rows from empty to many quads of edges: the walk over quads across row
+    boundaries at every alignment."""
+    r = np.random.default_rng(7000 + seed)
+    if seed % 2 == 0:
+        nA = nW2 = nO2 = int(r.choice([4, 9, 16]))
+    else:
+        nA, nW2, nO2 = (int(x) for x in r.integers(1, 17, 3))
+    L = int(r.choice([32, 32, 8, 20, 40, 64]))
+    n = int(r.integers(1, 60))
+    E = int(r.integers(1, 1500))
+    N = int(r.integers(1, 400))
+    weights = r.random(n) ** 4
+    weights[r.random(n) < 0.3] = 0.0
+    if weights.sum() == 0:
+        weights[0] = 1.0
+    d = workloads.sasaw(E=E, nA=nA, L=L, n=n, N=N, nW2=nW2, nO2=nO2, seed=seed)
+    d["indices_output_1"] = np.sort(r.choice(n, size=E, p=weights / weights.sum())).astype(np.int32)
+    # one row may hold most of the edges here: an f32 sum of that many terms (thousands, in
+    # two different orders) is good to a few 1e-5 of the largest element, not to 1e-5
+    for dtype, tol in ((np.float64, None), (np.float32, 5e-5)):
+        compare("sasaw", d, dtype, oracle, tol=tol,
+                what=f"sasaw random {nA},{nW2},{nO2} L={L} E={E} n={n} N={N}")
 
 
 @pytest.mark.parametrize("op", ["opsa", "opsaw", "sasaw"])
