@@ -540,6 +540,20 @@ template <typename T, bool WEIGHTED> PipeLayout choose_pipe_layout(int K, int L,
     return pipe_layout(sizeof(T), K, L, WEIGHTED, vjp, ch, stages);
 }
 
+// Grid of a VJP streaming kernel, whose warps split the entries: at most one warp per chunk.
+template <typename Kernel>
+unsigned pipe_grid_entries(const Call& call, Kernel kernel, size_t smem, int64_t J, int ch) {
+    if (smem > 48 * 1024)
+        MOPS_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          static_cast<int>(smem)));
+    int per_sm = 0;
+    MOPS_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kPipeWarps * 32, smem));
+    per_sm = std::max(1, per_sm);
+    return static_cast<unsigned>(std::max<int64_t>(
+        1, std::min<int64_t>(ceil_div(J, static_cast<int64_t>(kPipeWarps) * ch),
+                             static_cast<int64_t>(sm_count(call.device)) * per_sm)));
+}
+
 template <typename Kernel>
 unsigned pipe_grid(const Call& call, Kernel kernel, size_t smem, int64_t nO) {
     if (smem > 48 * 1024)
@@ -639,12 +653,12 @@ bool forward_pipe(const Call& call, T* O, const T* A, const T* B, const T* W, co
 }
 
 template <typename T, int KT, bool WEIGHTED, typename... Args>
-void launch_vjp_pipe_l(const Call& call, const PipeLayout& lay, int64_t nO, Args... args) {
+void launch_vjp_pipe_l(const Call& call, const PipeLayout& lay, int64_t J, Args... args) {
     const size_t smem = static_cast<size_t>(lay.warp_bytes) * kPipeWarps;
 #define MOPS_B200_CASE(LT_)                                                                        \
     {                                                                                              \
         auto kernel = opsa_vjp_pipe<T, KT, LT_, WEIGHTED>;                                         \
-        const unsigned blocks = pipe_grid(call, kernel, smem, nO);                                 \
+        const unsigned blocks = pipe_grid_entries(call, kernel, smem, J, lay.ch);                  \
         kernel<<<blocks, kPipeWarps * 32, smem, call.stream>>>(args..., lay, call.status);         \
     }
     switch ((lay.L + 7) / 8) {
@@ -671,7 +685,7 @@ bool backward_pipe(const Call& call, T* gA, T* gB, T* gW, const T* gO, const T* 
 #define MOPS_B200_CASE(KS_, LS_)                                                                   \
     {                                                                                              \
         auto kernel = opsa_vjp_pipe_tf32<KS_, LS_>;                                                \
-        const unsigned blocks = pipe_grid(call, kernel, smem, nO);                                 \
+        const unsigned blocks = pipe_grid_entries(call, kernel, smem, J, lay.ch);                  \
         kernel<<<blocks, kPipeWarps * 32, smem, call.stream>>>(gA, gB, gO, A, B, offsets, J, nO,   \
                                                                lay, call.status);                 \
     }
@@ -698,7 +712,7 @@ bool backward_pipe(const Call& call, T* gA, T* gB, T* gW, const T* gO, const T* 
 #define MOPS_B200_CASE(K_)                                                                         \
     {                                                                                              \
         auto kernel = opsa_vjp_pipe<T, (K_ + 3) / 4, 4, true, K_, 32>;                             \
-        const unsigned blocks = pipe_grid(call, kernel, smem, nO);                                 \
+        const unsigned blocks = pipe_grid_entries(call, kernel, smem, J, lay.ch);                  \
         kernel<<<blocks, kPipeWarps * 32, smem, call.stream>>>(gA, gB, gW, gO, A, B, W, PW,        \
                                                                offsets, J, nO, nO, lay,           \
                                                                call.status);                      \
@@ -716,10 +730,10 @@ bool backward_pipe(const Call& call, T* gA, T* gB, T* gW, const T* gO, const T* 
     note_kernel_f("opsa_vjp_pipe<%s,KT=%d,LT8=%d,W=%d> ch=%d stages=%d", scalar_name<T>(),
                   (K + 3) / 4, (L + 7) / 8, WEIGHTED ? 1 : 0, lay.ch, lay.stages);
     switch ((K + 3) / 4) {
-    case 1: launch_vjp_pipe_l<T, 1, WEIGHTED>(call, lay, nO, gA, gB, gW, gO, A, B, W, PW, offsets, J, nO, nO); break;
-    case 2: launch_vjp_pipe_l<T, 2, WEIGHTED>(call, lay, nO, gA, gB, gW, gO, A, B, W, PW, offsets, J, nO, nO); break;
-    case 3: launch_vjp_pipe_l<T, 3, WEIGHTED>(call, lay, nO, gA, gB, gW, gO, A, B, W, PW, offsets, J, nO, nO); break;
-    default: launch_vjp_pipe_l<T, 4, WEIGHTED>(call, lay, nO, gA, gB, gW, gO, A, B, W, PW, offsets, J, nO, nO); break;
+    case 1: launch_vjp_pipe_l<T, 1, WEIGHTED>(call, lay, J, gA, gB, gW, gO, A, B, W, PW, offsets, J, nO, nO); break;
+    case 2: launch_vjp_pipe_l<T, 2, WEIGHTED>(call, lay, J, gA, gB, gW, gO, A, B, W, PW, offsets, J, nO, nO); break;
+    case 3: launch_vjp_pipe_l<T, 3, WEIGHTED>(call, lay, J, gA, gB, gW, gO, A, B, W, PW, offsets, J, nO, nO); break;
+    default: launch_vjp_pipe_l<T, 4, WEIGHTED>(call, lay, J, gA, gB, gW, gO, A, B, W, PW, offsets, J, nO, nO); break;
     }
     MOPS_CUDA_OK(cudaGetLastError());
     return true;

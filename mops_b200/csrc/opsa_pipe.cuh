@@ -144,6 +144,34 @@ __device__ __forceinline__ PipeWarp pipe_partition(const int64_t* __restrict__ o
     return w;
 }
 
+// The VJP produces one gradient row per entry and sums nothing over the entries of an output
+// row (grad_W goes through atomics anyway), so its warps split the ENTRIES evenly, in units
+// of four so that every warp's first slice is 16-byte aligned: a warp may start and stop
+// inside a row. One very long row, or fewer rows than warps, still occupies the whole GPU.
+// r0 .. r1 are then the rows the warp's entries fall into (the first and the last one possibly
+// shared with its neighbours).
+__device__ __forceinline__ PipeWarp pipe_partition_entries(const int64_t* __restrict__ offsets,
+                                                           int64_t nO, int ch, int warp) {
+    PipeWarp w;
+    const int lane = threadIdx.x & 31;
+    const int64_t total = static_cast<int64_t>(gridDim.x) * kPipeWarps;
+    const int64_t gwarp = static_cast<int64_t>(blockIdx.x) * kPipeWarps + warp;
+    const int64_t J = offsets[nO], quads = (J + 3) / 4;
+    const int64_t lo = quads / total * gwarp + quads % total * gwarp / total;
+    const int64_t hi = quads / total * (gwarp + 1) + quads % total * (gwarp + 1) / total;
+    w.e_begin = w.e_first = 4 * lo < J ? 4 * lo : J;
+    w.e_last = 4 * hi < J ? 4 * hi : J;
+    w.r0 = w.r1 = 0;
+    w.nchunks = 0;
+    if (w.e_last <= w.e_begin) return w;
+    // the row that holds e_begin: the last one that starts at or before it (offsets[0] = 0 and
+    // offsets[nO] = J > e_begin bracket it); likewise for the last entry
+    w.r0 = warp_count_weighted_le(offsets, nO + 1, 0, w.e_begin, lane) - 1;
+    w.r1 = warp_count_weighted_le(offsets, nO + 1, 0, w.e_last - 1, lane);
+    w.nchunks = static_cast<int>((w.e_last - w.e_first + ch - 1) / ch);
+    return w;
+}
+
 // ------------------------------------------------------------------------------- forward
 // O[r] = A[seg]^T (B[seg] * W[PW[seg]]) with the entries as the MMA's k dimension, four per
 // step. MT = ceil(K / 8), NT = ceil(L / 8).
@@ -373,7 +401,7 @@ opsa_vjp_pipe(S* __restrict__ gA, S* __restrict__ gB, S* __restrict__ gW,
         mbarrier_init_fence();
     }
     __syncwarp();
-    const PipeWarp w = pipe_partition(offsets, nO, CH, warp);
+    const PipeWarp w = pipe_partition_entries(offsets, nO, CH, warp);
     if (w.r0 >= w.r1 || w.nchunks == 0) return; // gradients exist per entry only
 
     const bool want_a = gA != nullptr, want_b = gB != nullptr || (WEIGHTED && gW != nullptr);
@@ -804,7 +832,7 @@ opsa_vjp_pipe_tf32(float* __restrict__ gA, float* __restrict__ gB, const float* 
         mbarrier_init_fence();
     }
     __syncwarp();
-    const PipeWarp w = pipe_partition(offsets, nO, CH, warp);
+    const PipeWarp w = pipe_partition_entries(offsets, nO, CH, warp);
     if (w.r0 >= w.r1 || w.nchunks == 0) return;
     const bool want_a = gA != nullptr, want_b = gB != nullptr;
     const int64_t rowsize = static_cast<int64_t>(K) * L;
