@@ -194,7 +194,7 @@ __device__ __forceinline__ PipeLayout fixed_layout_or(const PipeLayout& run_time
 }
 
 template <typename S, int MT, int NT, bool WEIGHTED, int KC = 0, int LC = 0>
-__global__ void __launch_bounds__(kPipeWarps * 32, 4)
+__global__ void __launch_bounds__(kPipeWarps * 32, (KC > 0 && WEIGHTED) ? 5 : 4)
 opsa_fwd_pipe(S* __restrict__ O, const S* __restrict__ A, const S* __restrict__ B,
               const S* __restrict__ W, const int32_t* __restrict__ PW,
               const int64_t* __restrict__ offsets, int64_t J, int64_t nO, int64_t nW,
