@@ -707,8 +707,16 @@ bool backward_pipe(const Call& call, T* gA, T* gB, T* gW, const T* gO, const T* 
     if constexpr (WEIGHTED) {
         if (fixed_shape(K, L) && lay.ch == kFixedChunk<true> && lay.stages == 2 &&
             env_int("MOPS_B200_FIXED", 1) != 0) {
+            const PipeLayout& lay2 = lay;
+            // Rows of 32 entries or more: one grad_output slot per warp instead of two (the
+            // copy of the next row then has the whole current row to arrive), which is what
+            // lets a fourth block fit an SM's shared memory (forward / VJP at E = 2^22,
+            // 2^16 rows: 0.99 ms with two slots and three blocks).
+            const bool long_rows = J / std::max<int64_t>(nO, 1) >= 32;
+            const PipeLayout lay = pipe_layout(sizeof(T), K, L, true, true, lay2.ch, 2, long_rows ? 1 : 2);
             const size_t smem = static_cast<size_t>(lay.warp_bytes) * kPipeWarps;
-            note_kernel_f("opsa_vjp_pipe<%s,W=1,K=%d,L=%d> ch=%d stages=2", scalar_name<T>(), K, L, lay.ch);
+            note_kernel_f("opsa_vjp_pipe<%s,W=1,K=%d,L=%d> ch=%d stages=2 g=%d", scalar_name<T>(), K, L, lay.ch,
+                          lay.g_slots);
 #define MOPS_B200_CASE(K_)                                                                         \
     {                                                                                              \
         auto kernel = opsa_vjp_pipe<T, (K_ + 3) / 4, 4, true, K_, 32>;                             \

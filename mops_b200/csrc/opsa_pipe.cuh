@@ -27,8 +27,9 @@ struct PipeLayout {
     int stages_log2;
     int a_off, b_off, w_off, pw_off; // byte offsets inside a stage (16-byte aligned)
     int stage_bytes;
-    int g_off;    // grad_output ring (VJP): two rows of g_bytes each; unused in the forward
+    int g_off;    // grad_output ring (VJP): g_slots rows of g_bytes each; unused in the forward
     int g_bytes;
+    int g_slots;  // 2, or 1 when rows are long (the next row's copy then has a whole row's time)
     int bar_off;  // mbarriers: one per stage, then two for the grad_output ring
     int warp_bytes;
 };
@@ -38,7 +39,7 @@ constexpr int kPipeWarps = 4;
 __host__ __device__ constexpr int round16(size_t n) { return static_cast<int>((n + 15) / 16 * 16); }
 
 __host__ __device__ constexpr PipeLayout pipe_layout(size_t s, int K, int L, bool weighted, bool vjp, int ch,
-                                                     int stages) {
+                                                     int stages, int g_slots = 2) {
     PipeLayout p{};
     p.K = K, p.L = L;
     p.LP = weighted ? L + 4 : L;
@@ -56,7 +57,8 @@ __host__ __device__ constexpr PipeLayout pipe_layout(size_t s, int K, int L, boo
     p.stage_bytes = weighted ? p.pw_off + round16(static_cast<size_t>(ch) * 4) : p.pw_off;
     p.g_bytes = static_cast<int>(static_cast<size_t>(K) * L * s);
     p.g_off = p.stages * p.stage_bytes;
-    p.bar_off = p.g_off + (vjp ? 2 * round16(p.g_bytes) : 0);
+    p.g_slots = g_slots < 2 ? 1 : 2;
+    p.bar_off = p.g_off + (vjp ? p.g_slots * round16(p.g_bytes) : 0);
     p.warp_bytes = (p.bar_off + 8 * (p.stages + 2) + 127) / 128 * 128;
     return p;
 }
@@ -187,7 +189,10 @@ template <typename S, bool WEIGHTED, bool VJP, int KC, int LC>
 __device__ __forceinline__ PipeLayout fixed_layout_or(const PipeLayout& run_time) {
     if constexpr (KC > 0) {
         constexpr PipeLayout fixed = pipe_layout(sizeof(S), KC, LC, WEIGHTED, VJP, kFixedChunk<WEIGHTED>, 2);
-        return fixed;
+        PipeLayout lay = fixed;
+        // the depth of the grad_output ring is the host's choice: it moves what lies behind it
+        lay.g_slots = run_time.g_slots, lay.bar_off = run_time.bar_off, lay.warp_bytes = run_time.warp_bytes;
+        return lay;
     } else {
         return run_time;
     }
@@ -372,7 +377,7 @@ opsa_fwd_pipe(S* __restrict__ O, const S* __restrict__ A, const S* __restrict__ 
 // MMA fragments while the row lasts; entries are the MMA's m dimension, eight per tile.
 // KT = ceil(K / 4), LT8 = ceil(L / 8).
 template <typename S, int KT, int LT8, bool WEIGHTED, int KC = 0, int LC = 0>
-__global__ void __launch_bounds__(kPipeWarps * 32, 3)
+__global__ void __launch_bounds__(kPipeWarps * 32, (KC > 0 && WEIGHTED) ? 4 : 3)
 opsa_vjp_pipe(S* __restrict__ gA, S* __restrict__ gB, S* __restrict__ gW,
               const S* __restrict__ gO, const S* __restrict__ A, const S* __restrict__ B,
               const S* __restrict__ W, const int32_t* __restrict__ PW,
@@ -431,16 +436,17 @@ opsa_vjp_pipe(S* __restrict__ gA, S* __restrict__ gB, S* __restrict__ gW,
         }
     };
     // grad_output rows r0, r0 + 1, ... go through a ring of two slots
+    const bool two_slots = lay.g_slots == 2;
     auto issue_g = [&](int64_t r) {
         if (r < w.r1 && lane == 0) {
-            const int slot = static_cast<int>(r - w.r0) & 1;
+            const int slot = two_slots ? static_cast<int>(r - w.r0) & 1 : 0;
             mbarrier_arrive_expect(gbars + slot, static_cast<unsigned>(lay.g_bytes));
             bulk_copy_in(area + lay.g_off + slot * g_slot_bytes, gO + r * rowsize,
                          static_cast<unsigned>(lay.g_bytes), gbars + slot);
         }
     };
     issue_g(w.r0);
-    issue_g(w.r0 + 1);
+    if (two_slots) issue_g(w.r0 + 1);
     for (int i = 0; i < NS - 1; i++) issue_next();
 
     int64_t wbase = w.r0;
@@ -465,12 +471,13 @@ opsa_vjp_pipe(S* __restrict__ gA, S* __restrict__ gB, S* __restrict__ gW,
     // the slot to row r + 2.
     auto enter_row = [&](int64_t r, bool has_entries) {
         const int use = static_cast<int>(r - w.r0);
-        if (!mbarrier_wait(gbars + (use & 1), (use >> 1) & 1)) {
+        const int slot = two_slots ? use & 1 : 0;
+        if (!mbarrier_wait(gbars + slot, (two_slots ? use >> 1 : use) & 1)) {
             stalled = true;
             return;
         }
         if (has_entries) {
-            const S* g = reinterpret_cast<const S*>(area + lay.g_off + (use & 1) * g_slot_bytes);
+            const S* g = reinterpret_cast<const S*>(area + lay.g_off + slot * g_slot_bytes);
 #pragma unroll
             for (int nt = 0; nt < NTK; nt++)
 #pragma unroll
@@ -487,7 +494,7 @@ opsa_vjp_pipe(S* __restrict__ gA, S* __restrict__ gB, S* __restrict__ gW,
                 }
         }
         __syncwarp(); // every lane has its fragments: the slot can be refilled
-        issue_g(r + 2);
+        issue_g(r + (two_slots ? 2 : 1));
     };
 
     // positions of entries below are relative to e_first (the warp's range fits an int)

@@ -160,6 +160,14 @@ def test_weighted_outer_product_fixed_shapes(oracle, K, dtype):
     po.sort()
     compare("opsaw", d, dtype, oracle, what=f"opsaw fixed {K}x32")
     compare("opsaw", workloads.opsaw(E=7, K=K, L=32, n=3), dtype, oracle, what=f"opsaw tiny {K}x32")
+    # long rows on average (the VJP then keeps one grad_output slot per warp), among them
+    # empty rows and rows of a single entry
+    d = workloads.opsaw(E=6001, K=K, L=32, n=60)
+    po = d["indices_output"]
+    po[(po % 7 == 3) & (po < 59)] += 1
+    po[:3] = 0
+    po.sort()
+    compare("opsaw", d, dtype, oracle, what=f"opsaw fixed {K}x32, long rows")
 
 
 @pytest.mark.parametrize("seed", list(range(16)))
